@@ -1,0 +1,57 @@
+"""Build recipe of libb2fil.so: nvcc for sm_100a, in-tree output under cuml_b200/lib/.
+
+`python -m cuml_b200.build [--force] [--verbose]` (also called by `__graft_entry__.build()`).
+The register / shared-memory report of ptxas is written to cuml_b200/lib/ptxas.log.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "csrc")
+LIB_DIR = os.path.join(HERE, "lib")
+LIB = os.path.join(LIB_DIR, "libb2fil.so")
+SOURCES = ["api.cu", "kernels.cu", "pack.cpp"]
+HEADERS = ["forest.hpp", "kernels.hpp", os.path.join("..", "..", "include", "b2fil.h")]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; libb2fil.so cannot be built")
+    return exe
+
+
+def up_to_date() -> bool:
+    if not os.path.exists(LIB):
+        return False
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(SRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    return all((not os.path.exists(d)) or os.path.getmtime(d) <= t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and up_to_date():
+        return LIB
+    if not all(os.path.exists(os.path.join(SRC, s)) for s in SOURCES):
+        raise RuntimeError("kernel sources missing; cannot build libb2fil.so")
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
+           "-std=c++17", "-Xcompiler", "-fPIC,-Wall", "-Xptxas", "-v", "-shared", "-o", LIB]
+    cmd += [os.path.join(SRC, s) for s in SOURCES]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    with open(os.path.join(LIB_DIR, "ptxas.log"), "w") as fh:
+        fh.write(" ".join(cmd) + "\n" + proc.stdout)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout)
+        raise RuntimeError("nvcc failed building libb2fil.so")
+    if verbose:
+        print(proc.stdout)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,483 @@
+// C-ABI layer of libb2fil.so: error convention, forest lifetime, prediction entry points.
+// Declarations and the reference interfaces they replace are in include/b2fil.h.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "forest.hpp"
+#include "kernels.hpp"
+
+using namespace b2fil;
+
+namespace {
+
+thread_local std::string g_last_error;
+std::atomic<int64_t> g_launches{0};
+
+int set_error(int code, const std::string& msg)
+{
+  g_last_error = msg;
+  return code;
+}
+int cuda_error(const char* what, cudaError_t e)
+{
+  return set_error(B2FIL_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define B2FIL_CUDA(call)                                  \
+  do {                                                    \
+    const cudaError_t e_ = (call);                        \
+    if (e_ != cudaSuccess) return cuda_error(#call, e_);  \
+  } while (0)
+
+// Makes a device current for the lifetime of the guard and restores the previous one.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok  = false;
+  explicit DeviceGuard(int dev)
+  {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    ok = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard()
+  {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace
+
+// One slot of the host-buffer pipeline: device staging buffers and the stream that orders them.
+struct HostSlot {
+  cudaStream_t stream = nullptr;
+  void* x             = nullptr;
+  void* out           = nullptr;
+  size_t x_bytes      = 0;
+  size_t out_bytes    = 0;
+};
+
+struct b2fil_forest {
+  ForestView view{};
+  int32_t precision = B2FIL_F32, storage = 0, layout = 0, align_bytes = 0, node_bytes = 0;
+  int32_t device = 0, sm_count = 0, default_chunk = 0;
+  int64_t n_nodes_in = 0, n_nodes_packed = 0, device_bytes = 0;
+  int32_t* status = nullptr;
+  struct Block {
+    void* ptr;
+    size_t bytes;
+    size_t view_offset;  // offset of the pointer member inside ForestView
+  };
+  std::vector<Block> blocks;
+  std::mutex host_mu;  // serialises the calls that use the slots below
+  HostSlot slots[2];
+  ~b2fil_forest()
+  {
+    DeviceGuard g(device);
+    for (auto& b : blocks) cudaFree(b.ptr);
+    if (status) cudaFree(status);
+    for (auto& s : slots) {
+      if (s.x) cudaFree(s.x);
+      if (s.out) cudaFree(s.out);
+      if (s.stream) cudaStreamDestroy(s.stream);
+    }
+  }
+};
+
+namespace {
+
+template <typename V>
+int upload(b2fil_forest* f, const V& host, size_t view_offset)
+{
+  if (host.empty()) return B2FIL_OK;
+  const size_t bytes = host.size() * sizeof(typename V::value_type);
+  void* d            = nullptr;
+  cudaError_t e      = cudaMalloc(&d, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return set_error(B2FIL_ERR_NO_MEMORY, "device allocation of " + std::to_string(bytes) +
+                                            " bytes for the forest failed");
+  }
+  if (e != cudaSuccess) return cuda_error("cudaMalloc", e);
+  f->blocks.push_back({d, bytes, view_offset});
+  f->device_bytes += static_cast<int64_t>(bytes);
+  B2FIL_CUDA(cudaMemcpy(d, host.data(), bytes, cudaMemcpyHostToDevice));
+  std::memcpy(reinterpret_cast<char*>(&f->view) + view_offset, &d, sizeof(void*));
+  return B2FIL_OK;
+}
+
+int init_device_state(b2fil_forest* f)
+{
+  cudaDeviceProp prop;
+  B2FIL_CUDA(cudaGetDeviceProperties(&prop, f->device));
+  f->sm_count = prop.multiProcessorCount;
+  B2FIL_CUDA(cudaMalloc(&f->status, sizeof(int32_t)));
+  B2FIL_CUDA(cudaMemset(f->status, 0, sizeof(int32_t)));
+  return B2FIL_OK;
+}
+
+size_t elem_bytes(const b2fil_forest* f) { return f->precision == B2FIL_F32 ? 4 : 8; }
+
+int64_t out_elems(const b2fil_forest* f, int kind)
+{
+  switch (kind) {
+    case B2FIL_INFER_DEFAULT: return f->view.n_outputs;
+    case B2FIL_INFER_PER_TREE:
+      return static_cast<int64_t>(f->view.n_trees) *
+             (f->view.leaf_vector_len > 1 ? f->view.n_outputs : 1);
+    case B2FIL_INFER_LEAF_ID: return f->view.n_trees;
+    case B2FIL_INFER_CLASS: return 1;
+    case B2FIL_INFER_PROBA2: return 2;
+    default: return 0;
+  }
+}
+size_t out_elem_bytes(const b2fil_forest* f, int kind)
+{
+  if (kind == B2FIL_INFER_LEAF_ID || kind == B2FIL_INFER_CLASS) return 4;
+  return elem_bytes(f);
+}
+
+int check_predict_args(const b2fil_forest* f, int kind, const void* X, int64_t n_rows,
+                       int64_t row_stride, const void* out)
+{
+  if (!f) return set_error(B2FIL_ERR_INVALID_ARG, "forest is NULL");
+  if (out_elems(f, kind) == 0) return set_error(B2FIL_ERR_INVALID_ARG, "unknown infer_kind");
+  if (n_rows < 0) return set_error(B2FIL_ERR_INVALID_ARG, "n_rows is negative");
+  if (n_rows > 0 && (!X || !out)) return set_error(B2FIL_ERR_INVALID_ARG, "NULL buffer");
+  if (row_stride < f->view.n_features)
+    return set_error(B2FIL_ERR_INVALID_ARG, "row_stride is smaller than n_features");
+  if (kind == B2FIL_INFER_PROBA2 && f->view.n_outputs != 1)
+    return set_error(B2FIL_ERR_INVALID_ARG, "B2FIL_INFER_PROBA2 needs a forest with one output");
+  return B2FIL_OK;
+}
+
+int enqueue(const b2fil_forest* f, int kind, const void* X, int64_t n_rows, int64_t row_stride,
+            void* out, int chunk_size, double threshold, cudaStream_t stream)
+{
+  PredictParams p{};
+  p.f          = f->view;
+  p.X          = X;
+  p.n_rows     = n_rows;
+  p.row_stride = row_stride;
+  p.out        = out;
+  p.kind       = kind;
+  p.threshold  = threshold;
+  p.status     = f->status;
+  std::string err;
+  int64_t n = 0;
+  const int rc =
+    launch_predict(p, chunk_size > 0 ? chunk_size : f->default_chunk, f->sm_count, stream, err, &n);
+  g_launches += n;
+  if (rc != B2FIL_OK) return set_error(rc, err);
+  return B2FIL_OK;
+}
+
+int ensure_slot(b2fil_forest* f, HostSlot& s, size_t x_bytes, size_t out_bytes)
+{
+  if (!s.stream) B2FIL_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+  if (s.x_bytes < x_bytes) {
+    if (s.x) cudaFree(s.x);
+    s.x = nullptr;
+    s.x_bytes = 0;
+    B2FIL_CUDA(cudaMalloc(&s.x, x_bytes));
+    s.x_bytes = x_bytes;
+  }
+  if (s.out_bytes < out_bytes) {
+    if (s.out) cudaFree(s.out);
+    s.out = nullptr;
+    s.out_bytes = 0;
+    B2FIL_CUDA(cudaMalloc(&s.out, out_bytes));
+    s.out_bytes = out_bytes;
+  }
+  (void)f;
+  return B2FIL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* b2fil_last_error(void) { return g_last_error.c_str(); }
+
+int b2fil_version(void) { return 100; }
+
+int64_t b2fil_kernel_launches(void) { return g_launches.load(); }
+
+int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* opts,
+                        b2fil_forest** out)
+{
+  if (!desc || !opts || !out) return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument");
+  *out = nullptr;
+  try {
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return set_error(B2FIL_ERR_CUDA, std::string("no usable CUDA device: ") +
+                                         cudaGetErrorString(e));
+    }
+    if (opts->device_id < 0 || opts->device_id >= n_dev)
+      return set_error(B2FIL_ERR_INVALID_ARG, "device_id " + std::to_string(opts->device_id) +
+                                                " out of range (" + std::to_string(n_dev) +
+                                                " devices)");
+    PackedForest pf;
+    std::string err;
+    int rc = pack_forest(*desc, *opts, dense_ok, pf, err);
+    if (rc != B2FIL_OK) return set_error(rc, err);
+
+    std::unique_ptr<b2fil_forest> f(new b2fil_forest());
+    f->device = opts->device_id;
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+    f->view           = pf.view;
+    f->precision      = pf.precision;
+    f->storage        = pf.storage;
+    f->layout         = opts->layout;
+    f->align_bytes    = pf.align_bytes;
+    f->node_bytes     = pf.node_bytes;
+    f->n_nodes_in     = pf.n_nodes_in;
+    f->n_nodes_packed = pf.n_nodes_packed;
+    f->default_chunk  = std::max(0, opts->default_chunk_size);
+    if ((rc = init_device_state(f.get())) != B2FIL_OK) return rc;
+    if ((rc = upload(f.get(), pf.nodes, offsetof(ForestView, nodes))) != B2FIL_OK) return rc;
+    if ((rc = upload(f.get(), pf.roots, offsetof(ForestView, roots))) != B2FIL_OK) return rc;
+    if ((rc = upload(f.get(), pf.leaf_ids, offsetof(ForestView, leaf_ids))) != B2FIL_OK) return rc;
+    if ((rc = upload(f.get(), pf.cat_pool, offsetof(ForestView, cat_pool))) != B2FIL_OK) return rc;
+    if ((rc = upload(f.get(), pf.tree_class, offsetof(ForestView, tree_class))) != B2FIL_OK)
+      return rc;
+    if ((rc = upload(f.get(), pf.tree_orig, offsetof(ForestView, tree_orig))) != B2FIL_OK)
+      return rc;
+    if ((rc = upload(f.get(), pf.leaf_vectors, offsetof(ForestView, leaf_vectors))) != B2FIL_OK)
+      return rc;
+    if ((rc = upload(f.get(), pf.out_scale, offsetof(ForestView, out_scale))) != B2FIL_OK)
+      return rc;
+    if ((rc = upload(f.get(), pf.out_bias, offsetof(ForestView, out_bias))) != B2FIL_OK) return rc;
+    *out = f.release();
+    return B2FIL_OK;
+  } catch (const std::bad_alloc&) {
+    return set_error(B2FIL_ERR_NO_MEMORY, "host allocation failed while packing the forest");
+  } catch (const std::exception& ex) {
+    return set_error(B2FIL_ERR_INVALID_ARG, std::string("unexpected failure: ") + ex.what());
+  }
+}
+
+int b2fil_forest_clone_to_device(const b2fil_forest* src, int device_id, b2fil_forest** out)
+{
+  if (!src || !out) return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument");
+  *out = nullptr;
+  try {
+    int n_dev = 0;
+    B2FIL_CUDA(cudaGetDeviceCount(&n_dev));
+    if (device_id < 0 || device_id >= n_dev)
+      return set_error(B2FIL_ERR_INVALID_ARG, "device_id out of range");
+    std::unique_ptr<b2fil_forest> f(new b2fil_forest());
+    f->view           = src->view;
+    f->precision      = src->precision;
+    f->storage        = src->storage;
+    f->layout         = src->layout;
+    f->align_bytes    = src->align_bytes;
+    f->node_bytes     = src->node_bytes;
+    f->n_nodes_in     = src->n_nodes_in;
+    f->n_nodes_packed = src->n_nodes_packed;
+    f->default_chunk  = src->default_chunk;
+    f->device         = device_id;
+    DeviceGuard guard(device_id);
+    if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+    int rc;
+    if ((rc = init_device_state(f.get())) != B2FIL_OK) return rc;
+    for (const auto& b : src->blocks) {
+      void* d       = nullptr;
+      cudaError_t e = cudaMalloc(&d, b.bytes);
+      if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return set_error(B2FIL_ERR_NO_MEMORY, "device allocation for the forest copy failed");
+      }
+      if (e != cudaSuccess) return cuda_error("cudaMalloc", e);
+      f->blocks.push_back({d, b.bytes, b.view_offset});
+      f->device_bytes += static_cast<int64_t>(b.bytes);
+      // cudaMemcpyPeer uses a direct peer path when the devices can reach each other and stages
+      // through the host otherwise
+      B2FIL_CUDA(cudaMemcpyPeer(d, device_id, b.ptr, src->device, b.bytes));
+      std::memcpy(reinterpret_cast<char*>(&f->view) + b.view_offset, &d, sizeof(void*));
+    }
+    *out = f.release();
+    return B2FIL_OK;
+  } catch (const std::bad_alloc&) {
+    return set_error(B2FIL_ERR_NO_MEMORY, "host allocation failed");
+  }
+}
+
+int b2fil_forest_free(b2fil_forest* f)
+{
+  delete f;
+  return B2FIL_OK;
+}
+
+int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info)
+{
+  if (!f || !info) return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument");
+  std::memset(info, 0, sizeof(*info));
+  info->precision          = f->precision;
+  info->layout             = f->layout;
+  info->storage            = f->storage;
+  info->device_id          = f->device;
+  info->n_trees            = f->view.n_trees;
+  info->n_features         = f->view.n_features;
+  info->n_outputs          = f->view.n_outputs;
+  info->leaf_vector_len    = f->view.leaf_vector_len;
+  info->max_depth          = f->view.max_depth;
+  info->dense_depth        = f->view.dense_depth;
+  info->node_bytes         = f->node_bytes;
+  info->has_categorical    = f->view.has_categorical;
+  info->n_nodes_in         = f->n_nodes_in;
+  info->n_nodes_packed     = f->n_nodes_packed;
+  info->device_bytes       = f->device_bytes;
+  info->default_chunk_size = f->default_chunk;
+  return B2FIL_OK;
+}
+
+int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind)
+{
+  if (!f) {
+    set_error(B2FIL_ERR_INVALID_ARG, "forest is NULL");
+    return 0;
+  }
+  const int64_t n = out_elems(f, infer_kind);
+  if (n == 0) set_error(B2FIL_ERR_INVALID_ARG, "unknown infer_kind");
+  return n;
+}
+
+int b2fil_forest_status(const b2fil_forest* f, int32_t* status)
+{
+  if (!f || !status) return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument");
+  DeviceGuard guard(f->device);
+  B2FIL_CUDA(cudaMemcpy(status, f->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (*status != 0)
+    return set_error(B2FIL_ERR_TIMEOUT, "a bounded wait inside a prediction kernel ran out");
+  return B2FIL_OK;
+}
+
+int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int64_t n_rows,
+                  int64_t row_stride, void* out_dev, int chunk_size, double threshold,
+                  void* cuda_stream)
+{
+  int rc = check_predict_args(f, infer_kind, X_dev, n_rows, row_stride, out_dev);
+  if (rc != B2FIL_OK) return rc;
+  DeviceGuard guard(f->device);
+  if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+  return enqueue(f, infer_kind, X_dev, n_rows, row_stride, out_dev, chunk_size, threshold,
+                 static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int64_t n_rows,
+                       int64_t row_stride, void* out_host, int chunk_size, double threshold)
+{
+  int rc = check_predict_args(f, infer_kind, X_host, n_rows, row_stride, out_host);
+  if (rc != B2FIL_OK) return rc;
+  if (n_rows == 0) return B2FIL_OK;
+  std::lock_guard<std::mutex> lock(f->host_mu);
+  DeviceGuard guard(f->device);
+  if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+  const size_t es        = elem_bytes(f);
+  const int64_t F        = f->view.n_features;
+  const size_t in_row_b  = static_cast<size_t>(F) * es;
+  const size_t out_row_b = static_cast<size_t>(out_elems(f, infer_kind)) * out_elem_bytes(f, infer_kind);
+  // row blocks of about 256 MiB of input (and at most 256 MiB of output) keep both copy engines
+  // and the SMs busy while two blocks are in flight
+  const size_t budget = size_t(256) << 20;
+  int64_t block_rows  = static_cast<int64_t>(std::max<size_t>(1, budget / std::max(in_row_b, out_row_b)));
+  block_rows          = std::max<int64_t>(block_rows / 128 * 128, 128);
+  block_rows          = std::min(block_rows, n_rows);
+  for (auto& s : f->slots) {
+    rc = ensure_slot(f, s, static_cast<size_t>(block_rows) * in_row_b,
+                     static_cast<size_t>(block_rows) * out_row_b);
+    if (rc != B2FIL_OK) return rc;
+  }
+  const char* xin = static_cast<const char*>(X_host);
+  char* yout      = static_cast<char*>(out_host);
+  int which       = 0;
+  for (int64_t r0 = 0; r0 < n_rows; r0 += block_rows, which ^= 1) {
+    HostSlot& s     = f->slots[which];
+    const int64_t n = std::min(block_rows, n_rows - r0);
+    // stream order makes the slot's previous block finish before its buffers are reused
+    if (row_stride == F) {
+      B2FIL_CUDA(cudaMemcpyAsync(s.x, xin + static_cast<size_t>(r0) * in_row_b,
+                                 static_cast<size_t>(n) * in_row_b, cudaMemcpyHostToDevice,
+                                 s.stream));
+    } else {
+      B2FIL_CUDA(cudaMemcpy2DAsync(s.x, in_row_b, xin + static_cast<size_t>(r0) * row_stride * es,
+                                   static_cast<size_t>(row_stride) * es, in_row_b,
+                                   static_cast<size_t>(n), cudaMemcpyHostToDevice, s.stream));
+    }
+    rc = enqueue(f, infer_kind, s.x, n, F, s.out, chunk_size, threshold, s.stream);
+    if (rc != B2FIL_OK) return rc;
+    B2FIL_CUDA(cudaMemcpyAsync(yout + static_cast<size_t>(r0) * out_row_b, s.out,
+                               static_cast<size_t>(n) * out_row_b, cudaMemcpyDeviceToHost,
+                               s.stream));
+  }
+  for (auto& s : f->slots) B2FIL_CUDA(cudaStreamSynchronize(s.stream));
+  int32_t status = 0;
+  return b2fil_forest_status(f, &status);
+}
+
+int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer_kind,
+                          const void* const* X_shards, const int64_t* shard_rows,
+                          int64_t row_stride, void* out_dev0, int chunk_size, double threshold)
+{
+  if (!forests || !X_shards || !shard_rows || n_devices <= 0)
+    return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument or no devices");
+  for (int i = 0; i < n_devices; ++i) {
+    if (!forests[i]) return set_error(B2FIL_ERR_INVALID_ARG, "forest is NULL");
+    const int rc = check_predict_args(forests[i], infer_kind, X_shards[i], shard_rows[i],
+                                      row_stride, out_dev0);
+    if (rc != B2FIL_OK) return rc;
+  }
+  b2fil_forest* f0       = forests[0];
+  const size_t out_row_b = static_cast<size_t>(out_elems(f0, infer_kind)) * out_elem_bytes(f0, infer_kind);
+  // every device predicts its shard on its own stream; shards of devices other than the first
+  // land in a staging buffer on their device and are pushed to device 0 by a peer copy
+  std::vector<std::unique_lock<std::mutex>> locks;
+  for (int i = 0; i < n_devices; ++i) locks.emplace_back(forests[i]->host_mu);
+  int64_t row_off = 0;
+  for (int i = 0; i < n_devices; ++i) {
+    b2fil_forest* f = forests[i];
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+    HostSlot& s     = f->slots[0];
+    const int64_t n = shard_rows[i];
+    char* dst0      = static_cast<char*>(out_dev0) + static_cast<size_t>(row_off) * out_row_b;
+    row_off += n;
+    if (n == 0) continue;
+    const bool local = f->device == f0->device;
+    int rc = ensure_slot(f, s, 0, local ? 0 : static_cast<size_t>(n) * out_row_b);
+    if (rc != B2FIL_OK) return rc;
+    rc = enqueue(f, infer_kind, X_shards[i], n, row_stride, local ? static_cast<void*>(dst0) : s.out,
+                 chunk_size, threshold, s.stream);
+    if (rc != B2FIL_OK) return rc;
+    if (!local) {
+      B2FIL_CUDA(cudaMemcpyPeerAsync(dst0, f0->device, s.out, f->device,
+                                     static_cast<size_t>(n) * out_row_b, s.stream));
+    }
+  }
+  int rc_final = B2FIL_OK;
+  for (int i = 0; i < n_devices; ++i) {
+    b2fil_forest* f = forests[i];
+    DeviceGuard guard(f->device);
+    if (f->slots[0].stream) {
+      const cudaError_t e = cudaStreamSynchronize(f->slots[0].stream);
+      if (e != cudaSuccess && rc_final == B2FIL_OK) rc_final = cuda_error("cudaStreamSynchronize", e);
+    }
+    int32_t status = 0;
+    const int rc   = b2fil_forest_status(f, &status);
+    if (rc != B2FIL_OK && rc_final == B2FIL_OK) rc_final = rc;
+  }
+  return rc_final;
+}
+
+}  // extern "C"

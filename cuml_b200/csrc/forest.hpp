@@ -1,0 +1,129 @@
+// Packed-forest types shared by the host packer, the kernels and the C-ABI layer.
+//
+// Two device storages exist.
+//
+// DENSE: every tree is padded to a complete binary tree of depth D (the forest's maximum depth)
+// and stored in heap order with 1-based indices: the root is node 1, the children of node i are
+// 2i and 2i+1, level d is [2^d, 2^(d+1)), leaf slot j is heap index 2^D + j.  One tree is one
+// contiguous block
+//     [ 2^D test nodes (entry 0 unused) ][ 2^D leaf payloads ]
+// so that a whole tree moves to shared memory with one bulk copy and no child index is stored.
+//
+// SPARSE: nodes keep an offset to their children and honour the requested node order
+// (depth-first: left child adjacent, offset to the right child; breadth-first / layered:
+// children adjacent to each other, offset to the left child).
+//
+// In both storages every numerical test is normalised at import to "x < threshold goes left" and
+// every categorical test to "listed category goes right", by swapping children and moving
+// thresholds to the next representable value where needed, so the kernels evaluate one operator.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/b2fil.h"
+
+namespace b2fil {
+
+// ---- meta word of a test node -----------------------------------------------------------------
+// bit 31: a missing value goes left; bit 30: categorical test; bit 29: leaf (sparse only).
+// Dense nodes keep the feature index in bits 0..29.  The two top bits fall off the end of the
+// 32-bit shared-memory address when the meta word is multiplied by a row stride that is a
+// multiple of four bytes, so the hot loop never masks them.
+constexpr uint32_t META_DEFAULT_LEFT = 0x80000000u;
+constexpr uint32_t META_CATEGORICAL  = 0x40000000u;
+constexpr uint32_t META_LEAF         = 0x20000000u;
+constexpr uint32_t META_LOW29        = 0x1FFFFFFFu;
+
+// ---- node records -----------------------------------------------------------------------------
+struct DenseNodeF {  // 8 bytes
+  uint32_t value;    // float threshold bits | inline category bitset | category pool offset
+  uint32_t meta;     // flags | feature
+};
+struct DenseNodeD {  // 16 bytes
+  uint64_t value;    // double threshold bits | bitset / pool offset in the low word
+  uint32_t meta;
+  uint32_t pad;
+};
+struct SparseNode8 {  // fp32, compact: feature and child offset share the low 29 meta bits
+  uint32_t value;     // threshold | bitset | pool offset | leaf scalar | leaf-vector index
+  uint32_t meta;      // flags | offset << feat_bits | feature
+};
+struct SparseNode16F {  // fp32, wide
+  uint32_t value;
+  uint32_t meta;  // flags | feature
+  uint32_t offset;
+  uint32_t pad;
+};
+struct SparseNode16D {  // fp64
+  uint64_t value;
+  uint32_t meta;  // flags | feature
+  uint32_t offset;
+};
+
+enum NodeFormat : int32_t {
+  FMT_DENSE_F   = 0,
+  FMT_DENSE_D   = 1,
+  FMT_SPARSE_8  = 2,
+  FMT_SPARSE_16F = 3,
+  FMT_SPARSE_16D = 4,
+};
+
+// Device view handed to kernels by value.  Pointers are device pointers on the forest's device.
+struct ForestView {
+  int32_t format;
+  int32_t n_trees;
+  int32_t n_features;
+  int32_t n_outputs;
+  int32_t leaf_vector_len;
+  int32_t postproc;
+  int32_t has_categorical;
+  int32_t cat_inline;       // 1: every category list fits a 32-bit inline bitset
+  int32_t max_depth;        // loop bound of sparse traversal
+  int32_t dense_depth;      // D
+  int32_t feat_bits;        // SparseNode8: width of the feature field
+  int32_t layout;
+  int64_t tree_stride;      // dense: bytes between trees
+  const void* nodes;        // dense: tree blocks; sparse: node array
+  const uint32_t* roots;    // sparse: index of every tree's root in `nodes`
+  const uint32_t* leaf_ids; // dense: [n_trees << D] id per leaf slot; sparse: [n_nodes] id per node
+  const uint32_t* cat_pool; // [n_words, words...] records of large category lists
+  const int32_t* tree_class;// [n_trees] output a scalar leaf adds to (packed tree order)
+  const int32_t* tree_orig; // [n_trees] index of the packed tree in the description
+  const void* leaf_vectors; // [n_vectors * n_outputs] of the forest precision
+  const void* out_scale;    // [n_outputs] 1/divisor of average_tree_output (or 1)
+  const void* out_bias;     // [n_outputs] base scores
+  double sigmoid_alpha;
+  double ratio_c;
+};
+
+// Host-side result of packing, before upload.
+struct PackedForest {
+  ForestView view{};  // pointer members unset
+  int32_t precision = B2FIL_F32;
+  int32_t storage   = B2FIL_STORAGE_SPARSE;
+  int32_t align_bytes = 0;
+  int32_t node_bytes = 0;
+  int64_t n_nodes_in = 0;
+  int64_t n_nodes_packed = 0;
+  std::vector<uint8_t> nodes;
+  std::vector<uint32_t> roots;
+  std::vector<uint32_t> leaf_ids;
+  std::vector<uint32_t> cat_pool;
+  std::vector<int32_t> tree_class;
+  std::vector<int32_t> tree_orig;
+  std::vector<uint8_t> leaf_vectors;
+  std::vector<uint8_t> out_scale;
+  std::vector<uint8_t> out_bias;
+};
+
+// Validate `desc`, normalise its tests and lay its nodes out.  Returns B2FIL_OK or an error code
+// with `err` set.  `dense_ok(depth, precision, n_features, n_outputs)` tells whether the dense
+// kernel can run a forest of that shape (shared-memory fit); AUTO storage asks it.
+int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
+                bool (*dense_ok)(int depth, int precision, int n_features, int n_outputs),
+                PackedForest& out,
+                std::string& err);
+
+}  // namespace b2fil

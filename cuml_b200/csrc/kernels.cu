@@ -1,0 +1,913 @@
+// Prediction kernels for sm_100a.
+//
+// Work decomposition (both storages): a CTA owns a tile of R consecutive rows, staged once in
+// shared memory feature-major (`tile[f][r]`, row stride R+1 elements) so that the 32 lanes of a
+// warp - 32 different rows - always read 32 different banks whatever feature each lane needs.
+// Warps are organised as (R/32 row sets) x (G tree groups): every warp walks its 32 rows through
+// the trees of its group, NT trees at a time for instruction-level parallelism, and keeps its
+// partial sums private; a fixed-order reduction over the G groups, averaging, base score and the
+// postprocessor run in the CTA's epilogue, so one launch reads every row once and writes every
+// result once.
+//
+// DENSE storage: trees are complete and heap ordered, so a step is "load node, load feature,
+// compare, index = 2*index + went_right" with no child pointer.  A producer warp streams batches
+// of G*NT whole trees from global memory (L2 resident) into a ring of shared-memory stages with
+// bulk asynchronous copies (cp.async.bulk, completion on an mbarrier); consumer warps release a
+// stage through a second mbarrier.  CTAs are persistent (one per SM) and loop over row tiles.
+//
+// SPARSE storage: nodes are fetched from global memory through the read-only path; each thread
+// keeps NT independent traversals in flight to cover the latency of the dependent loads.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel sets the status word,
+// stops working and returns.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "kernels.hpp"
+
+namespace b2fil {
+namespace {
+
+constexpr uint32_t kSpinLimit = 1u << 24;  // tries of a bounded mbarrier wait
+constexpr int kBarBytes       = 128;       // room for the mbarriers at the start of shared memory
+constexpr int kMaxStages      = 4;
+
+// ---------------------------------------------------------------------------------------------
+// shared-memory and mbarrier primitives (inline PTX)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p)
+{
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init()
+{
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile(
+    "{\n"
+    ".reg .pred p;\n"
+    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+    "selp.u32 %0, 1, 0, p;\n"
+    "}\n"
+    : "=r"(ok)
+    : "r"(bar), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the barrier did not complete within kSpinLimit tries.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+// Bulk asynchronous copy global -> shared memory of this CTA, completing `bytes` on `bar`.
+// Both addresses are 16-byte aligned and `bytes` is a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar)
+{
+  asm volatile(
+    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+      dst),
+    "l"(src), "r"(bytes), "r"(bar)
+    : "memory");
+}
+// Barrier among the consumer threads only (the producer warp never joins it).
+__device__ __forceinline__ void consumer_sync(int n_threads)
+{
+  asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-precision traits
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct Traits;
+
+template <>
+struct Traits<float> {
+  using Val                    = uint32_t;
+  static constexpr uint32_t NB = 8;  // dense node bytes
+  static constexpr uint32_t ES = 4;  // element bytes (rows, leaves, outputs)
+  static __device__ __forceinline__ void ld_node(uint32_t a, Val& v, uint32_t& m)
+  {
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(m) : "r"(a));
+  }
+  static __device__ __forceinline__ float ld_real(uint32_t a)
+  {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+  }
+  static __device__ __forceinline__ void st_real(uint32_t a, float v)
+  {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+  }
+  static __device__ __forceinline__ Val ld_val(uint32_t a)
+  {
+    Val v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+  }
+  static __device__ __forceinline__ float as_real(Val v) { return __uint_as_float(v); }
+  static __device__ __forceinline__ uint32_t low32(Val v) { return v; }
+  static __device__ __forceinline__ float exp_(float x) { return expf(x); }
+  static __device__ __forceinline__ float exp2_(float x) { return exp2f(x); }
+  static __device__ __forceinline__ float log1p_(float x) { return log1pf(x); }
+};
+
+template <>
+struct Traits<double> {
+  using Val                    = uint64_t;
+  static constexpr uint32_t NB = 16;
+  static constexpr uint32_t ES = 8;
+  static __device__ __forceinline__ void ld_node(uint32_t a, Val& v, uint32_t& m)
+  {
+    uint64_t second;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v), "=l"(second) : "r"(a));
+    m = static_cast<uint32_t>(second);
+  }
+  static __device__ __forceinline__ double ld_real(uint32_t a)
+  {
+    double v;
+    asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(a));
+    return v;
+  }
+  static __device__ __forceinline__ void st_real(uint32_t a, double v)
+  {
+    asm volatile("st.shared.f64 [%0], %1;" ::"r"(a), "d"(v) : "memory");
+  }
+  static __device__ __forceinline__ Val ld_val(uint32_t a)
+  {
+    Val v;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(a));
+    return v;
+  }
+  static __device__ __forceinline__ double as_real(Val v) { return __longlong_as_double(v); }
+  static __device__ __forceinline__ uint32_t low32(Val v) { return static_cast<uint32_t>(v); }
+  static __device__ __forceinline__ double exp_(double x) { return exp(x); }
+  static __device__ __forceinline__ double exp2_(double x) { return exp2(x); }
+  static __device__ __forceinline__ double log1p_(double x) { return log1p(x); }
+};
+
+// ---------------------------------------------------------------------------------------------
+// one test: does the row go to the right child?
+//   numerical: x < threshold goes left; categorical: a listed category goes right;
+//   a missing value (NaN) follows the node's default direction.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool CAT, bool NANS>
+__device__ __forceinline__ bool goes_right(typename Traits<T>::Val v, uint32_t meta, T x,
+                                           const ForestView& f)
+{
+  bool left = x < Traits<T>::as_real(v);
+  if (CAT) {
+    if (meta & META_CATEGORICAL) {
+      // category = truncated value; negative and huge values match nothing
+      const bool in_range = (x >= T(0)) && (x < T(16777216));
+      const uint32_t c    = in_range ? static_cast<uint32_t>(x) : 0u;
+      bool matched;
+      if (f.cat_inline) {
+        const uint32_t bits = Traits<T>::low32(v);
+        matched             = in_range && (c < 32u) && (((bits >> (c & 31u)) & 1u) != 0u);
+      } else {
+        const uint32_t off     = Traits<T>::low32(v);
+        const uint32_t n_words = __ldg(f.cat_pool + off);
+        const uint32_t w       = c >> 5;
+        matched                = false;
+        if (in_range && w < n_words) {
+          matched = ((__ldg(f.cat_pool + off + 1 + w) >> (c & 31u)) & 1u) != 0u;
+        }
+      }
+      left = !matched;
+    }
+  }
+  if (CAT || NANS) {
+    if (x != x) left = (meta & META_DEFAULT_LEFT) != 0u;
+  }
+  return !left;
+}
+
+// ---------------------------------------------------------------------------------------------
+// shared pieces of both kernels: row-tile staging, accumulation of a leaf, epilogue
+// ---------------------------------------------------------------------------------------------
+
+// Stage rows [row0, row0+R) feature-major.  A warp reads 32 consecutive features of one row
+// (one 128-byte line for fp32) and scatters them to 32 different banks.  Rows past the end of the
+// batch are filled with zeros.  Returns true when this thread saw a NaN.
+template <typename T>
+__device__ __forceinline__ bool stage_rows(const PredictParams& p, uint32_t tile, int R,
+                                           int64_t row0, int warp, int lane, int n_warps)
+{
+  const int F             = p.f.n_features;
+  const uint32_t stride_b = (R + 1) * Traits<T>::ES;
+  const T* X              = static_cast<const T*>(p.X);
+  bool saw_nan            = false;
+  for (int rr = warp; rr < R; rr += n_warps) {
+    const int64_t row = row0 + rr;
+    const bool live   = row < p.n_rows;
+    const T* src      = X + row * p.row_stride;
+    for (int c = lane; c < F; c += 32) {
+      const T v = live ? __ldg(src + c) : T(0);
+      saw_nan |= (v != v);
+      Traits<T>::st_real(tile + c * stride_b + rr * Traits<T>::ES, v);
+    }
+  }
+  return saw_nan;
+}
+
+template <typename T>
+__device__ __forceinline__ T postprocess_one(T s, int postproc, T alpha, T ratio_c)
+{
+  switch (postproc) {
+    case B2FIL_POST_SIGMOID:
+    case B2FIL_POST_MULTICLASS_OVA: return T(1) / (T(1) + Traits<T>::exp_(-alpha * s));
+    case B2FIL_POST_EXPONENTIAL: return Traits<T>::exp_(s);
+    case B2FIL_POST_LOG1PEXP: return Traits<T>::log1p_(Traits<T>::exp_(s));
+    case B2FIL_POST_SIGNED_SQUARE: return (s < T(0) ? T(-1) : T(1)) * s * s;
+    case B2FIL_POST_HINGE: return s > T(0) ? T(1) : T(0);
+    case B2FIL_POST_EXP_STD_RATIO: return Traits<T>::exp2_(-s / ratio_c);
+    default: return s;
+  }
+}
+
+// Epilogue of a row tile, one thread per row: fixed-order sum over the G tree groups, average and
+// base score, postprocessor, then the output the caller asked for.  `acc` is laid out
+// [group][output][row]; results overwrite group 0.
+template <typename T>
+__device__ __forceinline__ void finish_row(const PredictParams& p, T* acc, int R, int G, int j,
+                                           int64_t row)
+{
+  const ForestView& f = p.f;
+  const int NC        = f.n_outputs;
+  const T* scale      = static_cast<const T*>(f.out_scale);
+  const T* bias       = static_cast<const T*>(f.out_bias);
+  const T alpha       = static_cast<T>(f.sigmoid_alpha);
+  const T ratio_c     = static_cast<T>(f.ratio_c);
+  T mx                = T(0);
+  for (int c = 0; c < NC; ++c) {
+    T s = acc[c * R + j];
+    for (int g = 1; g < G; ++g) s += acc[(g * NC + c) * R + j];
+    s = s * __ldg(scale + c) + __ldg(bias + c);
+    if (f.postproc != B2FIL_POST_SOFTMAX) s = postprocess_one(s, f.postproc, alpha, ratio_c);
+    acc[c * R + j] = s;
+    mx             = (c == 0 || s > mx) ? s : mx;
+  }
+  if (f.postproc == B2FIL_POST_SOFTMAX) {
+    T z = T(0);
+    for (int c = 0; c < NC; ++c) {
+      const T e      = Traits<T>::exp_(acc[c * R + j] - mx);
+      acc[c * R + j] = e;
+      z += e;
+    }
+    for (int c = 0; c < NC; ++c) acc[c * R + j] = acc[c * R + j] / z;
+  }
+  if (row >= p.n_rows) return;
+  if (p.kind == B2FIL_INFER_DEFAULT) {
+    T* out = static_cast<T*>(p.out) + row * NC;
+    for (int c = 0; c < NC; ++c) out[c] = acc[c * R + j];
+  } else if (p.kind == B2FIL_INFER_PROBA2) {
+    T* out       = static_cast<T*>(p.out) + row * 2;
+    const T prob = acc[j];
+    out[0]       = T(1) - prob;
+    out[1]       = prob;
+  } else {  // B2FIL_INFER_CLASS
+    int best = 0;
+    if (NC == 1) {
+      best = acc[j] > static_cast<T>(p.threshold) ? 1 : 0;
+    } else {
+      T bv = acc[j];
+      for (int c = 1; c < NC; ++c) {
+        const T s = acc[c * R + j];
+        if (s > bv) {  // first maximum wins
+          bv   = s;
+          best = c;
+        }
+      }
+    }
+    static_cast<int32_t*>(p.out)[row] = best;
+  }
+}
+
+// Kernel modes.
+constexpr int MODE_SCALAR  = 0;  // scalar leaves, reduced outputs
+constexpr int MODE_VECTOR  = 1;  // vector leaves, reduced outputs
+constexpr int MODE_PERTREE = 2;  // raw per-tree outputs
+constexpr int MODE_LEAFID  = 3;  // id of the leaf reached
+
+// Per-thread running state of the reduced modes.
+template <typename T>
+struct Running {
+  T sum;
+  int cls;
+};
+
+// Consume one leaf.  `payload` is the leaf's scalar (as bits) or the index of its vector;
+// `leaf_id_index` is the index of the leaf in `leaf_ids`.
+template <typename T, int MODE>
+__device__ __forceinline__ void take_leaf(const PredictParams& p, int tree,
+                                          typename Traits<T>::Val payload, uint32_t leaf_id_index,
+                                          T* acc_group, int R, int r, int64_t row, Running<T>& run)
+{
+  const ForestView& f = p.f;
+  const int NC        = f.n_outputs;
+  if (MODE == MODE_SCALAR) {
+    if (NC > 1) {
+      const int cls = __ldg(f.tree_class + tree);  // same for the whole warp
+      if (cls != run.cls) {
+        acc_group[run.cls * R + r] += run.sum;
+        run.sum = T(0);
+        run.cls = cls;
+      }
+    }
+    run.sum += Traits<T>::as_real(payload);
+  } else if (MODE == MODE_VECTOR) {
+    const T* lv = static_cast<const T*>(f.leaf_vectors) +
+                  static_cast<size_t>(Traits<T>::low32(payload)) * NC;
+    for (int c = 0; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
+  } else if (MODE == MODE_PERTREE) {
+    if (row < p.n_rows) {
+      const int orig = __ldg(f.tree_orig + tree);
+      if (f.leaf_vector_len > 1) {
+        const T* lv = static_cast<const T*>(f.leaf_vectors) +
+                      static_cast<size_t>(Traits<T>::low32(payload)) * NC;
+        T* out = static_cast<T*>(p.out) + (row * f.n_trees + orig) * NC;
+        for (int c = 0; c < NC; ++c) out[c] = __ldg(lv + c);
+      } else {
+        static_cast<T*>(p.out)[row * f.n_trees + orig] = Traits<T>::as_real(payload);
+      }
+    }
+  } else {
+    if (row < p.n_rows) {
+      const int orig = __ldg(f.tree_orig + tree);
+      static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = __ldg(f.leaf_ids + leaf_id_index);
+    }
+  }
+}
+
+__host__ __device__ inline size_t align16(size_t x) { return (x + 15) / 16 * 16; }
+
+// ---------------------------------------------------------------------------------------------
+// DENSE kernel
+// ---------------------------------------------------------------------------------------------
+// Shared memory: [mbarriers 128 B][row tile][accumulators][flags 16 B][S tree stages].
+template <typename T, bool CAT, int MODE, int NT>
+struct DenseWalker {
+  using TR = Traits<T>;
+
+  // Walk the warp's rows through all trees of the CTA's current tile.
+  template <bool NANS>
+  static __device__ __forceinline__ bool walk(const PredictParams& p, int G, int S, int g, int r,
+                                              int64_t row, int lane, uint32_t bars,
+                                              uint32_t stages, uint32_t stage_bytes,
+                                              uint32_t row_addr, uint32_t stride_b, T* acc_group,
+                                              int R, uint32_t& it, Running<T>& run)
+  {
+    const ForestView& f    = p.f;
+    const int D            = f.dense_depth;
+    const uint32_t tstride = static_cast<uint32_t>(f.tree_stride);
+    const uint32_t width_b = (1u << D) * TR::NB;  // bytes of the node array of one tree
+    const int per_batch    = G * NT;
+    const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
+    bool ok                = true;
+    for (int b = 0; b < n_batches; ++b, ++it) {
+      const uint32_t s = it % S;
+      if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
+      if (ok) {
+        const int first = b * per_batch + g * NT;
+        const int n_act = min(NT, f.n_trees - first);
+        if (n_act > 0) {
+          uint32_t base[NT], a[NT];
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            // slots past the end of the forest repeat the last live tree; results are dropped
+            const int slot = g * NT + min(k, n_act - 1);
+            base[k]        = stages + s * stage_bytes + slot * tstride;
+            a[k]           = base[k] + TR::NB;  // heap index 1
+          }
+          for (int lvl = 0; lvl < D; ++lvl) {
+#pragma unroll
+            for (int k = 0; k < NT; ++k) {
+              typename TR::Val v;
+              uint32_t meta;
+              TR::ld_node(a[k], v, meta);
+              // flag bits 30/31 of meta leave the 32-bit product: stride_b is a multiple of 4
+              const T x        = TR::ld_real(meta * stride_b + row_addr);
+              const bool right = goes_right<T, CAT, NANS>(v, meta, x, f);
+              // address of heap node 2i+right from the address of node i
+              a[k] = 2u * a[k] - base[k] + (right ? TR::NB : 0u);
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            if (k < n_act) {
+              const uint32_t slot = (a[k] - base[k]) / TR::NB - (1u << D);
+              const typename TR::Val payload = TR::ld_val(base[k] + width_b + slot * TR::ES);
+              take_leaf<T, MODE>(p, first + k, payload,
+                                 (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
+                                 row, run);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
+    }
+    return ok;
+  }
+};
+
+template <typename T, bool CAT, int MODE, int NT>
+__global__ void __launch_bounds__(544, 1)
+dense_kernel(const PredictParams p, const int R, const int G, const int S)
+{
+  using TR = Traits<T>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const ForestView& f = p.f;
+  const int F         = f.n_features;
+  const int NC        = f.n_outputs;
+  const int rw        = R >> 5;
+  const int n_cw      = rw * G;        // consumer warps
+  const int n_ct      = n_cw * 32;     // consumer threads
+  const int warp      = threadIdx.x >> 5;
+  const int lane      = threadIdx.x & 31;
+
+  const uint32_t stride_b   = (R + 1) * TR::ES;
+  const size_t tile_bytes   = align16(static_cast<size_t>(F) * stride_b);
+  const size_t acc_bytes    = (MODE <= MODE_VECTOR) ? align16(static_cast<size_t>(G) * NC * R * TR::ES) : 0;
+  unsigned char* tile_ptr   = smem + kBarBytes;
+  T* acc                    = reinterpret_cast<T*>(tile_ptr + tile_bytes);
+  volatile int* flags       = reinterpret_cast<volatile int*>(tile_ptr + tile_bytes + acc_bytes);
+  unsigned char* stage_ptr  = tile_ptr + tile_bytes + acc_bytes + 16;
+  const uint32_t bars       = smem_addr(smem);
+  const uint32_t tile       = smem_addr(tile_ptr);
+  const uint32_t stages     = smem_addr(stage_ptr);
+  const uint32_t tstride    = static_cast<uint32_t>(f.tree_stride);
+  const int per_batch       = G * NT;
+  const uint32_t stage_bytes = per_batch * tstride;
+  const int n_batches       = (f.n_trees + per_batch - 1) / per_batch;
+  const int64_t n_tiles     = (p.n_rows + R - 1) / R;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bars + 8u * s, 1);                    // full: the producer's expect_tx arrival
+      mbar_init(bars + 8u * (kMaxStages + s), n_cw);  // empty: one arrival per consumer warp
+    }
+    flags[0] = 0;
+    flags[1] = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == n_cw) {
+    // ---- producer: one thread streams tree batches into the stage ring ----------------------
+    if (lane == 0) {
+      const unsigned char* src = static_cast<const unsigned char*>(f.nodes);
+      uint32_t it              = 0;
+      for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        for (int b = 0; b < n_batches; ++b, ++it) {
+          const uint32_t s   = it % S;
+          const uint32_t use = it / S;
+          if (use > 0 && !mbar_wait(bars + 8u * (kMaxStages + s), (use - 1) & 1u)) {
+            atomicExch(p.status, 1);
+            return;
+          }
+          const int first      = b * per_batch;
+          const int count      = min(per_batch, f.n_trees - first);
+          const uint32_t bytes = count * tstride;
+          mbar_expect_tx(bars + 8u * s, bytes);
+          bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
+                        bytes, bars + 8u * s);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ------------------------------------------------------------------------------
+  const int g           = warp / rw;
+  const int r           = (warp % rw) * 32 + lane;
+  T* acc_group          = acc + static_cast<size_t>(g) * NC * R;
+  const uint32_t row_addr = tile + r * TR::ES;
+  uint32_t it           = 0;
+  bool ok               = true;
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t row0 = t * R;
+    const bool saw_nan = stage_rows<T>(p, tile, R, row0, warp, lane, n_cw);
+    if (MODE <= MODE_VECTOR) {
+      for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
+    }
+    if (__any_sync(0xffffffffu, saw_nan) && lane == 0) flags[0] = 1;
+    consumer_sync(n_ct);
+    const bool nans = flags[0] != 0;
+    Running<T> run{T(0), 0};
+    if (ok) {
+      if (CAT || nans) {
+        ok = DenseWalker<T, CAT, MODE, NT>::template walk<true>(
+          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
+          R, it, run);
+      } else {
+        ok = DenseWalker<T, CAT, MODE, NT>::template walk<false>(
+          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
+          R, it, run);
+      }
+      if (!ok) atomicExch(p.status, 2);
+    }
+    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    consumer_sync(n_ct);
+    if (MODE <= MODE_VECTOR) {
+      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+    }
+    if (threadIdx.x == 0) flags[0] = 0;
+    consumer_sync(n_ct);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SPARSE kernel
+// ---------------------------------------------------------------------------------------------
+template <int FMT>
+struct SparseFmt;
+template <>
+struct SparseFmt<FMT_SPARSE_8> {
+  using T = float;
+  struct Node {
+    uint32_t value, meta, offset;
+  };
+  static __device__ __forceinline__ Node load(const void* nodes, uint32_t i, int feat_bits)
+  {
+    const uint2 raw = __ldg(static_cast<const uint2*>(nodes) + i);
+    Node n;
+    n.value  = raw.x;
+    n.meta   = raw.y;
+    n.offset = (raw.y & META_LOW29) >> feat_bits;
+    return n;
+  }
+  static __device__ __forceinline__ uint32_t feature(const Node& n, int feat_bits)
+  {
+    return n.meta & ((1u << feat_bits) - 1u);
+  }
+};
+template <>
+struct SparseFmt<FMT_SPARSE_16F> {
+  using T = float;
+  struct Node {
+    uint32_t value, meta, offset;
+  };
+  static __device__ __forceinline__ Node load(const void* nodes, uint32_t i, int)
+  {
+    const uint4 raw = __ldg(static_cast<const uint4*>(nodes) + i);
+    return Node{raw.x, raw.y, raw.z};
+  }
+  static __device__ __forceinline__ uint32_t feature(const Node& n, int)
+  {
+    return n.meta & META_LOW29;
+  }
+};
+template <>
+struct SparseFmt<FMT_SPARSE_16D> {
+  using T = double;
+  struct Node {
+    uint64_t value;
+    uint32_t meta, offset;
+  };
+  static __device__ __forceinline__ Node load(const void* nodes, uint32_t i, int)
+  {
+    const uint4 raw = __ldg(static_cast<const uint4*>(nodes) + i);
+    return Node{static_cast<uint64_t>(raw.x) | (static_cast<uint64_t>(raw.y) << 32), raw.z, raw.w};
+  }
+  static __device__ __forceinline__ uint32_t feature(const Node& n, int)
+  {
+    return n.meta & META_LOW29;
+  }
+};
+
+// Shared memory: [row tile (when rows_in_smem)][accumulators].
+template <int FMT, int MODE, int NT>
+__global__ void __launch_bounds__(1024, 1)
+sparse_kernel(const PredictParams p, const int R, const int G, const int rows_in_smem)
+{
+  using SF = SparseFmt<FMT>;
+  using T  = typename SF::T;
+  using TR = Traits<T>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const ForestView& f = p.f;
+  const int F         = f.n_features;
+  const int NC        = f.n_outputs;
+  const int rw        = R >> 5;
+  const int n_warps   = rw * G;
+  const int warp      = threadIdx.x >> 5;
+  const int lane      = threadIdx.x & 31;
+  const int g         = warp / rw;
+  const int r         = (warp % rw) * 32 + lane;
+  const bool dfs      = f.layout == B2FIL_LAYOUT_DEPTH_FIRST;
+  const int fb        = f.feat_bits;
+
+  const uint32_t stride_b = (R + 1) * TR::ES;
+  const size_t tile_bytes = rows_in_smem ? align16(static_cast<size_t>(F) * stride_b) : 0;
+  T* acc                  = reinterpret_cast<T*>(smem + tile_bytes);
+  T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
+  const uint32_t tile     = smem_addr(smem);
+  const uint32_t row_addr = tile + r * TR::ES;
+  const int64_t n_tiles   = (p.n_rows + R - 1) / R;
+  const int per_batch     = G * NT;
+  const T* X              = static_cast<const T*>(p.X);
+
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t row0 = t * R;
+    const int64_t row  = row0 + r;
+    if (rows_in_smem) stage_rows<T>(p, tile, R, row0, warp, lane, n_warps);
+    if (MODE <= MODE_VECTOR) {
+      for (int i = threadIdx.x; i < G * NC * R; i += n_warps * 32) acc[i] = T(0);
+    }
+    __syncthreads();
+    // rows past the end of the batch read row 0 of the tile's global memory when not staged
+    const T* xrow = X + (row < p.n_rows ? row : row0) * p.row_stride;
+    Running<T> run{T(0), 0};
+    for (int first = g * NT; first < f.n_trees; first += per_batch) {
+      const int n_act = min(NT, f.n_trees - first);
+      uint32_t idx[NT];
+      typename SF::Node node[NT];
+      bool done[NT];
+#pragma unroll
+      for (int k = 0; k < NT; ++k) {
+        idx[k]  = __ldg(f.roots + first + min(k, n_act - 1));
+        done[k] = false;
+      }
+      // max_depth + 1 nodes lie on the longest path: the loop cannot run away on a bad forest
+      for (int step = 0; step <= f.max_depth; ++step) {
+        bool all_done = true;
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          if (!done[k]) {
+            node[k] = SF::load(f.nodes, idx[k], fb);
+            if (node[k].meta & META_LEAF) {
+              done[k] = true;
+            } else {
+              const uint32_t feat = SF::feature(node[k], fb);
+              const T x = rows_in_smem ? TR::ld_real(feat * stride_b + row_addr) : __ldg(xrow + feat);
+              typename TR::Val v  = node[k].value;
+              const bool right    = f.has_categorical
+                                      ? goes_right<T, true, true>(v, node[k].meta, x, f)
+                                      : goes_right<T, false, true>(v, node[k].meta, x, f);
+              // depth-first: left child follows its parent, `offset` reaches the right child;
+              // otherwise the children are adjacent and `offset` reaches the left one
+              idx[k] += dfs ? (right ? node[k].offset : 1u) : (node[k].offset + (right ? 1u : 0u));
+              all_done = false;
+            }
+          }
+        }
+        if (all_done) break;
+      }
+#pragma unroll
+      for (int k = 0; k < NT; ++k) {
+        if (k < n_act && done[k]) {
+          take_leaf<T, MODE>(p, first + k, node[k].value, idx[k], acc_group, R, r, row, run);
+        }
+      }
+    }
+    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    __syncthreads();
+    if (MODE <= MODE_VECTOR) {
+      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side: launch shapes and dispatch
+// ---------------------------------------------------------------------------------------------
+size_t dense_tree_stride(int depth, int precision)
+{
+  const size_t nb = precision == B2FIL_F32 ? 8 : 16;
+  const size_t lb = precision == B2FIL_F32 ? 4 : 8;
+  return align16((size_t(1) << depth) * (nb + lb));
+}
+
+size_t dense_smem(int depth, int precision, int F, int NC, bool reduce, int R, int G, int NT, int S)
+{
+  const size_t es = precision == B2FIL_F32 ? 4 : 8;
+  size_t b        = kBarBytes;
+  b += align16(static_cast<size_t>(F) * (R + 1) * es);
+  if (reduce) b += align16(static_cast<size_t>(G) * NC * R * es);
+  b += 16;
+  b += static_cast<size_t>(S) * G * NT * dense_tree_stride(depth, precision);
+  return b;
+}
+
+template <typename K>
+int set_smem(K kernel, size_t bytes, std::string& err)
+{
+  const cudaError_t e = cudaFuncSetAttribute(
+    kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) {
+    err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
+  return B2FIL_OK;
+}
+
+template <typename T, bool CAT, int MODE>
+int launch_dense_mode(const PredictParams& p, const DenseCfg& c, int grid, cudaStream_t stream,
+                      std::string& err)
+{
+  int rc;
+  if (c.trees_in_flight == 2) {
+    auto k = dense_kernel<T, CAT, MODE, 2>;
+    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+  } else {
+    auto k = dense_kernel<T, CAT, MODE, 1>;
+    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+  }
+  return B2FIL_OK;
+}
+
+template <typename T, bool CAT>
+int launch_dense_cat(const PredictParams& p, int mode, const DenseCfg& c, int grid,
+                     cudaStream_t stream, std::string& err)
+{
+  switch (mode) {
+    case MODE_SCALAR: return launch_dense_mode<T, CAT, MODE_SCALAR>(p, c, grid, stream, err);
+    case MODE_VECTOR: return launch_dense_mode<T, CAT, MODE_VECTOR>(p, c, grid, stream, err);
+    case MODE_PERTREE: return launch_dense_mode<T, CAT, MODE_PERTREE>(p, c, grid, stream, err);
+    default: return launch_dense_mode<T, CAT, MODE_LEAFID>(p, c, grid, stream, err);
+  }
+}
+
+template <int FMT>
+int launch_sparse_fmt(const PredictParams& p, int mode, int R, int G, int rows_in_smem, int grid,
+                      size_t smem, cudaStream_t stream, std::string& err)
+{
+  constexpr int NT = 4;
+  const int threads = (R / 32) * G * 32;
+  int rc;
+#define B2FIL_SPARSE_CASE(M)                                                       \
+  {                                                                                \
+    auto k = sparse_kernel<FMT, M, NT>;                                            \
+    if ((rc = set_smem(k, smem, err)) != B2FIL_OK) return rc;                      \
+    k<<<grid, threads, smem, stream>>>(p, R, G, rows_in_smem);                     \
+  }
+  switch (mode) {
+    case MODE_SCALAR: B2FIL_SPARSE_CASE(MODE_SCALAR) break;
+    case MODE_VECTOR: B2FIL_SPARSE_CASE(MODE_VECTOR) break;
+    case MODE_PERTREE: B2FIL_SPARSE_CASE(MODE_PERTREE) break;
+    default: B2FIL_SPARSE_CASE(MODE_LEAFID) break;
+  }
+#undef B2FIL_SPARSE_CASE
+  return B2FIL_OK;
+}
+
+int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
+{
+  if (chunk_size > 0) return std::min(128, std::max(32, 32 * chunk_size));
+  // keep every SM busy before growing the tile
+  if (n_rows >= static_cast<int64_t>(128) * sm_count) return 128;
+  if (n_rows >= static_cast<int64_t>(64) * sm_count) return 64;
+  return 32;
+}
+
+}  // namespace
+
+bool dense_config(int depth, int precision, int n_features, int n_outputs, bool reduce_kind,
+                  int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
+{
+  const int want = pick_rows_per_tile(n_rows, chunk_size, sm_count);
+  for (int R = want; R >= 32; R /= 2) {
+    const int rw = R / 32;
+    for (int G = 16 / rw; G >= 1; G /= 2) {
+      for (int NT = 2; NT >= 1; --NT) {
+        for (int S = 3; S >= 2; --S) {
+          const size_t b =
+            dense_smem(depth, precision, n_features, n_outputs, reduce_kind, R, G, NT, S);
+          if (b <= kMaxSmemBytes) {
+            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32};
+            return true;
+          }
+        }
+      }
+    }
+  }
+  return false;
+}
+
+bool dense_ok(int depth, int precision, int n_features, int n_outputs)
+{
+  // usable when at least 64 rows and two tree groups fit next to a two-stage ring
+  return dense_smem(depth, precision, n_features, n_outputs, true, 64, 2, 1, 2) <= kMaxSmemBytes;
+}
+
+int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
+                   std::string& err, int64_t* launches)
+{
+  const ForestView& f = p.f;
+  if (p.n_rows == 0) return B2FIL_OK;
+  int mode;
+  switch (p.kind) {
+    case B2FIL_INFER_DEFAULT:
+    case B2FIL_INFER_CLASS: mode = f.leaf_vector_len > 1 ? MODE_VECTOR : MODE_SCALAR; break;
+    case B2FIL_INFER_PROBA2:
+      if (f.n_outputs != 1) {
+        err = "B2FIL_INFER_PROBA2 needs a forest with one output";
+        return B2FIL_ERR_INVALID_ARG;
+      }
+      mode = MODE_SCALAR;
+      break;
+    case B2FIL_INFER_PER_TREE: mode = MODE_PERTREE; break;
+    case B2FIL_INFER_LEAF_ID: mode = MODE_LEAFID; break;
+    default: err = "unknown infer_kind"; return B2FIL_ERR_INVALID_ARG;
+  }
+  const bool reduce = mode <= MODE_VECTOR;
+  int rc            = B2FIL_OK;
+  if (f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) {
+    const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
+    DenseCfg c;
+    if (!dense_config(f.dense_depth, precision, f.n_features, f.n_outputs, reduce, p.n_rows,
+                      chunk_size, sm_count, c)) {
+      err = "no dense launch shape fits shared memory";
+      return B2FIL_ERR_UNSUPPORTED;
+    }
+    const int64_t n_tiles = (p.n_rows + c.rows_per_tile - 1) / c.rows_per_tile;
+    const int grid        = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
+    if (precision == B2FIL_F32) {
+      rc = f.has_categorical ? launch_dense_cat<float, true>(p, mode, c, grid, stream, err)
+                             : launch_dense_cat<float, false>(p, mode, c, grid, stream, err);
+    } else {
+      rc = f.has_categorical ? launch_dense_cat<double, true>(p, mode, c, grid, stream, err)
+                             : launch_dense_cat<double, false>(p, mode, c, grid, stream, err);
+    }
+  } else {
+    const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
+    int R           = pick_rows_per_tile(p.n_rows, chunk_size, sm_count);
+    int G           = std::min(8, 32 / (R / 32));
+    G               = std::max(1, std::min(G, (f.n_trees + 3) / 4));
+    // two CTAs per SM when the tile is small enough, else one; rows stay in global memory when
+    // even a 32-row tile does not fit
+    size_t acc_b = 0, tile_b = 0;
+    int rows_in_smem = 1;
+    for (;;) {
+      acc_b  = reduce ? align16(static_cast<size_t>(G) * f.n_outputs * R * es) : 0;
+      tile_b = align16(static_cast<size_t>(f.n_features) * (R + 1) * es);
+      if (acc_b + tile_b <= kMaxSmemBytes) break;
+      if (R > 32) {
+        R /= 2;
+        continue;
+      }
+      rows_in_smem = 0;
+      tile_b       = 0;
+      if (acc_b > kMaxSmemBytes) {
+        if (G > 1) {
+          G /= 2;
+          continue;
+        }
+        err = "too many outputs for the accumulators to fit shared memory";
+        return B2FIL_ERR_UNSUPPORTED;
+      }
+      break;
+    }
+    const size_t smem     = acc_b + tile_b;
+    const int64_t n_tiles = (p.n_rows + R - 1) / R;
+    const int grid        = static_cast<int>(std::min<int64_t>(n_tiles, int64_t(sm_count) * 8));
+    switch (f.format) {
+      case FMT_SPARSE_8:
+        rc = launch_sparse_fmt<FMT_SPARSE_8>(p, mode, R, G, rows_in_smem, grid, smem, stream, err);
+        break;
+      case FMT_SPARSE_16F:
+        rc = launch_sparse_fmt<FMT_SPARSE_16F>(p, mode, R, G, rows_in_smem, grid, smem, stream, err);
+        break;
+      default:
+        rc = launch_sparse_fmt<FMT_SPARSE_16D>(p, mode, R, G, rows_in_smem, grid, smem, stream, err);
+        break;
+    }
+  }
+  if (rc != B2FIL_OK) return rc;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    err = std::string("kernel launch: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
+  if (launches) ++*launches;
+  return B2FIL_OK;
+}
+
+}  // namespace b2fil

@@ -1,0 +1,49 @@
+// Launch interface of the prediction kernels (host side).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "forest.hpp"
+
+namespace b2fil {
+
+// Everything a prediction launch needs; passed to kernels by value.
+struct PredictParams {
+  ForestView f;
+  const void* X;       // device, row-major, forest precision
+  int64_t n_rows;
+  int64_t row_stride;  // elements between rows
+  void* out;           // device
+  int32_t kind;        // B2FIL_INFER_*
+  double threshold;    // binary decision threshold of B2FIL_INFER_CLASS
+  int32_t* status;     // device word: set non-zero when a bounded wait inside a kernel ran out
+};
+
+// Shape of one dense launch.
+struct DenseCfg {
+  int rows_per_tile;   // R: rows staged in shared memory per CTA, multiple of 32
+  int tree_groups;     // G: warp groups that split the trees of a batch
+  int trees_in_flight; // NT: trees one warp walks at once
+  int stages;          // S: depth of the tree pipeline
+  size_t smem_bytes;
+  int threads;
+};
+
+// Largest dynamic shared memory a CTA may use on sm_100 (227 KiB).
+constexpr size_t kMaxSmemBytes = 227 * 1024;
+
+// Pick a dense launch shape for `n_rows` rows; false when no shape fits shared memory.
+bool dense_config(int depth, int precision, int n_features, int n_outputs, bool reduce_kind,
+                  int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg);
+
+// True when the dense kernels can run forests of this shape at all.
+bool dense_ok(int depth, int precision, int n_features, int n_outputs);
+
+// Enqueue a prediction on `stream`.  Returns B2FIL_OK or an error code with `err` set.
+// `launches` (optional) is incremented by the number of kernels enqueued.
+int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
+                   std::string& err, int64_t* launches);
+
+}  // namespace b2fil

@@ -1,0 +1,610 @@
+// Forest import / packing: validates a host description, normalises every test to one operator
+// and lays the nodes out for the device (see forest.hpp for the two storages).
+//
+// This is the work the reference delegates to nvforest.load_from_treelite_model /
+// nvforest::import_from_treelite_handle (python/cuml/cuml/ensemble/randomforest_common.pyx:402-409,
+// cpp/tests/sg/rf_test.cu:257-263): walk every tree on the host, choose precision and node order,
+// pad trees to `align_bytes`, produce one contiguous node array.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <numeric>
+
+#include "forest.hpp"
+
+namespace b2fil {
+namespace {
+
+struct Test {
+  bool is_cat;
+  bool default_left;
+  int32_t left, right;  // relative indices after normalisation
+  double thr;           // numerical threshold in the target precision, operator is `<`
+};
+
+template <typename T>
+T bump_up(T t, bool& always_left)
+{
+  always_left = false;
+  if (std::isnan(t)) return t;
+  if (t == std::numeric_limits<T>::infinity()) {
+    always_left = true;
+    return t;
+  }
+  return std::nextafter(t, std::numeric_limits<T>::infinity());
+}
+
+// Rewrite the test of node g as "x < thr -> left" (numerical) or "listed -> right" (categorical).
+//  x <= t  <=>  x < next(t);  x > t -> L  <=>  x <= t -> R;  x >= t -> L  <=>  x < t -> R.
+// A swap of the children flips the missing-value direction so that it names the same child.
+Test normalise(const b2fil_forest_desc& d, int64_t g, int precision)
+{
+  Test t{};
+  t.left         = d.left[g];
+  t.right        = d.right[g];
+  t.default_left = d.default_left[g] != 0;
+  t.is_cat       = d.node_kind[g] == B2FIL_NODE_CATEGORICAL;
+  auto swap_children = [&]() {
+    std::swap(t.left, t.right);
+    t.default_left = !t.default_left;
+  };
+  if (t.is_cat) {
+    const bool right_on_match = d.cat_right ? d.cat_right[g] != 0 : true;
+    if (!right_on_match) swap_children();
+    t.thr = 0;
+    return t;
+  }
+  int op        = d.op ? d.op[g] : d.op_all;
+  double thr    = d.threshold[g];
+  const bool sp = precision == B2FIL_F32;
+  if (sp) thr = static_cast<double>(static_cast<float>(thr));
+  if (op == B2FIL_OP_GT) {
+    swap_children();
+    op = B2FIL_OP_LE;
+  } else if (op == B2FIL_OP_GE) {
+    swap_children();
+    op = B2FIL_OP_LT;
+  }
+  if (op == B2FIL_OP_LE) {
+    bool always_left = false;
+    if (sp) {
+      thr = static_cast<double>(bump_up(static_cast<float>(thr), always_left));
+    } else {
+      thr = bump_up(thr, always_left);
+    }
+    if (always_left) {  // x <= +inf holds for every number: send numbers right after a swap
+      swap_children();
+      thr = -std::numeric_limits<double>::infinity();
+    }
+  }
+  t.thr = thr;
+  return t;
+}
+
+template <typename T>
+void put(std::vector<uint8_t>& buf, size_t byte_off, const T& v)
+{
+  std::memcpy(buf.data() + byte_off, &v, sizeof(T));
+}
+
+uint32_t f32_bits(double v)
+{
+  float f = static_cast<float>(v);
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  return u;
+}
+uint64_t f64_bits(double v)
+{
+  uint64_t u;
+  std::memcpy(&u, &v, 8);
+  return u;
+}
+
+int bits_for(uint32_t max_value)
+{
+  int b = 1;
+  while (b < 32 && (max_value >> b) != 0) ++b;
+  return b;
+}
+
+struct Packer {
+  const b2fil_forest_desc& d;
+  const b2fil_create_opts& o;
+  PackedForest& out;
+  std::string& err;
+  int precision;
+  bool vec;
+  int64_t n_vectors = 0;
+  bool cat_inline   = true;
+  bool has_cat      = false;
+  std::vector<int32_t> depth_of;   // per node of the description (global index), -1 = unreachable
+  std::vector<int32_t> tree_depth;
+
+  Packer(const b2fil_forest_desc& d_, const b2fil_create_opts& o_, PackedForest& out_,
+         std::string& err_)
+    : d(d_), o(o_), out(out_), err(err_), precision(o_.precision), vec(d_.leaf_vector_len > 1)
+  {
+  }
+
+  int fail(int code, const std::string& msg)
+  {
+    err = msg;
+    return code;
+  }
+
+  int validate()
+  {
+    if (d.n_trees <= 0) return fail(B2FIL_ERR_INVALID_ARG, "n_trees must be positive");
+    if (d.n_features <= 0) return fail(B2FIL_ERR_INVALID_ARG, "n_features must be positive");
+    if (d.n_features > (1 << 29))
+      return fail(B2FIL_ERR_UNSUPPORTED, "more than 2^29 features");
+    if (d.n_outputs <= 0) return fail(B2FIL_ERR_INVALID_ARG, "n_outputs must be positive");
+    if (d.leaf_vector_len != 1 && d.leaf_vector_len != d.n_outputs)
+      return fail(B2FIL_ERR_INVALID_ARG, "leaf_vector_len must be 1 or n_outputs");
+    if (!d.tree_offsets || !d.node_kind || !d.feature || !d.threshold || !d.left || !d.right ||
+        !d.default_left || !d.leaf_value)
+      return fail(B2FIL_ERR_INVALID_ARG, "a required array of the forest description is NULL");
+    if (d.postproc < 0 || d.postproc > B2FIL_POST_EXP_STD_RATIO)
+      return fail(B2FIL_ERR_INVALID_ARG, "unknown postprocessor");
+    if (d.postproc == B2FIL_POST_EXP_STD_RATIO && d.ratio_c == 0.0)
+      return fail(B2FIL_ERR_INVALID_ARG, "ratio_c must not be zero");
+    if (d.tree_offsets[0] != 0) return fail(B2FIL_ERR_BAD_FOREST, "tree_offsets[0] must be 0");
+    for (int t = 0; t < d.n_trees; ++t) {
+      const int64_t n = d.tree_offsets[t + 1] - d.tree_offsets[t];
+      if (n <= 0) return fail(B2FIL_ERR_BAD_FOREST, "tree " + std::to_string(t) + " is empty");
+      if (n > (int64_t(1) << 31) - 1)
+        return fail(B2FIL_ERR_TOO_LARGE, "tree " + std::to_string(t) + " has too many nodes");
+      if (d.class_id && !vec && (d.class_id[t] < 0 || d.class_id[t] >= d.n_outputs))
+        return fail(B2FIL_ERR_BAD_FOREST, "class_id of tree " + std::to_string(t) + " out of range");
+    }
+    return B2FIL_OK;
+  }
+
+  // Depth of every reachable node; rejects out-of-range children, bad features, shared nodes.
+  int measure()
+  {
+    const int64_t total = d.tree_offsets[d.n_trees];
+    depth_of.assign(static_cast<size_t>(total), -1);
+    tree_depth.assign(d.n_trees, 0);
+    std::vector<int32_t> stack;
+    for (int t = 0; t < d.n_trees; ++t) {
+      const int64_t base = d.tree_offsets[t];
+      const int64_t n    = d.tree_offsets[t + 1] - base;
+      stack.clear();
+      stack.push_back(0);
+      depth_of[base] = 0;
+      int md         = 0;
+      while (!stack.empty()) {
+        const int32_t r = stack.back();
+        stack.pop_back();
+        const int64_t g = base + r;
+        const int dep   = depth_of[g];
+        md              = std::max(md, dep);
+        const uint8_t k = d.node_kind[g];
+        if (k == B2FIL_NODE_LEAF) {
+          if (vec) ++n_vectors;
+          continue;
+        }
+        if (k != B2FIL_NODE_NUMERICAL && k != B2FIL_NODE_CATEGORICAL)
+          return fail(B2FIL_ERR_BAD_FOREST, "unknown node kind in tree " + std::to_string(t));
+        if (d.feature[g] < 0 || d.feature[g] >= d.n_features)
+          return fail(B2FIL_ERR_BAD_FOREST, "feature index out of range in tree " +
+                                              std::to_string(t) + " node " + std::to_string(r));
+        if (k == B2FIL_NODE_NUMERICAL) {
+          const int op = d.op ? d.op[g] : d.op_all;
+          if (op < B2FIL_OP_LT || op > B2FIL_OP_GE)
+            return fail(B2FIL_ERR_BAD_FOREST, "unknown comparison operator");
+        } else {
+          if (!d.cat_ptr || !d.cat_values)
+            return fail(B2FIL_ERR_BAD_FOREST, "categorical node without category arrays");
+          if (d.cat_ptr[g + 1] < d.cat_ptr[g])
+            return fail(B2FIL_ERR_BAD_FOREST, "cat_ptr is not monotone");
+          has_cat = true;
+          for (int64_t c = d.cat_ptr[g]; c < d.cat_ptr[g + 1]; ++c) {
+            if (d.cat_values[c] >= 32) cat_inline = false;
+            if (d.cat_values[c] >= (1u << 24))
+              return fail(B2FIL_ERR_UNSUPPORTED, "category value of 2^24 or more");
+          }
+        }
+        const int32_t ch[2] = {d.left[g], d.right[g]};
+        for (int32_t c : ch) {
+          if (c < 0 || c >= n)
+            return fail(B2FIL_ERR_BAD_FOREST, "child index out of range in tree " +
+                                                std::to_string(t) + " node " + std::to_string(r));
+          if (depth_of[base + c] != -1)
+            return fail(B2FIL_ERR_BAD_FOREST, "node reached twice (cycle or shared child) in tree " +
+                                                std::to_string(t));
+          depth_of[base + c] = dep + 1;
+          stack.push_back(c);
+        }
+      }
+      tree_depth[t] = md;
+    }
+    return B2FIL_OK;
+  }
+
+  // Category list of node g as a record in the pool: [n_words, words...]; returns its offset.
+  uint32_t pool_record(int64_t g)
+  {
+    uint32_t mx = 0;
+    for (int64_t c = d.cat_ptr[g]; c < d.cat_ptr[g + 1]; ++c) mx = std::max(mx, d.cat_values[c]);
+    const uint32_t n_words = (d.cat_ptr[g + 1] > d.cat_ptr[g]) ? mx / 32 + 1 : 0;
+    const uint32_t off     = static_cast<uint32_t>(out.cat_pool.size());
+    out.cat_pool.push_back(n_words);
+    out.cat_pool.resize(out.cat_pool.size() + n_words, 0u);
+    for (int64_t c = d.cat_ptr[g]; c < d.cat_ptr[g + 1]; ++c) {
+      const uint32_t v = d.cat_values[c];
+      out.cat_pool[off + 1 + v / 32] |= 1u << (v % 32);
+    }
+    return off;
+  }
+  uint32_t inline_bitset(int64_t g)
+  {
+    uint32_t b = 0;
+    for (int64_t c = d.cat_ptr[g]; c < d.cat_ptr[g + 1]; ++c) b |= 1u << d.cat_values[c];
+    return b;
+  }
+  // value word(s) of a test node
+  uint64_t test_value(int64_t g, const Test& t)
+  {
+    if (t.is_cat) return cat_inline ? inline_bitset(g) : pool_record(g);
+    return precision == B2FIL_F32 ? f32_bits(t.thr) : f64_bits(t.thr);
+  }
+  // payload of a leaf: scalar in the forest precision or the index of its vector
+  uint64_t leaf_payload(int64_t g, int64_t& vec_counter)
+  {
+    if (!vec) {
+      return precision == B2FIL_F32 ? f32_bits(d.leaf_value[g]) : f64_bits(d.leaf_value[g]);
+    }
+    const int64_t idx = vec_counter++;
+    const int k       = d.n_outputs;
+    for (int c = 0; c < k; ++c) {
+      const double v = d.leaf_value[g * k + c];
+      if (precision == B2FIL_F32) {
+        put(out.leaf_vectors, (idx * k + c) * 4, static_cast<float>(v));
+      } else {
+        put(out.leaf_vectors, (idx * k + c) * 8, v);
+      }
+    }
+    return static_cast<uint64_t>(idx);
+  }
+
+  void common_tables()
+  {
+    const int k   = d.n_outputs;
+    const int nt  = d.n_trees;
+    out.tree_orig.resize(nt);
+    std::iota(out.tree_orig.begin(), out.tree_orig.end(), 0);
+    std::vector<int32_t> cls(nt, 0);
+    if (!vec) {
+      for (int t = 0; t < nt; ++t) cls[t] = d.class_id ? d.class_id[t] : t % k;
+      // trees of one output run back to back so that a thread keeps one running sum
+      std::stable_sort(out.tree_orig.begin(), out.tree_orig.end(),
+                       [&](int a, int b) { return cls[a] < cls[b]; });
+    }
+    out.tree_class.resize(nt);
+    for (int t = 0; t < nt; ++t) out.tree_class[t] = vec ? 0 : cls[out.tree_orig[t]];
+    std::vector<double> count(k, 0.0);
+    for (int t = 0; t < nt; ++t) {
+      if (vec) {
+        for (int c = 0; c < k; ++c) count[c] += 1;
+      } else {
+        count[cls[t]] += 1;
+      }
+    }
+    const size_t es = precision == B2FIL_F32 ? 4 : 8;
+    out.out_scale.resize(k * es);
+    out.out_bias.resize(k * es);
+    for (int c = 0; c < k; ++c) {
+      const double s = (d.average_tree_output && count[c] > 0) ? 1.0 / count[c] : 1.0;
+      const double b = d.base_scores ? d.base_scores[c] : 0.0;
+      if (precision == B2FIL_F32) {
+        put(out.out_scale, c * 4, static_cast<float>(s));
+        put(out.out_bias, c * 4, static_cast<float>(b));
+      } else {
+        put(out.out_scale, c * 8, s);
+        put(out.out_bias, c * 8, b);
+      }
+    }
+    if (vec) out.leaf_vectors.resize(static_cast<size_t>(n_vectors) * k * es);
+  }
+
+  // ---- dense ----------------------------------------------------------------------------------
+  int pack_dense(int D)
+  {
+    const bool sp        = precision == B2FIL_F32;
+    const size_t nb      = sp ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
+    const size_t lb      = sp ? 4 : 8;
+    const int64_t width  = int64_t(1) << D;
+    int64_t stride       = width * static_cast<int64_t>(nb + lb);
+    stride               = (stride + 15) / 16 * 16;
+    const int nt         = d.n_trees;
+    out.nodes.assign(static_cast<size_t>(stride) * nt, 0);
+    out.leaf_ids.assign(static_cast<size_t>(width) * nt, 0);
+    int64_t vec_counter = 0;
+    struct Item {
+      int32_t rel;
+      uint32_t heap;
+      int32_t level;
+      bool leaf_fill;
+      uint64_t payload;
+    };
+    std::vector<Item> stack;
+    for (int p = 0; p < nt; ++p) {
+      const int t        = out.tree_orig[p];
+      const int64_t base = d.tree_offsets[t];
+      const size_t tb    = static_cast<size_t>(stride) * p;
+      stack.clear();
+      stack.push_back({0, 1u, 0, false, 0});
+      while (!stack.empty()) {
+        Item it = stack.back();
+        stack.pop_back();
+        const int64_t g = base + it.rel;
+        if (!it.leaf_fill && d.node_kind[g] != B2FIL_NODE_LEAF) {
+          const Test ts     = normalise(d, g, precision);
+          const uint64_t v  = test_value(g, ts);
+          uint32_t meta     = static_cast<uint32_t>(d.feature[g]);
+          if (ts.default_left) meta |= META_DEFAULT_LEFT;
+          if (ts.is_cat) meta |= META_CATEGORICAL;
+          if (sp) {
+            put(out.nodes, tb + it.heap * nb, DenseNodeF{static_cast<uint32_t>(v), meta});
+          } else {
+            put(out.nodes, tb + it.heap * nb, DenseNodeD{v, meta, 0});
+          }
+          stack.push_back({ts.right, it.heap * 2 + 1, it.level + 1, false, 0});
+          stack.push_back({ts.left, it.heap * 2, it.level + 1, false, 0});
+          continue;
+        }
+        // a leaf above the last level is repeated below itself: both children of a filler test
+        // lead to the same payload, so its outcome does not matter
+        if (!it.leaf_fill) {
+          it.payload   = leaf_payload(g, vec_counter);
+          it.leaf_fill = true;
+        }
+        if (it.level == D) {
+          const uint64_t slot = it.heap - static_cast<uint32_t>(width);
+          if (sp) {
+            put(out.nodes, tb + width * nb + slot * 4, static_cast<uint32_t>(it.payload));
+          } else {
+            put(out.nodes, tb + width * nb + slot * 8, it.payload);
+          }
+          out.leaf_ids[static_cast<size_t>(width) * p + slot] = static_cast<uint32_t>(it.rel);
+        } else {
+          if (sp) {
+            put(out.nodes, tb + it.heap * nb, DenseNodeF{f32_bits(0.0), 0u});
+          } else {
+            put(out.nodes, tb + it.heap * nb, DenseNodeD{f64_bits(0.0), 0u, 0u});
+          }
+          stack.push_back({it.rel, it.heap * 2 + 1, it.level + 1, true, it.payload});
+          stack.push_back({it.rel, it.heap * 2, it.level + 1, true, it.payload});
+        }
+      }
+    }
+    out.view.format       = sp ? FMT_DENSE_F : FMT_DENSE_D;
+    out.view.dense_depth  = D;
+    out.view.tree_stride  = stride;
+    out.storage           = B2FIL_STORAGE_DENSE;
+    out.node_bytes        = static_cast<int32_t>(nb);
+    out.n_nodes_packed    = width * 2 * nt;
+    return B2FIL_OK;
+  }
+
+  // ---- sparse ---------------------------------------------------------------------------------
+  int pack_sparse()
+  {
+    const bool sp = precision == B2FIL_F32;
+    const int nt  = d.n_trees;
+    const int layout = o.layout;
+    // position of every reachable node in the packed array
+    const int64_t total = d.tree_offsets[nt];
+    std::vector<uint32_t> pos(static_cast<size_t>(total), 0xFFFFFFFFu);
+    out.roots.assign(nt, 0);
+    size_t node_bytes_guess = sp ? 8 : 16;
+    int64_t cursor          = 0;
+    uint32_t max_offset     = 0;
+    std::vector<int32_t> order;  // scratch
+    auto align_cursor = [&](size_t nbytes) {
+      if (o.align_bytes > 0) {
+        const int64_t per = std::max<int64_t>(1, o.align_bytes / static_cast<int64_t>(nbytes));
+        cursor            = (cursor + per - 1) / per * per;
+      }
+    };
+    if (layout == B2FIL_LAYOUT_LAYERED) {
+      // level by level over the whole forest; siblings adjacent
+      int maxd = 0;
+      for (int p = 0; p < nt; ++p) maxd = std::max(maxd, tree_depth[out.tree_orig[p]]);
+      std::vector<std::vector<int32_t>> frontier(nt), next(nt);
+      for (int p = 0; p < nt; ++p) frontier[p].push_back(0);
+      for (int lvl = 0; lvl <= maxd; ++lvl) {
+        for (int p = 0; p < nt; ++p) {
+          const int64_t base = d.tree_offsets[out.tree_orig[p]];
+          next[p].clear();
+          for (int32_t r : frontier[p]) {
+            pos[base + r] = static_cast<uint32_t>(cursor++);
+            if (d.node_kind[base + r] != B2FIL_NODE_LEAF) {
+              const Test ts = normalise(d, base + r, precision);
+              next[p].push_back(ts.left);
+              next[p].push_back(ts.right);
+            }
+          }
+        }
+        frontier.swap(next);
+      }
+    } else {
+      for (int p = 0; p < nt; ++p) {
+        const int64_t base = d.tree_offsets[out.tree_orig[p]];
+        align_cursor(node_bytes_guess);
+        order.clear();
+        if (layout == B2FIL_LAYOUT_DEPTH_FIRST) {
+          std::vector<int32_t>& stack = order;  // positions are assigned on pop
+          stack.push_back(0);
+          while (!stack.empty()) {
+            const int32_t r = stack.back();
+            stack.pop_back();
+            pos[base + r] = static_cast<uint32_t>(cursor++);
+            if (d.node_kind[base + r] != B2FIL_NODE_LEAF) {
+              const Test ts = normalise(d, base + r, precision);
+              stack.push_back(ts.right);
+              stack.push_back(ts.left);  // left is popped next: it sits right after its parent
+            }
+          }
+        } else {
+          size_t head = 0;
+          order.push_back(0);
+          while (head < order.size()) {
+            const int32_t r = order[head++];
+            pos[base + r]   = static_cast<uint32_t>(cursor++);
+            if (d.node_kind[base + r] != B2FIL_NODE_LEAF) {
+              const Test ts = normalise(d, base + r, precision);
+              order.push_back(ts.left);
+              order.push_back(ts.right);
+            }
+          }
+        }
+      }
+    }
+    if (cursor >= (int64_t(1) << 32))
+      return fail(B2FIL_ERR_TOO_LARGE, "packed forest has 2^32 nodes or more");
+    const int64_t n_packed = cursor;
+    // offsets decide the node format
+    for (int p = 0; p < nt; ++p) {
+      const int t        = out.tree_orig[p];
+      const int64_t base = d.tree_offsets[t];
+      const int64_t n    = d.tree_offsets[t + 1] - base;
+      out.roots[p]       = pos[base];
+      for (int64_t r = 0; r < n; ++r) {
+        const int64_t g = base + r;
+        if (depth_of[g] < 0 || d.node_kind[g] == B2FIL_NODE_LEAF) continue;
+        const Test ts      = normalise(d, g, precision);
+        const uint32_t far = layout == B2FIL_LAYOUT_DEPTH_FIRST ? pos[base + ts.right]
+                                                                : pos[base + ts.left];
+        max_offset = std::max(max_offset, far - pos[g]);
+      }
+    }
+    const int feat_bits = bits_for(static_cast<uint32_t>(d.n_features - 1));
+    int format          = FMT_SPARSE_16D;
+    if (sp) {
+      const int off_bits = 29 - feat_bits;
+      format = (off_bits >= 1 && max_offset < (1u << off_bits)) ? FMT_SPARSE_8 : FMT_SPARSE_16F;
+    }
+    const size_t nb = format == FMT_SPARSE_8 ? 8 : 16;
+    // tree starts were aligned assuming the narrowest node of the precision; with wider nodes a
+    // tree start stays on a multiple of align_bytes because its byte offset only doubles
+    out.nodes.assign(static_cast<size_t>(n_packed) * nb, 0);
+    out.leaf_ids.assign(static_cast<size_t>(n_packed), 0);
+    int64_t vec_counter = 0;
+    for (int p = 0; p < nt; ++p) {
+      const int t        = out.tree_orig[p];
+      const int64_t base = d.tree_offsets[t];
+      const int64_t n    = d.tree_offsets[t + 1] - base;
+      for (int64_t r = 0; r < n; ++r) {
+        const int64_t g = base + r;
+        if (depth_of[g] < 0) continue;
+        const uint32_t at = pos[g];
+        uint64_t value;
+        uint32_t meta = 0, offset = 0;
+        if (d.node_kind[g] == B2FIL_NODE_LEAF) {
+          value = leaf_payload(g, vec_counter);
+          meta  = META_LEAF;
+          out.leaf_ids[at] = static_cast<uint32_t>(r);
+        } else {
+          const Test ts = normalise(d, g, precision);
+          value         = test_value(g, ts);
+          meta          = static_cast<uint32_t>(d.feature[g]);
+          if (ts.default_left) meta |= META_DEFAULT_LEFT;
+          if (ts.is_cat) meta |= META_CATEGORICAL;
+          const uint32_t far = layout == B2FIL_LAYOUT_DEPTH_FIRST ? pos[base + ts.right]
+                                                                  : pos[base + ts.left];
+          offset = far - at;
+        }
+        if (format == FMT_SPARSE_8) {
+          meta |= offset << feat_bits;
+          put(out.nodes, at * nb, SparseNode8{static_cast<uint32_t>(value), meta});
+        } else if (format == FMT_SPARSE_16F) {
+          put(out.nodes, at * nb, SparseNode16F{static_cast<uint32_t>(value), meta, offset, 0});
+        } else {
+          put(out.nodes, at * nb, SparseNode16D{value, meta, offset});
+        }
+      }
+    }
+    out.view.format      = format;
+    out.view.feat_bits   = feat_bits;
+    out.view.dense_depth = -1;
+    out.view.tree_stride = 0;
+    out.storage          = B2FIL_STORAGE_SPARSE;
+    out.node_bytes       = static_cast<int32_t>(nb);
+    out.n_nodes_packed   = n_packed;
+    return B2FIL_OK;
+  }
+};
+
+}  // namespace
+
+int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
+                bool (*dense_ok)(int, int, int, int), PackedForest& out, std::string& err)
+{
+  if (opts.precision != B2FIL_F32 && opts.precision != B2FIL_F64) {
+    err = "precision must be B2FIL_F32 or B2FIL_F64";
+    return B2FIL_ERR_INVALID_ARG;
+  }
+  if (opts.layout < B2FIL_LAYOUT_DEPTH_FIRST || opts.layout > B2FIL_LAYOUT_LAYERED) {
+    err = "unknown layout";
+    return B2FIL_ERR_INVALID_ARG;
+  }
+  if (opts.storage < B2FIL_STORAGE_AUTO || opts.storage > B2FIL_STORAGE_SPARSE) {
+    err = "unknown storage";
+    return B2FIL_ERR_INVALID_ARG;
+  }
+  if (opts.align_bytes < 0 || (opts.align_bytes & (opts.align_bytes - 1)) != 0) {
+    err = "align_bytes must be 0 or a power of two";
+    return B2FIL_ERR_INVALID_ARG;
+  }
+  Packer pk(desc, opts, out, err);
+  int rc = pk.validate();
+  if (rc != B2FIL_OK) return rc;
+  rc = pk.measure();
+  if (rc != B2FIL_OK) return rc;
+  out.precision   = opts.precision;
+  out.align_bytes = opts.align_bytes;
+  out.n_nodes_in  = desc.tree_offsets[desc.n_trees];
+  pk.common_tables();
+  const int max_depth = *std::max_element(pk.tree_depth.begin(), pk.tree_depth.end());
+
+  ForestView& v     = out.view;
+  v.n_trees         = desc.n_trees;
+  v.n_features      = desc.n_features;
+  v.n_outputs       = desc.n_outputs;
+  v.leaf_vector_len = desc.leaf_vector_len;
+  v.postproc        = desc.postproc;
+  v.has_categorical = pk.has_cat ? 1 : 0;
+  v.cat_inline      = pk.cat_inline ? 1 : 0;
+  v.max_depth       = max_depth;
+  v.layout          = opts.layout;
+  v.sigmoid_alpha   = desc.sigmoid_alpha;
+  v.ratio_c         = desc.ratio_c;
+
+  bool dense = false;
+  if (opts.storage != B2FIL_STORAGE_SPARSE) {
+    const bool fits = max_depth <= 16 && dense_ok(max_depth, opts.precision, desc.n_features, desc.n_outputs);
+    if (opts.storage == B2FIL_STORAGE_DENSE) {
+      if (!fits) {
+        err = "dense storage cannot hold this forest: depth " + std::to_string(max_depth) +
+              " with " + std::to_string(desc.n_features) +
+              " features exceeds the shared memory of one SM";
+        return B2FIL_ERR_UNSUPPORTED;
+      }
+      dense = true;
+    } else if (fits) {
+      // padded size against the real size: padding a ragged forest is worth it only while the
+      // padded forest stays small (it streams through shared memory once per row tile)
+      const double padded = static_cast<double>(desc.n_trees) * std::ldexp(2.0, max_depth);
+      dense = padded <= 4.0 * static_cast<double>(out.n_nodes_in) + 4096.0 ||
+              padded * 6.0 <= 8.0 * 1024 * 1024;
+    }
+  }
+  return dense ? pk.pack_dense(max_depth) : pk.pack_sparse();
+}
+
+}  // namespace b2fil

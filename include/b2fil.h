@@ -1,0 +1,225 @@
+/*
+ * b2fil.h - C ABI of the B200 forest-inference library (libb2fil.so).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns 0 on success or a
+ * negative B2FIL_ERR_* code, never throws and never aborts.  The text of the last error of the
+ * calling thread is read with b2fil_last_error(), the same convention the Treelite C API uses
+ * (reference: python/cuml/cuml/internals/treelite.pxd:7-12, treelite.pyx:5-12).
+ *
+ * The functions replace what cuML binds from the un-vendored nvForest library for batched
+ * tree-ensemble prediction.  Reference call sites (paths inside NVIDIA/cuml 26.10):
+ *   - import:   nvforest.load_from_treelite_model(tl_model, device, layout, default_chunk_size,
+ *               align_bytes, handle)          python/cuml/cuml/ensemble/randomforest_common.pyx:402-409
+ *               nvforest::import_from_treelite_handle(model, tree_layout, align_bytes, use_double,
+ *               device_type, device_id, stream)                     cpp/tests/sg/rf_test.cu:257-263
+ *   - predict:  forest_model.predict(handle, out, in, n_rows, out_mem, in_mem, infer_kind,
+ *               chunk_size)                                         cpp/tests/sg/rf_test.cu:268-275
+ *               .predict / .predict_proba / .predict_per_tree
+ *               python/cuml/cuml/ensemble/randomforestclassifier.py:337,388
+ *               python/cuml/cuml/ensemble/randomforest_common.pyx:652
+ *
+ * Device work is stream ordered: calls that take a `cuda_stream` enqueue on it and return without
+ * synchronising; the caller owns input and output buffers and synchronises the stream.  A forest
+ * is immutable after creation, so several host threads may predict with it on different streams.
+ */
+#ifndef B2FIL_H_
+#define B2FIL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes ------------------------------------------------------------------------- */
+#define B2FIL_OK 0
+#define B2FIL_ERR_INVALID_ARG (-1)   /* NULL pointer, negative size, unknown enum value          */
+#define B2FIL_ERR_BAD_FOREST (-2)    /* malformed tree: child out of range, cycle, bad feature   */
+#define B2FIL_ERR_UNSUPPORTED (-3)   /* legal model that this build cannot represent             */
+#define B2FIL_ERR_CUDA (-4)          /* a CUDA runtime call failed; message holds its text       */
+#define B2FIL_ERR_NO_MEMORY (-5)     /* host or device allocation failed                         */
+#define B2FIL_ERR_TOO_LARGE (-6)     /* size beyond a documented fixed limit                     */
+#define B2FIL_ERR_TIMEOUT (-7)       /* a bounded host wait ran out                              */
+
+/* ---- enums --------------------------------------------------------------------------------- */
+/* precision of thresholds, leaves, inputs and outputs on the device (nvForest: use_double) */
+#define B2FIL_F32 0
+#define B2FIL_F64 1
+
+/* node kinds in a forest description */
+#define B2FIL_NODE_LEAF 0
+#define B2FIL_NODE_NUMERICAL 1
+#define B2FIL_NODE_CATEGORICAL 2
+
+/* comparison operator of a numerical test; the test being TRUE sends the row to the LEFT child
+ * (reference: cpp/src/decisiontree/decisiontree.cuh:204-205,379-383 uses <=;
+ *  cpp/src/isolation_forest/isolation_forest.cu:75-79 uses <) */
+#define B2FIL_OP_LT 0
+#define B2FIL_OP_LE 1
+#define B2FIL_OP_GT 2
+#define B2FIL_OP_GE 3
+
+/* node order on the device (nvforest::tree_layout; randomforest_common.pyx:381-383) */
+#define B2FIL_LAYOUT_DEPTH_FIRST 0
+#define B2FIL_LAYOUT_BREADTH_FIRST 1
+#define B2FIL_LAYOUT_LAYERED 2
+
+/* storage of the packed forest: SPARSE keeps child offsets in every node and honours `layout`;
+ * DENSE pads every tree to a complete binary tree of the forest's maximum depth and indexes
+ * children implicitly (heap order), which removes the offset arithmetic from the hot loop and
+ * lets whole trees be staged in shared memory.  AUTO picks DENSE when the padded forest is small
+ * enough. */
+#define B2FIL_STORAGE_AUTO 0
+#define B2FIL_STORAGE_DENSE 1
+#define B2FIL_STORAGE_SPARSE 2
+
+/* what predict writes (nvforest::infer_kind) */
+#define B2FIL_INFER_DEFAULT 0   /* (n_rows, n_outputs) scores after averaging/base/postprocess  */
+#define B2FIL_INFER_PER_TREE 1  /* (n_rows, n_trees[, n_classes]) raw per-tree outputs          */
+#define B2FIL_INFER_LEAF_ID 2   /* (n_rows, n_trees) uint32 id of the leaf reached              */
+#define B2FIL_INFER_CLASS 3     /* (n_rows,) int32 class index (argmax or threshold)            */
+#define B2FIL_INFER_PROBA2 4    /* (n_rows, 2): [1-p, p] for one-output binary classifiers      */
+
+/* postprocessing applied to the summed tree outputs (Treelite postprocessor names) */
+#define B2FIL_POST_IDENTITY 0
+#define B2FIL_POST_SIGMOID 1
+#define B2FIL_POST_EXPONENTIAL 2
+#define B2FIL_POST_LOG1PEXP 3
+#define B2FIL_POST_SIGNED_SQUARE 4
+#define B2FIL_POST_HINGE 5
+#define B2FIL_POST_SOFTMAX 6
+#define B2FIL_POST_MULTICLASS_OVA 7
+#define B2FIL_POST_EXP_STD_RATIO 8
+
+/* ---- forest description (host, structure of arrays) ----------------------------------------- */
+/*
+ * Mirrors the Treelite fields cuML reads and writes (cpp/src/decisiontree/decisiontree.cuh:165-221,
+ * cpp/src/randomforest/randomforest.cu:262-279,308-333, cpp/src/explainer/tree_shap.cu:268-300).
+ * Nodes of tree t occupy [tree_offsets[t], tree_offsets[t+1]) of every per-node array; node 0 of
+ * that range is the root; `left` / `right` are indices relative to the tree's first node; the
+ * relative index of a node is also the id that B2FIL_INFER_LEAF_ID reports for it.
+ */
+typedef struct b2fil_forest_desc {
+  int32_t n_trees;
+  int32_t n_features;
+  int32_t n_outputs;       /* classes for classifiers, 1 for regression and one-score binary     */
+  int32_t leaf_vector_len; /* 1: scalar leaves; n_outputs: every leaf holds a vector             */
+  const int64_t* tree_offsets; /* [n_trees + 1]                                                  */
+  const uint8_t* node_kind;    /* [n_nodes] B2FIL_NODE_*                                         */
+  const int32_t* feature;      /* [n_nodes] split feature (ignored for leaves)                   */
+  const double* threshold;     /* [n_nodes] numerical threshold (ignored otherwise)              */
+  const int32_t* left;         /* [n_nodes] relative index of the left child                     */
+  const int32_t* right;        /* [n_nodes] relative index of the right child                    */
+  const uint8_t* default_left; /* [n_nodes] 1: a missing (NaN) value goes left                   */
+  const uint8_t* op;           /* [n_nodes] B2FIL_OP_* or NULL = every numerical test uses op_all */
+  int32_t op_all;
+  const int64_t* cat_ptr;      /* [n_nodes + 1] CSR into cat_values, or NULL: no categorical node */
+  const uint32_t* cat_values;  /* categories listed by the node                                  */
+  const uint8_t* cat_right;    /* [n_nodes] 1: a listed category goes right, 0: goes left; NULL=1 */
+  const double* leaf_value;    /* [n_nodes * leaf_vector_len]                                    */
+  const int32_t* class_id;     /* [n_trees] output a scalar leaf adds to; NULL = t % n_outputs   */
+  int32_t average_tree_output; /* divide sums by the number of trees feeding each output         */
+  const double* base_scores;   /* [n_outputs] or NULL = zeros                                    */
+  int32_t postproc;            /* B2FIL_POST_*                                                   */
+  double sigmoid_alpha;        /* sigmoid(x) = 1 / (1 + exp(-alpha x))                           */
+  double ratio_c;              /* exp_std_ratio(x) = exp2(-x / c)                                */
+} b2fil_forest_desc;
+
+typedef struct b2fil_create_opts {
+  int32_t precision;   /* B2FIL_F32 / B2FIL_F64                                                  */
+  int32_t layout;      /* B2FIL_LAYOUT_*                                                          */
+  int32_t storage;     /* B2FIL_STORAGE_*                                                         */
+  int32_t align_bytes; /* 0 or a power of two: pad every tree of a sparse forest to this size    */
+  int32_t device_id;   /* CUDA device ordinal that will hold the forest                          */
+  int32_t default_chunk_size; /* 0 = choose; else the value predict uses when given chunk_size 0 */
+} b2fil_create_opts;
+
+typedef struct b2fil_info {
+  int32_t precision, layout, storage, device_id;
+  int32_t n_trees, n_features, n_outputs, leaf_vector_len;
+  int32_t max_depth;       /* edges on the longest root-to-leaf path                             */
+  int32_t dense_depth;     /* depth every tree is padded to (dense storage), else -1             */
+  int32_t node_bytes;      /* size of one packed node                                            */
+  int32_t has_categorical;
+  int64_t n_nodes_in;      /* nodes in the description                                           */
+  int64_t n_nodes_packed;  /* nodes stored on the device (with padding)                          */
+  int64_t device_bytes;    /* device memory held by the forest                                   */
+  int32_t default_chunk_size;
+  int32_t reserved;
+} b2fil_info;
+
+typedef struct b2fil_forest b2fil_forest; /* opaque */
+
+/* ---- entry points --------------------------------------------------------------------------- */
+
+/* Text of the last error raised on the calling thread ("" if none).
+ * Replaces TreeliteGetLastError (python/cuml/cuml/internals/treelite.pxd:12). */
+const char* b2fil_last_error(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int b2fil_version(void);
+
+/* Validate a description, pack it (layout / storage / precision) and upload it to opts->device_id.
+ * Synchronous.  Replaces nvforest.load_from_treelite_model / nvforest::import_from_treelite_handle
+ * (randomforest_common.pyx:402-409, cpp/tests/sg/rf_test.cu:257-263). */
+int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* opts,
+                        b2fil_forest** out);
+
+/* Copy a packed forest to another device of the same box (peer copy when the devices can reach
+ * each other, else through the host).  Model replication of the row-sharded multi-GPU path
+ * (python/cuml/cuml/dask/ensemble/base.py:153-175 broadcasts the model to every worker). */
+int b2fil_forest_clone_to_device(const b2fil_forest* src, int device_id, b2fil_forest** out);
+
+/* Release a forest and its device memory.
+ * (cpp/tests/sg/rf_test.cu:266 deletes the model handle explicitly.) */
+int b2fil_forest_free(b2fil_forest* f);
+
+/* Describe a packed forest.  `forest.get_dtype()` of the reference
+ * (python/cuml/cuml/ensemble/randomforestclassifier.py:333) is info->precision. */
+int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info);
+
+/* Read the forest's device status word (synchronises with the device).  Prediction kernels bound
+ * every internal wait; when a bound is hit they set the word, stop working and return.  Returns
+ * B2FIL_ERR_TIMEOUT when the word is set.  No counterpart in the reference. */
+int b2fil_forest_status(const b2fil_forest* f, int32_t* status);
+
+/* Number of prediction kernels this process has launched through the library so far. */
+int64_t b2fil_kernel_launches(void);
+
+/* Number of elements predict writes per row for `infer_kind` (0 and an error for a bad kind). */
+int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind);
+
+/* Batched prediction, device buffers.  X_dev: row-major (n_rows, n_features) of the forest's
+ * precision with `row_stride` elements between rows; out_dev: n_rows *
+ * b2fil_output_elems_per_row() elements (precision type; uint32 for LEAF_ID, int32 for CLASS).
+ * chunk_size 0 = the forest's default.  `threshold` is the binary decision threshold of
+ * B2FIL_INFER_CLASS for one-output classifiers.  Enqueues on cuda_stream (NULL = default stream)
+ * of the forest's device; allocates nothing.
+ * Replaces forest_model.predict(...) (cpp/tests/sg/rf_test.cu:268-275). */
+int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int64_t n_rows,
+                  int64_t row_stride, void* out_dev, int chunk_size, double threshold,
+                  void* cuda_stream);
+
+/* Batched prediction, host buffers: copies row blocks to the device, predicts and copies results
+ * back, with copies and kernels overlapped on two internal streams.  Pinned host memory gives
+ * full copy bandwidth; pageable memory works.  Synchronous: returns when out_host is complete.
+ * This is the call a host-array user of `.predict_proba(X)` reaches. */
+int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int64_t n_rows,
+                       int64_t row_stride, void* out_host, int chunk_size, double threshold);
+
+/* Row-sharded prediction over several devices of one box from a single process: forests[i] lives
+ * on device i of the set, rows are split into contiguous shards, shard i is predicted on its
+ * device, and results are gathered into out (a device buffer on forests[0]'s device, by peer
+ * copies; no collective library).  X_shards[i] is the device pointer of shard i's first row on
+ * device i; shard_rows[i] its row count.  Synchronous.
+ * (python/cuml/cuml/dask/ensemble/base.py:210-218, dask/common/base.py:276-316: model replicated,
+ *  row partitions predicted where they live, results concatenated by rows.) */
+int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer_kind,
+                          const void* const* X_shards, const int64_t* shard_rows,
+                          int64_t row_stride, void* out_dev0, int chunk_size, double threshold);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2FIL_H_ */

@@ -1,0 +1,146 @@
+// Test-only host walker over a PACKED forest (the arrays the kernels read), used by the CPU test
+// suite to check the packer without a GPU: it links cuml_b200/csrc/pack.cpp directly, packs a
+// description and follows the packed nodes with the same index arithmetic as the kernels
+// (heap addressing for dense storage, child offsets and bit fields for sparse storage).
+// It is not part of libb2fil.so.
+#include <cmath>
+#include <cstring>
+#include <string>
+
+#include "../../cuml_b200/csrc/forest.hpp"
+
+using namespace b2fil;
+
+namespace {
+bool always_dense(int depth, int, int, int) { return depth <= 16; }
+std::string g_err;
+
+template <typename T, typename V>
+bool goes_right(V value, uint32_t meta, T x, const PackedForest& pf)
+{
+  T thr;
+  std::memcpy(&thr, &value, sizeof(T));
+  bool left = x < thr;
+  if (meta & META_CATEGORICAL) {
+    const bool in_range = (x >= T(0)) && (x < T(16777216));
+    const uint32_t c    = in_range ? static_cast<uint32_t>(x) : 0u;
+    const uint32_t low  = static_cast<uint32_t>(value);
+    bool matched        = false;
+    if (pf.view.cat_inline) {
+      matched = in_range && c < 32u && ((low >> (c & 31u)) & 1u);
+    } else {
+      const uint32_t n_words = pf.cat_pool[low];
+      const uint32_t w       = c >> 5;
+      if (in_range && w < n_words) matched = (pf.cat_pool[low + 1 + w] >> (c & 31u)) & 1u;
+    }
+    left = !matched;
+  }
+  if (x != x) left = (meta & META_DEFAULT_LEFT) != 0;
+  return !left;
+}
+
+template <typename T>
+void walk(const PackedForest& pf, const T* X, int64_t n_rows, int64_t stride, uint32_t* ids,
+          double* payload)
+{
+  const ForestView& v = pf.view;
+  using V             = typename std::conditional<sizeof(T) == 4, uint32_t, uint64_t>::type;
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const T* row = X + r * stride;
+    for (int p = 0; p < v.n_trees; ++p) {
+      const int orig = pf.tree_orig[p];
+      uint32_t id;
+      V pay;
+      if (v.format == FMT_DENSE_F || v.format == FMT_DENSE_D) {
+        const size_t nb  = sizeof(T) == 4 ? 8 : 16;
+        const int D      = v.dense_depth;
+        const uint8_t* t = pf.nodes.data() + static_cast<size_t>(v.tree_stride) * p;
+        uint32_t i       = 1;
+        for (int l = 0; l < D; ++l) {
+          V value;
+          uint32_t meta;
+          std::memcpy(&value, t + i * nb, sizeof(V));
+          std::memcpy(&meta, t + i * nb + sizeof(V), 4);
+          const uint32_t feat = meta & 0x3FFFFFFFu;
+          i = 2 * i + (goes_right<T, V>(value, meta, row[feat], pf) ? 1 : 0);
+        }
+        const uint32_t slot = i - (1u << D);
+        std::memcpy(&pay, t + (size_t(1) << D) * nb + slot * sizeof(T), sizeof(V));
+        id = pf.leaf_ids[(static_cast<size_t>(p) << D) + slot];
+      } else {
+        uint32_t idx = pf.roots[p];
+        for (;;) {
+          V value;
+          uint32_t meta, offset, feat;
+          if (v.format == FMT_SPARSE_8) {
+            SparseNode8 n;
+            std::memcpy(&n, pf.nodes.data() + size_t(idx) * 8, 8);
+            value  = n.value;
+            meta   = n.meta;
+            offset = (n.meta & META_LOW29) >> v.feat_bits;
+            feat   = n.meta & ((1u << v.feat_bits) - 1u);
+          } else if (v.format == FMT_SPARSE_16F) {
+            SparseNode16F n;
+            std::memcpy(&n, pf.nodes.data() + size_t(idx) * 16, 16);
+            value  = n.value;
+            meta   = n.meta;
+            offset = n.offset;
+            feat   = n.meta & META_LOW29;
+          } else {
+            SparseNode16D n;
+            std::memcpy(&n, pf.nodes.data() + size_t(idx) * 16, 16);
+            value  = static_cast<V>(n.value);
+            meta   = n.meta;
+            offset = n.offset;
+            feat   = n.meta & META_LOW29;
+          }
+          if (meta & META_LEAF) {
+            pay = value;
+            id  = pf.leaf_ids[idx];
+            break;
+          }
+          const bool right = goes_right<T, V>(value, meta, row[feat], pf);
+          idx += (v.layout == B2FIL_LAYOUT_DEPTH_FIRST) ? (right ? offset : 1u)
+                                                         : (offset + (right ? 1u : 0u));
+        }
+      }
+      ids[r * v.n_trees + orig] = id;
+      if (v.leaf_vector_len > 1) {
+        payload[r * v.n_trees + orig] = static_cast<double>(static_cast<uint32_t>(pay));
+      } else {
+        T val;
+        std::memcpy(&val, &pay, sizeof(T));
+        payload[r * v.n_trees + orig] = static_cast<double>(val);
+      }
+    }
+  }
+}
+}  // namespace
+
+extern "C" {
+const char* pack_check_error() { return g_err.c_str(); }
+
+// Packs `desc` and walks n_rows rows.  ids: leaf id per (row, tree); payload: scalar leaf value
+// (or vector index) per (row, tree).  info[0..5] = format, storage, dense_depth, node_bytes,
+// n_nodes_packed, feat_bits.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
+int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, const void* X,
+               int64_t n_rows, int64_t stride, uint32_t* ids, double* payload, int64_t* info)
+{
+  PackedForest pf;
+  const int rc = pack_forest(*desc, *opts, always_dense, pf, g_err);
+  if (rc != B2FIL_OK) return rc;
+  info[0] = pf.view.format;
+  info[1] = pf.storage;
+  info[2] = pf.view.dense_depth;
+  info[3] = pf.node_bytes;
+  info[4] = pf.n_nodes_packed;
+  info[5] = pf.view.feat_bits;
+  if (n_rows > 0) {
+    if (opts->precision == B2FIL_F32)
+      walk<float>(pf, static_cast<const float*>(X), n_rows, stride, ids, payload);
+    else
+      walk<double>(pf, static_cast<const double*>(X), n_rows, stride, ids, payload);
+  }
+  return B2FIL_OK;
+}
+}

@@ -1,0 +1,158 @@
+"""The product packer (cuml_b200/csrc/pack.cpp) checked on the CPU: a test-only host walker follows
+the PACKED node arrays with the kernels' index arithmetic and must reach the leaves the oracle
+reaches, for every storage, node order, precision and operator normalisation."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from cuml_b200.fil._desc import INFER_LEAF_ID, INFER_PER_TREE, OP_GE, OP_GT, OP_LE, OP_LT
+from cuml_b200.fil.importers import synthetic_complete_forest
+from oracle import oracle
+from tests.helpers import load_golden, random_forest_desc, random_rows, run_pack_check
+
+LAYOUT_STORAGE = [("depth_first", "sparse"), ("breadth_first", "sparse"), ("layered", "sparse"),
+                  ("depth_first", "dense"), ("depth_first", "auto")]
+
+
+def _check(pack_check, desc, X, precision, layout, storage, align=0):
+    rc, ids, pay, info = run_pack_check(pack_check, desc, X, precision, layout, storage, align)
+    assert rc == 0, pack_check.pack_check_error()
+    want = oracle.predict(desc, X, INFER_LEAF_ID, precision)
+    assert np.array_equal(ids, want)
+    if desc.leaf_vector_len == 1:
+        pt = oracle.predict(desc, X, INFER_PER_TREE, precision)
+        assert np.array_equal(pay.astype(pt.dtype), pt)
+    return info
+
+
+@pytest.mark.parametrize("layout,storage", LAYOUT_STORAGE)
+@pytest.mark.parametrize("precision", ["single", "double"])
+def test_mixed_operators_ties_nan(pack_check, layout, storage, precision):
+    desc = random_forest_desc(1, n_trees=9, max_depth=6, mixed_ops=True, integer_thresholds=True)
+    X = random_rows(2, 400, desc.n_features, np.float64, nan_frac=0.15, integer=True)
+    _check(pack_check, desc, X, precision, layout, storage)
+
+
+@pytest.mark.parametrize("layout,storage", LAYOUT_STORAGE)
+@pytest.mark.parametrize("big", [False, True])
+def test_categorical(pack_check, layout, storage, big):
+    desc = random_forest_desc(3 + big, n_trees=8, max_depth=5, categorical=True,
+                              big_categories=big, mixed_ops=True)
+    X = random_rows(4, 500, desc.n_features, np.float32, nan_frac=0.1, categories=75 if big else 22)
+    _check(pack_check, desc, X, "single", layout, storage)
+    _check(pack_check, desc, X, "double", layout, storage)
+
+
+@pytest.mark.parametrize("layout,storage", LAYOUT_STORAGE)
+def test_vector_leaves(pack_check, layout, storage):
+    desc = random_forest_desc(5, n_trees=6, n_outputs=3, vector=True)
+    X = random_rows(6, 200, desc.n_features, np.float32)
+    _check(pack_check, desc, X, "single", layout, storage)
+
+
+@pytest.mark.parametrize("layout,storage", LAYOUT_STORAGE)
+def test_multiclass_tree_reordering_keeps_tree_index(pack_check, layout, storage):
+    # scalar-leaf multi-class forests are stored class by class; ids must still be reported
+    # under the tree's original index
+    desc = random_forest_desc(7, n_trees=11, n_outputs=4)
+    X = random_rows(8, 200, desc.n_features, np.float32)
+    _check(pack_check, desc, X, "single", layout, storage)
+
+
+@pytest.mark.parametrize("op", [OP_LT, OP_LE])
+def test_complete_forest_dense(pack_check, op):
+    desc = synthetic_complete_forest(20, 6, 16, seed=2, op=op, n_categorical=3, n_categories=32,
+                                     n_classes=3)
+    X = random_rows(9, 500, 16, np.float32, nan_frac=0.05, categories=32)
+    info = _check(pack_check, desc, X, "single", "depth_first", "auto")
+    assert info[1] == 1 and info[2] == 6  # dense storage, depth 6
+    assert info[4] == 20 * 2 * 64
+
+
+def test_golden_forests_all_layouts(pack_check):
+    for name, prec in (("rfc_depth8", "single"), ("rfr_depth20", "double"),
+                       ("rfc_missing", "single")):
+        desc, X, exp = load_golden(name)
+        X = X[:300]
+        for layout, storage in LAYOUT_STORAGE:
+            if storage == "dense" and name == "rfr_depth20":
+                continue  # depth 20 cannot be padded
+            rc, ids, _, info = run_pack_check(pack_check, desc, X, prec, layout, storage)
+            assert rc == 0, pack_check.pack_check_error()
+            assert np.array_equal(ids.astype(np.int64), exp["leaf_ids"][:300])
+        if name == "rfr_depth20":
+            rc, _, _, info = run_pack_check(pack_check, desc, X[:1], prec, "depth_first", "auto")
+            assert info[1] == 2  # AUTO falls back to sparse storage for deep ragged trees
+
+
+def test_align_bytes_and_wide_nodes(pack_check):
+    desc = random_forest_desc(11, n_trees=5, max_depth=7, p_leaf=0.1)
+    X = random_rows(12, 100, desc.n_features, np.float32)
+    info = _check(pack_check, desc, X, "single", "depth_first", "sparse", align=128)
+    assert info[0] == 2 and info[3] == 8  # compact 8-byte nodes
+    # many features leave too few offset bits for the compact node: the wide node is chosen
+    desc = random_forest_desc(13, n_trees=3, n_features=1 << 22, max_depth=9, p_leaf=0.05)
+    X = np.zeros((4, 1 << 22), np.float32)
+    X[:, ::7] = 1.5
+    info = _check(pack_check, desc, X, "single", "depth_first", "sparse")
+    assert info[0] == 3 and info[3] == 16
+
+
+def test_le_with_infinite_threshold(pack_check):
+    from cuml_b200.fil._desc import ForestDesc, NODE_LEAF, NODE_NUMERICAL
+
+    for op in (OP_LE, OP_GT, OP_LT, OP_GE):
+        for thr in (np.inf, -np.inf, np.float64(np.finfo(np.float32).max), 0.0, -0.0):
+            desc = ForestDesc(n_features=1, n_outputs=1, tree_offsets=[0, 3],
+                              node_kind=[NODE_NUMERICAL, NODE_LEAF, NODE_LEAF], feature=[0, 0, 0],
+                              threshold=[thr, 0, 0], left=[1, -1, -1], right=[2, -1, -1],
+                              default_left=[0, 0, 0], leaf_value=[0, 1.0, 2.0], op_all=op)
+            X = np.array([[np.inf], [-np.inf], [0.0], [-0.0], [np.nan], [3e38], [-3e38],
+                          [1e-45], [-1e-45]], np.float32)
+            for storage in ("sparse", "dense"):
+                _check(pack_check, desc, X, "single", "depth_first", storage)
+                _check(pack_check, desc, X, "double", "depth_first", storage)
+
+
+def _bad(desc_kwargs):
+    from cuml_b200.fil._desc import ForestDesc, NODE_LEAF, NODE_NUMERICAL
+
+    base = dict(n_features=2, n_outputs=1, tree_offsets=[0, 3],
+                node_kind=[NODE_NUMERICAL, NODE_LEAF, NODE_LEAF], feature=[0, 0, 0],
+                threshold=[0.5, 0, 0], left=[1, -1, -1], right=[2, -1, -1],
+                default_left=[0, 0, 0], leaf_value=[0, 1.0, 2.0])
+    base.update(desc_kwargs)
+    return ForestDesc(**base)
+
+
+@pytest.mark.parametrize("kwargs,code", [
+    (dict(left=[5, -1, -1]), -2),            # child out of range
+    (dict(left=[0, -1, -1]), -2),            # cycle: the root is its own child
+    (dict(right=[1, -1, -1]), -2),           # both children are the same node
+    (dict(feature=[2, 0, 0]), -2),           # feature >= n_features
+    (dict(feature=[-1, 0, 0]), -2),
+    (dict(tree_offsets=[0, 0, 3]), -2),      # empty tree
+    (dict(n_outputs=0), -1),
+    (dict(leaf_vector_len=3), -1),
+    (dict(node_kind=[7, 0, 0]), -2),
+    (dict(op_all=9), -2),
+])
+def test_malformed_forests_are_rejected(pack_check, kwargs, code):
+    desc = _bad(kwargs)
+    rc, _, _, _ = run_pack_check(pack_check, desc, np.zeros((1, 2), np.float32))
+    assert rc == code
+    assert pack_check.pack_check_error() != b""
+
+
+def test_bad_options_are_rejected(pack_check):
+    from cuml_b200.fil._desc import CCreateOpts
+
+    desc = _bad({})
+    cd = desc.to_c()
+    info = np.zeros(8, np.int64)
+    for opts in (CCreateOpts(5, 0, 0, 0, 0, 0), CCreateOpts(0, 9, 0, 0, 0, 0),
+                 CCreateOpts(0, 0, 7, 0, 0, 0), CCreateOpts(0, 0, 0, 48, 0, 0)):
+        rc = pack_check.pack_check(C.byref(cd), C.byref(opts), None, 0, 2, None, None,
+                                   info.ctypes.data)
+        assert rc == -1
