@@ -216,7 +216,7 @@ class ForestInference:
         lib = _lib.load()
         f = self.forest
         dt = f.get_dtype()
-        cs = int(chunk_size or 0)
+        cs = int(chunk_size or self.default_chunk_size or 0)
         if cs and (cs < 1 or cs & (cs - 1)):
             raise ValueError("chunk_size must be a positive power of two")
         torch = None
@@ -349,8 +349,6 @@ class ForestInference:
             if t < best_t:
                 best, best_t = cs, t
         self.default_chunk_size = best
-        self._forest.info.default_chunk_size = best
-        self._default_chunk_override = best
         return best
 
 

@@ -1,0 +1,318 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the golden fixtures.
+
+Bars: leaf ids and class labels bit-exact; scores within rtol 1e-5 (fp32) / 1e-12 (fp64) with a
+small absolute floor for values near zero (the reference's own boundary test uses rtol=1e-5,
+atol=1e-6: python/cuml/tests/test_isolation_forest.py:751-762).
+"""
+import numpy as np
+import pytest
+
+from cuml_b200.fil import ForestInference, synthetic_complete_forest
+from cuml_b200.fil._desc import (INFER_CLASS, INFER_DEFAULT, INFER_LEAF_ID, INFER_PER_TREE,
+                                 INFER_PROBA2, OP_LE, OP_LT)
+from oracle import oracle
+from tests.helpers import load_golden, random_forest_desc, random_rows
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"single": dict(rtol=1e-5, atol=1e-6), "double": dict(rtol=1e-12, atol=1e-13)}
+CONFIGS = [("depth_first", "sparse"), ("breadth_first", "sparse"), ("layered", "sparse"),
+           ("depth_first", "dense"), ("depth_first", "auto")]
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _dev(X, precision):
+    torch = _torch()
+    dt = torch.float32 if precision == "single" else torch.float64
+    return torch.as_tensor(np.ascontiguousarray(X), device="cuda:0").to(dt)
+
+
+def _all_kinds(desc, X, precision, layout, storage, chunk_size=None, host=False):
+    """Run every output kind on the GPU and compare with the oracle."""
+    fi = ForestInference.load_from_treelite_model(desc, precision=precision, layout=layout,
+                                                  storage=storage)
+    Xo = np.ascontiguousarray(X, np.float32 if precision == "single" else np.float64)
+    Xd = Xo if host else _dev(Xo, precision)
+
+    def get(a):
+        return a if isinstance(a, np.ndarray) else a.cpu().numpy()
+
+    ids = get(fi.apply(Xd, chunk_size=chunk_size))
+    assert np.array_equal(ids.astype(np.uint32), oracle.predict(desc, Xo, INFER_LEAF_ID, precision))
+    pt = get(fi.predict_per_tree(Xd, chunk_size=chunk_size))
+    assert np.array_equal(pt, oracle.predict(desc, Xo, INFER_PER_TREE, precision))
+    raw = get(fi._run(Xd, INFER_DEFAULT, chunk_size))
+    want = oracle.predict(desc, Xo, INFER_DEFAULT, precision)
+    np.testing.assert_allclose(raw, want, **TOL[precision])
+    cls = get(fi._run(Xd, INFER_CLASS, chunk_size, threshold=0.5))
+    want_cls = oracle.predict(desc, Xo, INFER_CLASS, precision, threshold=0.5)
+    if desc.n_outputs == 1:
+        safe = np.abs(want[:, 0] - 0.5) > 1e-4  # scores at the threshold may fall either way
+    else:
+        top2 = np.sort(want, axis=1)[:, -2:]
+        safe = (top2[:, 1] - top2[:, 0]) > 1e-4 * np.maximum(1.0, np.abs(top2[:, 1]))
+    assert np.array_equal(cls[safe], want_cls[safe])
+    if desc.n_outputs == 1:
+        p2 = get(fi._run(Xd, INFER_PROBA2, chunk_size))
+        np.testing.assert_allclose(p2, oracle.predict(desc, Xo, INFER_PROBA2, precision),
+                                   **TOL[precision])
+    return fi
+
+
+@pytest.mark.parametrize("layout,storage", CONFIGS)
+@pytest.mark.parametrize("precision", ["single", "double"])
+def test_random_forests_operators_nan(layout, storage, precision):
+    desc = random_forest_desc(1, n_trees=23, max_depth=6, mixed_ops=True, integer_thresholds=True,
+                              postproc="sigmoid")
+    X = random_rows(2, 777, desc.n_features, np.float64, nan_frac=0.15, integer=True)
+    _all_kinds(desc, X, precision, layout, storage)
+
+
+@pytest.mark.parametrize("layout,storage", CONFIGS)
+@pytest.mark.parametrize("big", [False, True])
+def test_categorical(layout, storage, big):
+    desc = random_forest_desc(3 + big, n_trees=17, max_depth=5, categorical=True,
+                              big_categories=big, mixed_ops=True, n_outputs=3, postproc="softmax")
+    X = random_rows(4, 500, desc.n_features, np.float32, nan_frac=0.1, categories=75 if big else 22)
+    _all_kinds(desc, X, "single", layout, storage)
+    _all_kinds(desc, X, "double", layout, storage)
+
+
+@pytest.mark.parametrize("layout,storage", CONFIGS)
+@pytest.mark.parametrize("precision", ["single", "double"])
+def test_vector_leaves(layout, storage, precision):
+    desc = random_forest_desc(5, n_trees=13, n_outputs=5, vector=True, average=True)
+    X = random_rows(6, 300, desc.n_features, np.float32)
+    _all_kinds(desc, X, precision, layout, storage)
+
+
+@pytest.mark.parametrize("post", ["identity", "sigmoid", "exponential", "logarithm_one_plus_exp",
+                                  "signed_square", "hinge", "exponential_standard_ratio"])
+def test_postprocessors_one_output(post):
+    desc = random_forest_desc(40, n_trees=6, postproc=post, base=True, average=True)
+    X = random_rows(5, 200, desc.n_features, np.float32, nan_frac=0.0)
+    for storage in ("dense", "sparse"):
+        fi = ForestInference.load_from_treelite_model(desc, storage=storage)
+        got = fi._run(_dev(X, "single"), INFER_DEFAULT, None).cpu().numpy()
+        want = oracle.predict(desc, X, INFER_DEFAULT, "single")
+        if post == "hinge":
+            safe = np.abs(oracle.predict(
+                random_forest_desc(40, n_trees=6, postproc="identity", base=True, average=True),
+                X, INFER_DEFAULT, "single")) > 1e-5
+            assert np.array_equal(got[safe], want[safe])
+        else:
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("post", ["softmax", "multiclass_ova"])
+def test_postprocessors_multiclass(post):
+    desc = random_forest_desc(41, n_trees=12, n_outputs=4, postproc=post, base=True)
+    X = random_rows(5, 200, desc.n_features, np.float32, nan_frac=0.0)
+    for storage in ("dense", "sparse"):
+        _all_kinds(desc, X, "single", "depth_first", storage)
+
+
+@pytest.mark.parametrize("n_rows", [0, 1, 31, 32, 33, 127, 129, 1000])
+def test_ragged_batch_sizes(n_rows):
+    desc = random_forest_desc(50, n_trees=9, max_depth=5, n_outputs=2, postproc="softmax")
+    X = random_rows(7, max(n_rows, 1), desc.n_features, np.float32)[:n_rows]
+    for storage in ("dense", "sparse"):
+        fi = ForestInference.load_from_treelite_model(desc, storage=storage)
+        got = fi.predict_proba(_dev(X, "single").reshape(n_rows, desc.n_features)).cpu().numpy()
+        assert got.shape == (n_rows, 2)
+        if n_rows:
+            np.testing.assert_allclose(got, oracle.predict(desc, X, INFER_DEFAULT, "single"),
+                                       rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("chunk_size", [1, 2, 4, 8, 16, 32])
+def test_chunk_sizes_give_identical_ids(chunk_size):
+    desc = random_forest_desc(51, n_trees=19, max_depth=6)
+    X = random_rows(8, 3000, desc.n_features, np.float32)
+    for storage in ("dense", "sparse"):
+        _all_kinds(desc, X, "single", "depth_first", storage, chunk_size=chunk_size)
+
+
+def test_single_leaf_trees_and_tiny_forests():
+    for depth in (0, 1):
+        desc = random_forest_desc(52, n_trees=3, max_depth=depth, p_leaf=0.0)
+        X = random_rows(9, 70, desc.n_features, np.float32)
+        for storage in ("dense", "sparse"):
+            _all_kinds(desc, X, "single", "depth_first", storage)
+
+
+def test_row_stride_and_host_buffers():
+    torch = _torch()
+    desc = random_forest_desc(53, n_trees=11, max_depth=5, n_features=6)
+    wide = torch.as_tensor(random_rows(10, 500, 10, np.float32), device="cuda:0")
+    view = wide[:, :6]  # rows 10 elements apart, 6 used
+    assert view.stride(0) == 10
+    fi = ForestInference.load_from_treelite_model(desc)
+    got = fi.apply(view).cpu().numpy()
+    X = view.cpu().numpy()
+    assert np.array_equal(got.astype(np.uint32), oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+    # host buffers take the copy-predict-copy pipeline inside the library
+    _all_kinds(desc, X, "single", "depth_first", "auto", host=True)
+    _all_kinds(desc, X, "double", "depth_first", "sparse", host=True)
+
+
+def test_golden_rfc_depth8():
+    desc, X, exp = load_golden("rfc_depth8")
+    for storage in ("dense", "sparse"):
+        fi = ForestInference.load_from_treelite_model(desc, storage=storage)
+        assert type(fi).__name__ == "ForestInferenceClassifier"
+        Xd = _dev(X, "single")
+        assert np.array_equal(fi.apply(Xd).cpu().numpy().astype(np.int64), exp["leaf_ids"])
+        np.testing.assert_allclose(fi.predict_proba(Xd).cpu().numpy(), exp["proba"],
+                                   rtol=1e-5, atol=1e-6)
+        pred = fi.predict(Xd).cpu().numpy()
+        safe = np.abs(exp["proba"][:, 0] - 0.5) > 1e-4
+        assert np.array_equal(pred[safe].astype(np.int64), exp["labels"][safe])
+        # predict == argmax(predict_proba): python/cuml/tests/test_random_forest.py:853-855
+        assert np.array_equal(pred, np.argmax(fi.predict_proba(Xd).cpu().numpy(), axis=1))
+
+
+def test_golden_rfr_depth20_fp64():
+    desc, X, exp = load_golden("rfr_depth20")
+    for layout in ("depth_first", "breadth_first", "layered"):
+        fi = ForestInference.load_from_treelite_model(desc, precision="double", layout=layout)
+        assert type(fi).__name__ == "ForestInferenceRegressor"
+        assert fi.describe()["storage"] == 2
+        Xd = _dev(X, "double")
+        assert np.array_equal(fi.apply(Xd).cpu().numpy().astype(np.int64), exp["leaf_ids"])
+        got = fi.predict(Xd).cpu().numpy()
+        assert got.shape == (X.shape[0], 1)
+        np.testing.assert_allclose(got[:, 0], exp["values"], rtol=1e-12, atol=1e-12)
+
+
+def test_golden_gbc_3class_and_missing():
+    desc, X, exp = load_golden("gbc_3class")
+    fi = ForestInference.load_from_treelite_model(desc, precision="double")
+    np.testing.assert_allclose(fi.predict_proba(_dev(X, "double")).cpu().numpy(), exp["proba"],
+                               rtol=1e-12, atol=1e-13)
+    desc, X, exp = load_golden("rfc_missing")
+    for storage in ("dense", "sparse"):
+        fi = ForestInference.load_from_treelite_model(desc, storage=storage)
+        Xd = _dev(X, "single")
+        assert np.array_equal(fi.apply(Xd).cpu().numpy().astype(np.int64), exp["leaf_ids"])
+        np.testing.assert_allclose(fi.predict_proba(Xd).cpu().numpy(), exp["proba"],
+                                   rtol=1e-5, atol=1e-6)
+
+
+def test_sklearn_models_trained_here():
+    from sklearn.datasets import make_classification
+    from sklearn.ensemble import GradientBoostingClassifier, RandomForestClassifier
+
+    X, y = make_classification(n_samples=3000, n_features=32, n_informative=16, n_classes=2,
+                               random_state=0)
+    X = X.astype(np.float32)
+    m = RandomForestClassifier(n_estimators=100, max_depth=8, random_state=0, n_jobs=-1).fit(X, y)
+    Xt = make_classification(n_samples=20000, n_features=32, n_informative=16, n_classes=2,
+                             random_state=1)[0].astype(np.float32)
+    fi = ForestInference.load_from_sklearn(m)
+    assert fi.is_classifier and fi.describe()["storage"] == 1
+    assert np.array_equal(fi.apply(Xt).astype(np.int64), m.apply(Xt))
+    np.testing.assert_allclose(fi.predict_proba(Xt), m.predict_proba(Xt), rtol=1e-5, atol=1e-6)
+    g = GradientBoostingClassifier(n_estimators=30, max_depth=3, random_state=0).fit(X[:, :8], y)
+    fg = ForestInference.load_from_sklearn(g, precision="double")
+    Xg = Xt[:, :8].astype(np.float64)
+    np.testing.assert_allclose(fg.predict_proba(Xg), g.predict_proba(Xg), rtol=1e-12, atol=1e-13)
+
+
+def _config_forest(name):
+    if name == "c2":  # 1000 complete depth-8 trees, 256 features, sigmoid (smaller row count)
+        return synthetic_complete_forest(1000, 8, 256, seed=2), 256, None, 0.0
+    if name == "c4":  # 10-class boosted forest, depth 6, 8 categorical features, 5 % NaN
+        return (synthetic_complete_forest(500, 6, 128, seed=4, n_classes=10, n_categorical=8,
+                                          n_categories=32), 128, 32, 0.05)
+    if name == "c5":  # complete depth-10 trees, 512 features
+        return synthetic_complete_forest(64, 10, 512, seed=6), 512, None, 0.0
+    raise KeyError(name)
+
+
+@pytest.mark.parametrize("name", ["c2", "c4", "c5"])
+def test_benchmark_config_shapes(name):
+    desc, F, cats, nan_frac = _config_forest(name)
+    rng = np.random.default_rng(3)
+    n = 6000
+    X = rng.standard_normal((n, F)).astype(np.float32)
+    if cats:
+        X[:, :8] = rng.integers(0, cats, size=(n, 8)).astype(np.float32)
+        X[rng.random((n, F)) < nan_frac] = np.nan
+    fi = ForestInference.load_from_treelite_model(desc)
+    assert fi.describe()["storage"] == 1
+    Xd = _dev(X, "single")
+    proba = fi.predict_proba(Xd).cpu().numpy()
+    kind = INFER_PROBA2 if desc.n_outputs == 1 else INFER_DEFAULT
+    np.testing.assert_allclose(proba, oracle.predict(desc, X, kind, "single"), rtol=1e-5, atol=1e-6)
+    ids = fi.apply(Xd[:1500]).cpu().numpy()
+    assert np.array_equal(ids.astype(np.uint32),
+                          oracle.predict(desc, X[:1500], INFER_LEAF_ID, "single"))
+    # the same forest with `<=` tests and sparse storage agrees as well
+    if name == "c2":
+        desc_le = synthetic_complete_forest(1000, 8, 256, seed=2, op=OP_LE)
+        fl = ForestInference.load_from_treelite_model(desc_le, storage="sparse",
+                                                      layout="breadth_first")
+        ids = fl.apply(Xd[:1500]).cpu().numpy()
+        assert np.array_equal(ids.astype(np.uint32),
+                              oracle.predict(desc_le, X[:1500], INFER_LEAF_ID, "single"))
+
+
+def test_full_size_c2_properties():
+    """The headline workload at full size (10 M rows x 256 features, 1000 depth-8 trees):
+    a random sample of rows against the oracle, and a sum-of-leaves check that ties the leaf-id
+    output to the score output on a slice."""
+    torch = _torch()
+    desc = synthetic_complete_forest(1000, 8, 256, seed=2)
+    fi = ForestInference.load_from_treelite_model(desc)
+    n = 10_000_000
+    g = torch.Generator(device="cuda:0")
+    g.manual_seed(3)
+    X = torch.randn((n, 256), generator=g, device="cuda:0", dtype=torch.float32)
+    proba = fi.predict_proba(X)
+    assert proba.shape == (n, 2)
+    idx = torch.randint(0, n, (4096,), generator=g, device="cuda:0")
+    idx[:3] = torch.tensor([0, n - 1, n // 2], device="cuda:0")
+    Xs = X[idx].cpu().numpy()
+    np.testing.assert_allclose(proba[idx].cpu().numpy(),
+                               oracle.predict(desc, Xs, INFER_PROBA2, "single"),
+                               rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(proba.sum(dim=1).cpu().numpy(), 1.0, rtol=1e-6)
+    # leaf ids -> leaf values -> sum -> sigmoid reproduces the scores
+    m = 200_000
+    ids = fi.apply(X[:m]).long()  # heap ids of the complete trees
+    leaf = torch.as_tensor(desc.leaf_value.reshape(1000, -1), device="cuda:0")
+    vals = leaf.gather(1, ids.t()).t()  # (m, 1000) float64
+    score = torch.sigmoid(vals.sum(dim=1))
+    np.testing.assert_allclose(proba[:m, 1].cpu().numpy(), score.cpu().numpy(), rtol=1e-5, atol=1e-6)
+    per_tree = fi.predict_per_tree(X[:m])
+    assert torch.equal(per_tree.double(), vals)
+
+
+def test_status_word_and_launch_counter(lib):
+    import ctypes as C
+
+    desc = random_forest_desc(60, n_trees=5)
+    fi = ForestInference.load_from_treelite_model(desc, storage="dense")
+    before = lib.b2fil_kernel_launches()
+    fi.apply(_dev(random_rows(1, 100, desc.n_features), "single"))
+    _torch().cuda.synchronize()
+    assert lib.b2fil_kernel_launches() == before + 1
+    st = C.c_int32(-1)
+    assert lib.b2fil_forest_status(fi.forest.handle, C.byref(st)) == 0 and st.value == 0
+
+
+def test_pickle_round_trip():
+    import pickle
+
+    desc = random_forest_desc(61, n_trees=7, n_outputs=3, vector=True, average=True)
+    fi = ForestInference.load_from_treelite_model(desc)
+    X = _dev(random_rows(2, 200, desc.n_features), "single")
+    a = fi.predict_proba(X).cpu().numpy()
+    fi2 = pickle.loads(pickle.dumps(fi))
+    assert np.array_equal(a, fi2.predict_proba(X).cpu().numpy())
