@@ -69,6 +69,7 @@ struct b2fil_forest {
   int32_t device = 0, sm_count = 0, default_chunk = 0;
   int64_t n_nodes_in = 0, n_nodes_packed = 0, device_bytes = 0;
   int32_t* status = nullptr;
+  cudaMemPool_t pool = nullptr;  // stream-ordered scratch of the rank-quantised path
   struct Block {
     void* ptr;
     size_t bytes;
@@ -82,6 +83,7 @@ struct b2fil_forest {
     DeviceGuard g(device);
     for (auto& b : blocks) cudaFree(b.ptr);
     if (status) cudaFree(status);
+    if (pool) cudaMemPoolDestroy(pool);
     for (auto& s : slots) {
       if (s.x) cudaFree(s.x);
       if (s.out) cudaFree(s.out);
@@ -119,6 +121,16 @@ int init_device_state(b2fil_forest* f)
   f->sm_count = prop.multiProcessorCount;
   B2FIL_CUDA(cudaMalloc(&f->status, sizeof(int32_t)));
   B2FIL_CUDA(cudaMemset(f->status, 0, sizeof(int32_t)));
+  // a pool of its own keeps freed scratch cached between predictions without touching the
+  // settings of the device's default pool
+  cudaMemPoolProps props{};
+  props.allocType     = cudaMemAllocationTypePinned;
+  props.handleTypes   = cudaMemHandleTypeNone;
+  props.location.type = cudaMemLocationTypeDevice;
+  props.location.id   = f->device;
+  B2FIL_CUDA(cudaMemPoolCreate(&f->pool, &props));
+  uint64_t keep = ~uint64_t(0);
+  B2FIL_CUDA(cudaMemPoolSetAttribute(f->pool, cudaMemPoolAttrReleaseThreshold, &keep));
   return B2FIL_OK;
 }
 
@@ -172,7 +184,8 @@ int enqueue(const b2fil_forest* f, int kind, const void* X, int64_t n_rows, int6
   std::string err;
   int64_t n = 0;
   const int rc =
-    launch_predict(p, chunk_size > 0 ? chunk_size : f->default_chunk, f->sm_count, stream, err, &n);
+    launch_predict(p, chunk_size > 0 ? chunk_size : f->default_chunk, f->sm_count, stream, f->pool,
+                   err, &n);
   g_launches += n;
   if (rc != B2FIL_OK) return set_error(rc, err);
   return B2FIL_OK;
@@ -258,6 +271,15 @@ int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* 
     if ((rc = upload(f.get(), pf.out_scale, offsetof(ForestView, out_scale))) != B2FIL_OK)
       return rc;
     if ((rc = upload(f.get(), pf.out_bias, offsetof(ForestView, out_bias))) != B2FIL_OK) return rc;
+    if (pf.view.q_enabled) {
+      if ((rc = upload(f.get(), pf.q_nodes, offsetof(ForestView, q_nodes))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.q_thresholds, offsetof(ForestView, q_thresholds))) != B2FIL_OK)
+        return rc;
+      if ((rc = upload(f.get(), pf.q_lut, offsetof(ForestView, q_lut))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.q_feats, offsetof(ForestView, q_feats))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.q_groups, offsetof(ForestView, q_groups))) != B2FIL_OK)
+        return rc;
+    }
     *out = f.release();
     return B2FIL_OK;
   } catch (const std::bad_alloc&) {
@@ -339,6 +361,7 @@ int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info)
   info->n_nodes_packed     = f->n_nodes_packed;
   info->device_bytes       = f->device_bytes;
   info->default_chunk_size = f->default_chunk;
+  info->row_quantization   = f->view.q_enabled;
   return B2FIL_OK;
 }
 

@@ -18,6 +18,7 @@
 // thresholds to the next representable value where needed, so the kernels evaluate one operator.
 #pragma once
 
+#include <cmath>
 #include <cstdint>
 #include <string>
 #include <vector>
@@ -62,6 +63,35 @@ struct SparseNode16D {  // fp64
   uint32_t offset;
 };
 
+// ---- rank quantisation of rows (dense storage without categorical tests) -----------------------
+// For every feature the distinct thresholds of the forest are sorted: T[0] < T[1] < ...  The rank
+// of a value, r(x) = #{i : T[i] <= x}, decides every test on that feature exactly:
+//     x < T[j]  <=>  r(x) <= j.
+// A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x7FFF); the traversal kernel
+// then reads 2-byte values and 4-byte nodes
+//     bits 31..16: j (0xFFFF = never left)   bit 15: missing goes left   bits 14..0: feature
+// so a test is one signed subtraction: right <=> int(node) - (rank << 16) < 0.
+// The rank is found through a per-feature bucket table: bucket(x) = clamp(int(fma(x, scale,
+// offset)), 0, n_buckets-1) is monotone in x, lut[b] is the number of thresholds in buckets below
+// b, and only the thresholds of the value's own bucket are compared one by one.
+struct QFeature {
+  uint32_t t_off;      // first threshold of the feature in the threshold table
+  uint32_t lut_off;    // first entry of the feature's bucket table (n_buckets + 1 entries)
+  uint32_t m;          // number of distinct thresholds
+  uint32_t n_buckets;
+  double scale;        // bucket(x) = fma(x, scale, offset) evaluated in the forest precision
+  double offset;
+};
+struct QGroup {        // consecutive features whose tables share one CTA's shared memory
+  uint32_t f_begin, f_end;
+  uint32_t smem_bytes; // bytes of their tables
+  uint32_t pad;
+};
+constexpr uint32_t Q_NAN_CODE     = 0x7FFFu;
+constexpr uint32_t Q_MAX_RANK     = 0x7FFEu;
+constexpr uint32_t Q_FEATURE_MASK = 0x7FFFu;
+constexpr uint32_t Q_DEFAULT_LEFT = 0x8000u;
+
 enum NodeFormat : int32_t {
   FMT_DENSE_F   = 0,
   FMT_DENSE_D   = 1,
@@ -96,6 +126,15 @@ struct ForestView {
   const void* out_bias;     // [n_outputs] base scores
   double sigmoid_alpha;
   double ratio_c;
+  // rank-quantised copy of a dense forest (q_enabled != 0)
+  int32_t q_enabled;
+  int32_t q_n_groups;
+  int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size), 16-byte multiple
+  const void* q_nodes;          // [n_trees] blocks of [2^D nodes uint32][2^D leaf payloads]
+  const void* q_thresholds;     // sorted distinct thresholds of all features, forest precision
+  const uint16_t* q_lut;        // bucket tables of all features
+  const QFeature* q_feats;      // [n_features]
+  const QGroup* q_groups;       // [q_n_groups]
 };
 
 // Host-side result of packing, before upload.
@@ -116,7 +155,27 @@ struct PackedForest {
   std::vector<uint8_t> leaf_vectors;
   std::vector<uint8_t> out_scale;
   std::vector<uint8_t> out_bias;
+  std::vector<uint8_t> q_nodes;
+  std::vector<uint8_t> q_thresholds;
+  std::vector<uint16_t> q_lut;
+  std::vector<QFeature> q_feats;
+  std::vector<QGroup> q_groups;
 };
+
+// Bucket of a value in a feature's table; the same expression runs on the device
+// (fma and float->int truncation are exactly specified, so host and device agree bit for bit).
+template <typename T>
+inline uint32_t q_bucket_host(T x, T scale, T offset, uint32_t n_buckets)
+{
+  T v = std::fma(x, scale, offset);
+  v   = std::fmax(v, T(0));  // also turns NaN (inf * 0) into 0
+  v   = std::fmin(v, static_cast<T>(n_buckets - 1));
+  return static_cast<uint32_t>(v);
+}
+
+// Shared memory the quantisation kernel may spend on the tables of one feature group.
+constexpr uint32_t kQGroupSmemBudget = 160 * 1024;
+constexpr uint32_t kQMaxGroupFeatures = 32;
 
 // Validate `desc`, normalise its tests and lay its nodes out.  Returns B2FIL_OK or an error code
 // with `err` set.  `dense_ok(depth, precision, n_features, n_outputs)` tells whether the dense

@@ -24,6 +24,8 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 
 #include "kernels.hpp"
 
@@ -90,6 +92,25 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
       dst),
     "l"(src), "r"(bytes), "r"(bar)
     : "memory");
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a)
+{
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a)
+{
+  uint32_t v;
+  asm volatile(
+    "{\n"
+    ".reg .u16 h;\n"
+    "ld.shared.u16 h, [%1];\n"
+    "cvt.u32.u16 %0, h;\n"
+    "}\n"
+    : "=r"(v)
+    : "r"(a));
+  return v;
 }
 // Barrier among the consumer threads only (the producer warp never joins it).
 __device__ __forceinline__ void consumer_sync(int n_threads)
@@ -542,6 +563,314 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
 }
 
 // ---------------------------------------------------------------------------------------------
+// RANK QUANTISATION of rows (pre-pass of the quantised dense kernel)
+// ---------------------------------------------------------------------------------------------
+// One CTA owns one feature group (its bucket tables and sorted thresholds sit in shared memory)
+// and loops over row tiles.  Thread (x = feature of the group, y = row stripe) reads one value,
+// finds its rank and parks it in a transposed staging buffer; the buffer is then written out as
+// Q[tile][feature][row in tile] (uint16), the layout the traversal kernel pulls into shared
+// memory with a single bulk copy.  A NaN becomes Q_NAN_CODE and raises the tile's flag.
+struct QFeatS {       // per-feature record in shared memory
+  uint32_t lut;       // shared-memory address of the bucket table
+  uint32_t thr;       // shared-memory address of the sorted thresholds
+  uint32_t nbm1;      // n_buckets - 1
+  uint32_t pad;
+  double scale, offset;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512, 1)
+quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __restrict__ tile_flags,
+                const int R)
+{
+  using TR = Traits<T>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const ForestView& f = p.f;
+  const QGroup grp    = f.q_groups[blockIdx.y];
+  const int GF        = grp.f_end - grp.f_begin;
+  const int F         = f.n_features;
+  const int tid       = threadIdx.y * 32 + threadIdx.x;
+  const int nthreads  = blockDim.y * 32;
+  QFeatS* fs          = reinterpret_cast<QFeatS*>(smem);
+  unsigned char* tab  = smem + kQMaxGroupFeatures * sizeof(QFeatS);
+  const int qstride   = R + 2;  // uint16 elements between features in the staging buffer
+  uint16_t* qbuf      = reinterpret_cast<uint16_t*>(tab + grp.smem_bytes);
+  const T* thr_all    = static_cast<const T*>(f.q_thresholds);
+
+  // tables of the group -> shared memory
+  if (tid == 0) {
+    uint32_t off = 0;
+    for (int i = 0; i < GF; ++i) {
+      const QFeature qf = f.q_feats[grp.f_begin + i];
+      fs[i].lut         = smem_addr(tab + off);
+      off += ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
+      fs[i].thr = smem_addr(tab + off);
+      off += (qf.m * sizeof(T) + 7) / 8 * 8;
+      fs[i].nbm1   = qf.n_buckets - 1;
+      fs[i].scale  = qf.scale;
+      fs[i].offset = qf.offset;
+    }
+  }
+  __syncthreads();
+  for (int i = 0; i < GF; ++i) {
+    const QFeature qf  = f.q_feats[grp.f_begin + i];
+    uint16_t* lut_s    = reinterpret_cast<uint16_t*>(smem + (fs[i].lut - smem_addr(smem)));
+    T* thr_s           = reinterpret_cast<T*>(smem + (fs[i].thr - smem_addr(smem)));
+    for (uint32_t k = tid; k <= qf.n_buckets; k += nthreads) lut_s[k] = f.q_lut[qf.lut_off + k];
+    for (uint32_t k = tid; k < qf.m; k += nthreads) thr_s[k] = thr_all[qf.t_off + k];
+  }
+  __syncthreads();
+
+  const int i           = threadIdx.x;
+  const bool live_lane  = i < GF;
+  const QFeatS my       = fs[live_lane ? i : 0];
+  const T scale         = static_cast<T>(my.scale);
+  const T offset        = static_cast<T>(my.offset);
+  const T nbm1          = static_cast<T>(my.nbm1);
+  const T* X            = static_cast<const T*>(p.X);
+  const int64_t n_tiles = (p.n_rows + R - 1) / R;
+  const int half        = R / 2;
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t row0 = t * R;
+    bool saw_nan       = false;
+    if (live_lane) {
+      for (int r = threadIdx.y; r < R; r += blockDim.y) {
+        const int64_t row = row0 + r;
+        uint32_t code     = 0;
+        if (row < p.n_rows) {
+          const T x = __ldg(X + row * p.row_stride + grp.f_begin + i);
+          if (x != x) {
+            code    = Q_NAN_CODE;
+            saw_nan = true;
+          } else {
+            // same expression as q_bucket_host: fma, clamp (NaN from inf * 0 becomes 0), truncate
+            T v = fma(x, scale, offset);
+            v   = fmax(v, T(0));
+            v   = fmin(v, nbm1);
+            const uint32_t b = static_cast<uint32_t>(v);
+            const uint32_t w = lds_u32(my.lut + (b & ~1u) * 2u);
+            uint32_t lo, hi;
+            if (b & 1u) {
+              lo = w >> 16;
+              hi = lds_u16(my.lut + (b + 1u) * 2u);
+            } else {
+              lo = w & 0xFFFFu;
+              hi = w >> 16;
+            }
+            // thresholds of lower buckets are all <= x, those of higher buckets all > x
+            while (lo < hi && !(x < TR::ld_real(my.thr + lo * TR::ES))) ++lo;
+            code = lo;
+          }
+        }
+        qbuf[i * qstride + r] = static_cast<uint16_t>(code);
+      }
+    }
+    if (__any_sync(0xffffffffu, saw_nan) && threadIdx.x == 0) atomicOr(tile_flags + t, 1);
+    __syncthreads();
+    // staging buffer -> Q[tile][feature][row], two rows per 32-bit store
+    const uint32_t* qbuf32 = reinterpret_cast<const uint32_t*>(qbuf);
+    uint32_t* out32 = reinterpret_cast<uint32_t*>(Q) + (t * F + grp.f_begin) * static_cast<int64_t>(half);
+    for (int e = tid; e < GF * half; e += nthreads) {
+      const int fi = e / half;
+      const int c  = e - fi * half;
+      out32[static_cast<int64_t>(fi) * half + c] = qbuf32[fi * (half + 1) + c];
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// DENSE kernel on rank-quantised rows
+// ---------------------------------------------------------------------------------------------
+// Shared memory: [mbarriers 128 B][row tile F x R uint16][accumulators][flags 16 B][S tree stages].
+// The row tile arrives with one bulk copy per tile (the pre-pass already stored it feature-major);
+// tree batches stream through the stage ring exactly as in dense_kernel.  A node is 4 bytes
+// (rank j << 16 | default-left << 15 | feature) and a test is one signed subtraction.
+constexpr int kBarTileFull  = 2 * kMaxStages;      // mbarrier slots after the stage ring
+constexpr int kBarTileEmpty = 2 * kMaxStages + 1;
+
+template <typename T, int MODE, int NT>
+struct DenseQWalker {
+  using TR = Traits<T>;
+  template <bool NANS>
+  static __device__ __forceinline__ bool walk(const PredictParams& p, int G, int S, int g, int r,
+                                              int64_t row, int lane, uint32_t bars,
+                                              uint32_t stages, uint32_t stage_bytes,
+                                              uint32_t row_addr, uint32_t stride_b, T* acc_group,
+                                              int R, uint32_t& it, Running<T>& run)
+  {
+    const ForestView& f    = p.f;
+    const int D            = f.dense_depth;
+    const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
+    const uint32_t width_b = (1u << D) * 4u;
+    const int per_batch    = G * NT;
+    const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
+    bool ok                = true;
+    for (int b = 0; b < n_batches; ++b, ++it) {
+      const uint32_t s = it % S;
+      if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
+      if (ok) {
+        const int first = b * per_batch + g * NT;
+        const int n_act = min(NT, f.n_trees - first);
+        if (n_act > 0) {
+          uint32_t base[NT], a[NT];
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            const int slot = g * NT + min(k, n_act - 1);
+            base[k]        = stages + s * stage_bytes + slot * tstride;
+            a[k]           = base[k] + 4u;  // heap index 1
+          }
+          for (int lvl = 0; lvl < D; ++lvl) {
+#pragma unroll
+            for (int k = 0; k < NT; ++k) {
+              const uint32_t node = lds_u32(a[k]);
+              const uint32_t q    = lds_u16((node & Q_FEATURE_MASK) * stride_b + row_addr);
+              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
+              bool right = (static_cast<int32_t>(node) - static_cast<int32_t>(q << 16)) < 0;
+              if (NANS) {
+                if (q == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) == 0u;
+              }
+              a[k] = 2u * a[k] - base[k] + (right ? 4u : 0u);
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            if (k < n_act) {
+              const uint32_t slot = (a[k] - base[k]) / 4u - (1u << D);
+              const typename TR::Val payload = TR::ld_val(base[k] + width_b + slot * TR::ES);
+              take_leaf<T, MODE>(p, first + k, payload,
+                                 (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
+                                 row, run);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
+    }
+    return ok;
+  }
+};
+
+template <typename T, int MODE, int NT>
+__global__ void __launch_bounds__(1056, 1)
+dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
+               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S)
+{
+  using TR = Traits<T>;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const ForestView& f = p.f;
+  const int F         = f.n_features;
+  const int NC        = f.n_outputs;
+  const int rw        = R >> 5;
+  const int n_cw      = rw * G;
+  const int n_ct      = n_cw * 32;
+  const int warp      = threadIdx.x >> 5;
+  const int lane      = threadIdx.x & 31;
+
+  const uint32_t stride_b    = R * 2u;  // bytes between features in the tile
+  const uint32_t tile_bytes  = static_cast<uint32_t>(F) * stride_b;  // multiple of 64
+  const size_t acc_bytes     = (MODE <= MODE_VECTOR) ? align16(static_cast<size_t>(G) * NC * R * TR::ES) : 0;
+  unsigned char* tile_ptr    = smem + kBarBytes;
+  T* acc                     = reinterpret_cast<T*>(tile_ptr + tile_bytes);
+  unsigned char* stage_ptr   = tile_ptr + tile_bytes + acc_bytes + 16;
+  const uint32_t bars        = smem_addr(smem);
+  const uint32_t tile        = smem_addr(tile_ptr);
+  const uint32_t stages      = smem_addr(stage_ptr);
+  const uint32_t tstride     = static_cast<uint32_t>(f.q_tree_stride);
+  const int per_batch        = G * NT;
+  const uint32_t stage_bytes = per_batch * tstride;
+  const int n_batches        = (f.n_trees + per_batch - 1) / per_batch;
+  const int64_t n_tiles      = (p.n_rows + R - 1) / R;
+  const uint32_t bar_tfull   = bars + 8u * kBarTileFull;
+  const uint32_t bar_tempty  = bars + 8u * kBarTileEmpty;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bars + 8u * s, 1);
+      mbar_init(bars + 8u * (kMaxStages + s), n_cw);
+    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, n_cw);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == n_cw) {
+    // ---- producer: row tile, then the tree batches of that tile ------------------------------
+    if (lane == 0) {
+      const unsigned char* src  = static_cast<const unsigned char*>(f.q_nodes);
+      const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(Q);
+      uint32_t it               = 0;
+      uint32_t n_done           = 0;
+      for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
+        // the tile buffer is free once every consumer warp has left the previous tile's trees
+        if (n_done > 0 && !mbar_wait(bar_tempty, (n_done - 1) & 1u)) {
+          atomicExch(p.status, 3);
+          return;
+        }
+        mbar_expect_tx(bar_tfull, tile_bytes);
+        bulk_copy_g2s(tile, qsrc + static_cast<size_t>(t) * tile_bytes, tile_bytes, bar_tfull);
+        for (int b = 0; b < n_batches; ++b, ++it) {
+          const uint32_t s   = it % S;
+          const uint32_t use = it / S;
+          if (use > 0 && !mbar_wait(bars + 8u * (kMaxStages + s), (use - 1) & 1u)) {
+            atomicExch(p.status, 1);
+            return;
+          }
+          const int first      = b * per_batch;
+          const int count      = min(per_batch, f.n_trees - first);
+          const uint32_t bytes = count * tstride;
+          mbar_expect_tx(bars + 8u * s, bytes);
+          bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
+                        bytes, bars + 8u * s);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ------------------------------------------------------------------------------
+  const int g             = warp / rw;
+  const int r             = (warp % rw) * 32 + lane;
+  T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
+  const uint32_t row_addr = tile + r * 2u;
+  uint32_t it             = 0;
+  uint32_t n_done         = 0;
+  bool ok                 = true;
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
+    const int64_t row0 = t * R;
+    if (MODE <= MODE_VECTOR) {
+      for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
+    }
+    const bool nans = __ldg(tile_flags + t) != 0;
+    consumer_sync(n_ct);
+    if (ok) ok = mbar_wait(bar_tfull, n_done & 1u);
+    Running<T> run{T(0), 0};
+    if (ok) {
+      if (nans) {
+        ok = DenseQWalker<T, MODE, NT>::template walk<true>(
+          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
+          R, it, run);
+      } else {
+        ok = DenseQWalker<T, MODE, NT>::template walk<false>(
+          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
+          R, it, run);
+      }
+      if (!ok) atomicExch(p.status, 2);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_tempty);
+    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    consumer_sync(n_ct);
+    if (MODE <= MODE_VECTOR) {
+      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+    }
+    consumer_sync(n_ct);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // SPARSE kernel
 // ---------------------------------------------------------------------------------------------
 template <int FMT>
@@ -778,6 +1107,173 @@ int launch_sparse_fmt(const PredictParams& p, int mode, int R, int G, int rows_i
   return B2FIL_OK;
 }
 
+size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R, int G, int NT, int S)
+{
+  const size_t es      = precision == B2FIL_F32 ? 4 : 8;
+  const size_t qstride = align16((size_t(1) << depth) * (4 + es));
+  size_t b             = kBarBytes;
+  b += static_cast<size_t>(F) * R * 2;
+  if (reduce) b += align16(static_cast<size_t>(G) * NC * R * es);
+  b += 16;
+  b += static_cast<size_t>(S) * G * NT * qstride;
+  return b;
+}
+
+// Launch shape of the quantised dense kernel: the largest row tile that fits, then as many warps
+// as fit (32 consumer warps at most), two trees in flight per warp and a three-stage tree ring.
+bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_t n_rows,
+                    int chunk_size, int sm_count, DenseCfg& cfg)
+{
+  int want = 256;
+  if (chunk_size > 0) {
+    want = std::min(256, std::max(32, 32 * chunk_size));
+  } else {
+    while (want > 32 && n_rows < static_cast<int64_t>(want) * sm_count) want /= 2;
+  }
+  if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S"
+    int R, G, NT, S;
+    if (sscanf(e, "%d,%d,%d,%d", &R, &G, &NT, &S) == 4 && R >= 32 && R % 32 == 0 && G >= 1 &&
+        (R / 32) * G <= 32 && (NT == 1 || NT == 2) && S >= 2 && S <= kMaxStages) {
+      const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S);
+      if (b <= kMaxSmemBytes) {
+        cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32};
+        return true;
+      }
+    }
+  }
+  for (int R = want; R >= 32; R /= 2) {
+    const int rw = R / 32;
+    for (int G = 32 / rw; G >= 1; G /= 2) {
+      for (int NT = 2; NT >= 1; --NT) {
+        for (int S = 3; S >= 2; --S) {
+          const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S);
+          if (b <= kMaxSmemBytes) {
+            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32};
+            return true;
+          }
+        }
+      }
+    }
+  }
+  return false;
+}
+
+template <typename T>
+int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const uint16_t* Q,
+                     const int32_t* flags, int grid, cudaStream_t stream, std::string& err)
+{
+  int rc;
+#define B2FIL_Q_CASE(M, N)                                                                  \
+  {                                                                                         \
+    auto k = dense_q_kernel<T, M, N>;                                                       \
+    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                       \
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups, \
+                                                 c.stages);                                 \
+  }
+  if (c.trees_in_flight == 2) {
+    switch (mode) {
+      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 2) break;
+      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 2) break;
+      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 2) break;
+      default: B2FIL_Q_CASE(MODE_LEAFID, 2) break;
+    }
+  } else {
+    switch (mode) {
+      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 1) break;
+      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 1) break;
+      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 1) break;
+      default: B2FIL_Q_CASE(MODE_LEAFID, 1) break;
+    }
+  }
+#undef B2FIL_Q_CASE
+  return B2FIL_OK;
+}
+
+// Rank-quantised prediction: rows are processed in chunks of whole waves of tiles; for each
+// chunk the pre-pass writes the ranks into stream-ordered scratch and the traversal kernel reads
+// them back (the chunk is sized to stay in L2).
+int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_count,
+                   cudaStream_t stream, cudaMemPool_t pool, std::string& err, int64_t* launches)
+{
+  const ForestView& f = p.f;
+  const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
+  const bool reduce   = mode <= MODE_VECTOR;
+  DenseCfg c;
+  if (!dense_q_config(f.dense_depth, precision, f.n_features, f.n_outputs, reduce, p.n_rows,
+                      chunk_size, sm_count, c)) {
+    err = "no quantised launch shape fits shared memory";
+    return B2FIL_ERR_UNSUPPORTED;
+  }
+  const int R            = c.rows_per_tile;
+  const size_t es        = precision == B2FIL_F32 ? 4 : 8;
+  const size_t tile_b    = static_cast<size_t>(f.n_features) * R * 2;
+  const int64_t wave     = static_cast<int64_t>(R) * sm_count;
+  const size_t target    = size_t(64) << 20;
+  const int64_t waves    = std::max<int64_t>(1, static_cast<int64_t>(target / (tile_b * sm_count)));
+  const int64_t chunk    = std::min<int64_t>(wave * waves, (p.n_rows + R - 1) / R * R);
+  const int64_t ch_tiles = (chunk + R - 1) / R;
+  const size_t q_bytes   = static_cast<size_t>(ch_tiles) * tile_b;
+  const size_t fl_bytes  = (static_cast<size_t>(ch_tiles) * 4 + 255) / 256 * 256;
+  unsigned char* scratch = nullptr;
+  cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), q_bytes + fl_bytes,
+                                          pool, stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    err = std::string("scratch allocation for quantised rows failed: ") + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? B2FIL_ERR_NO_MEMORY : B2FIL_ERR_CUDA;
+  }
+  uint16_t* Q    = reinterpret_cast<uint16_t*>(scratch);
+  int32_t* flags = reinterpret_cast<int32_t*>(scratch + q_bytes);
+  // shared memory of the pre-pass: feature records, the largest group's tables, staging buffer
+  uint32_t max_tab = 0;
+  {
+    // group table sizes live on the device; the packer bounds them by kQGroupSmemBudget
+    max_tab = kQGroupSmemBudget;
+  }
+  const size_t q_smem = kQMaxGroupFeatures * sizeof(QFeatS) + max_tab +
+                        static_cast<size_t>(kQMaxGroupFeatures) * (R + 2) * 2;
+  int rc = B2FIL_OK;
+  const size_t out_row_b =
+    (p.kind == B2FIL_INFER_LEAF_ID ? size_t(4) * f.n_trees
+     : p.kind == B2FIL_INFER_CLASS ? size_t(4)
+     : p.kind == B2FIL_INFER_PROBA2 ? 2 * es
+     : p.kind == B2FIL_INFER_PER_TREE
+       ? es * f.n_trees * (f.leaf_vector_len > 1 ? f.n_outputs : 1)
+       : es * f.n_outputs);
+  for (int64_t r0 = 0; r0 < p.n_rows && rc == B2FIL_OK; r0 += chunk) {
+    PredictParams pc = p;
+    pc.n_rows        = std::min<int64_t>(chunk, p.n_rows - r0);
+    pc.X             = static_cast<const unsigned char*>(p.X) + static_cast<size_t>(r0) * p.row_stride * es;
+    pc.out           = static_cast<unsigned char*>(p.out) + static_cast<size_t>(r0) * out_row_b;
+    const int64_t n_tiles = (pc.n_rows + R - 1) / R;
+    e = cudaMemsetAsync(flags, 0, static_cast<size_t>(n_tiles) * 4, stream);
+    if (e != cudaSuccess) {
+      err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e);
+      rc  = B2FIL_ERR_CUDA;
+      break;
+    }
+    const int gx = static_cast<int>(std::min<int64_t>(
+      n_tiles, std::max(1, (2 * sm_count + f.q_n_groups - 1) / f.q_n_groups)));
+    const dim3 qgrid(gx, f.q_n_groups);
+    const dim3 qblock(32, 16);
+    if (precision == B2FIL_F32) {
+      auto k = quantise_kernel<float>;
+      if ((rc = set_smem(k, q_smem, err)) != B2FIL_OK) break;
+      k<<<qgrid, qblock, q_smem, stream>>>(pc, Q, flags, R);
+    } else {
+      auto k = quantise_kernel<double>;
+      if ((rc = set_smem(k, q_smem, err)) != B2FIL_OK) break;
+      k<<<qgrid, qblock, q_smem, stream>>>(pc, Q, flags, R);
+    }
+    const int grid = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
+    rc = precision == B2FIL_F32 ? launch_dense_q_t<float>(pc, mode, c, Q, flags, grid, stream, err)
+                                : launch_dense_q_t<double>(pc, mode, c, Q, flags, grid, stream, err);
+    if (launches) *launches += 2;
+  }
+  cudaFreeAsync(scratch, stream);
+  return rc;
+}
+
 int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
 {
   if (chunk_size > 0) return std::min(128, std::max(32, 32 * chunk_size));
@@ -818,7 +1314,7 @@ bool dense_ok(int depth, int precision, int n_features, int n_outputs)
 }
 
 int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
-                   std::string& err, int64_t* launches)
+                   cudaMemPool_t pool, std::string& err, int64_t* launches)
 {
   const ForestView& f = p.f;
   if (p.n_rows == 0) return B2FIL_OK;
@@ -839,6 +1335,16 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
   }
   const bool reduce = mode <= MODE_VECTOR;
   int rc            = B2FIL_OK;
+  if ((f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled) {
+    rc = launch_dense_q(p, mode, chunk_size, sm_count, stream, pool, err, launches);
+    if (rc != B2FIL_OK) return rc;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      err = std::string("kernel launch: ") + cudaGetErrorString(e);
+      return B2FIL_ERR_CUDA;
+    }
+    return B2FIL_OK;
+  }
   if (f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) {
     const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
     DenseCfg c;

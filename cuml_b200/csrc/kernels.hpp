@@ -43,7 +43,8 @@ bool dense_ok(int depth, int precision, int n_features, int n_outputs);
 
 // Enqueue a prediction on `stream`.  Returns B2FIL_OK or an error code with `err` set.
 // `launches` (optional) is incremented by the number of kernels enqueued.
+// Forests with rank-quantised rows take stream-ordered scratch for the ranks from `pool`.
 int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
-                   std::string& err, int64_t* launches);
+                   cudaMemPool_t pool, std::string& err, int64_t* launches);
 
 }  // namespace b2fil

@@ -391,6 +391,131 @@ struct Packer {
     return B2FIL_OK;
   }
 
+  // ---- rank-quantised copy of a dense forest ----------------------------------------------------
+  // Returns false (and leaves the forest unquantised) when a limit is exceeded.
+  template <typename T>
+  bool build_quantised(int D)
+  {
+    const int F = d.n_features;
+    if (has_cat || F > static_cast<int>(Q_FEATURE_MASK) + 1) return false;
+    const int nt = d.n_trees;
+    // 1. distinct thresholds per feature, in the forest precision, after normalisation to `<`
+    std::vector<std::vector<T>> per(F);
+    for (int t = 0; t < nt; ++t) {
+      const int64_t base = d.tree_offsets[t];
+      const int64_t n    = d.tree_offsets[t + 1] - base;
+      for (int64_t r = 0; r < n; ++r) {
+        const int64_t g = base + r;
+        if (depth_of[g] < 0 || d.node_kind[g] != B2FIL_NODE_NUMERICAL) continue;
+        const T thr = static_cast<T>(normalise(d, g, precision).thr);
+        if (!std::isnan(thr)) per[d.feature[g]].push_back(thr);
+      }
+    }
+    size_t total_thr = 0, total_lut = 0;
+    out.q_feats.assign(F, QFeature{});
+    for (int f = 0; f < F; ++f) {
+      auto& v = per[f];
+      std::sort(v.begin(), v.end());
+      v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
+      if (v.size() > Q_MAX_RANK) return false;
+      QFeature& qf = out.q_feats[f];
+      qf.m         = static_cast<uint32_t>(v.size());
+      uint32_t nb  = 16;
+      while (nb < 2 * qf.m && nb < 4096) nb *= 2;
+      qf.n_buckets = qf.m == 0 ? 1 : nb;
+      // bucket grid over the finite thresholds
+      T scale = 0, offset = 0;
+      size_t lo = 0, hi = v.size();
+      while (lo < hi && !std::isfinite(v[lo])) ++lo;
+      while (hi > lo && !std::isfinite(v[hi - 1])) --hi;
+      if (hi - lo >= 2) {
+        const double range = static_cast<double>(v[hi - 1]) - static_cast<double>(v[lo]);
+        const T sc         = static_cast<T>(static_cast<double>(qf.n_buckets) / range);
+        const T of         = static_cast<T>(-static_cast<double>(v[lo]) * static_cast<double>(sc));
+        if (std::isfinite(sc) && std::isfinite(of) && sc > T(0)) {
+          scale  = sc;
+          offset = of;
+        }
+      }
+      qf.scale   = static_cast<double>(scale);
+      qf.offset  = static_cast<double>(offset);
+      qf.t_off   = static_cast<uint32_t>(total_thr);
+      qf.lut_off = static_cast<uint32_t>(total_lut);
+      total_thr += v.size();
+      total_lut += qf.n_buckets + 1;
+    }
+    out.q_thresholds.assign(total_thr * sizeof(T), 0);
+    out.q_lut.assign(total_lut, 0);
+    for (int f = 0; f < F; ++f) {
+      const QFeature& qf = out.q_feats[f];
+      const auto& v      = per[f];
+      std::vector<uint32_t> count(qf.n_buckets + 1, 0);
+      for (size_t i = 0; i < v.size(); ++i) {
+        put(out.q_thresholds, (qf.t_off + i) * sizeof(T), v[i]);
+        const uint32_t b = q_bucket_host<T>(v[i], static_cast<T>(qf.scale),
+                                            static_cast<T>(qf.offset), qf.n_buckets);
+        ++count[b + 1];  // lut[b'] counts thresholds in buckets below b'
+      }
+      uint32_t run = 0;
+      for (uint32_t b = 0; b <= qf.n_buckets; ++b) {
+        run += count[b];
+        out.q_lut[qf.lut_off + b] = static_cast<uint16_t>(run);
+      }
+    }
+    // 2. feature groups whose tables fit the quantisation kernel's shared memory
+    auto feat_bytes = [&](int f) {
+      const QFeature& qf = out.q_feats[f];
+      const uint32_t lut = ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
+      return lut + static_cast<uint32_t>((qf.m * sizeof(T) + 7) / 8 * 8);
+    };
+    out.q_groups.clear();
+    for (int f = 0; f < F;) {
+      QGroup g{static_cast<uint32_t>(f), static_cast<uint32_t>(f), 0, 0};
+      while (f < F && g.f_end - g.f_begin < kQMaxGroupFeatures &&
+             g.smem_bytes + feat_bytes(f) <= kQGroupSmemBudget) {
+        g.smem_bytes += feat_bytes(f);
+        ++g.f_end;
+        ++f;
+      }
+      if (g.f_end == g.f_begin) return false;  // one feature alone exceeds the budget
+      out.q_groups.push_back(g);
+    }
+    // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node
+    const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
+    const size_t es      = sizeof(T);
+    const int64_t width  = int64_t(1) << D;
+    int64_t qstride      = width * static_cast<int64_t>(4 + es);
+    qstride              = (qstride + 15) / 16 * 16;
+    out.q_nodes.assign(static_cast<size_t>(qstride) * nt, 0);
+    for (int p = 0; p < nt; ++p) {
+      const uint8_t* src = out.nodes.data() + static_cast<size_t>(out.view.tree_stride) * p;
+      uint8_t* dst       = out.q_nodes.data() + static_cast<size_t>(qstride) * p;
+      for (int64_t i = 1; i < width; ++i) {
+        T thr;
+        uint32_t meta;
+        std::memcpy(&thr, src + i * nb, sizeof(T));
+        std::memcpy(&meta, src + i * nb + sizeof(T), 4);
+        const uint32_t feat = meta & 0x3FFFFFFFu;
+        uint32_t j;
+        if (std::isnan(thr)) {
+          j = 0xFFFFu;  // x < NaN never holds: always right
+        } else {
+          const auto& v = per[feat];
+          const auto it = std::lower_bound(v.begin(), v.end(), thr);
+          // filler tests (both subtrees equal) need no real threshold
+          j = (it != v.end() && *it == thr) ? static_cast<uint32_t>(it - v.begin()) : 0u;
+        }
+        const uint32_t node = (j << 16) | ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | feat;
+        std::memcpy(dst + i * 4, &node, 4);
+      }
+      std::memcpy(dst + width * 4, src + width * nb, static_cast<size_t>(width) * es);
+    }
+    out.view.q_enabled     = 1;
+    out.view.q_n_groups    = static_cast<int32_t>(out.q_groups.size());
+    out.view.q_tree_stride = qstride;
+    return true;
+  }
+
   // ---- sparse ---------------------------------------------------------------------------------
   int pack_sparse()
   {
@@ -604,7 +729,22 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
               padded * 6.0 <= 8.0 * 1024 * 1024;
     }
   }
-  return dense ? pk.pack_dense(max_depth) : pk.pack_sparse();
+  if (!dense) return pk.pack_sparse();
+  rc = pk.pack_dense(max_depth);
+  if (rc != B2FIL_OK) return rc;
+  if (opts.row_quantization == 0) {
+    const bool ok = opts.precision == B2FIL_F32 ? pk.build_quantised<float>(max_depth)
+                                                : pk.build_quantised<double>(max_depth);
+    if (!ok) {
+      out.q_nodes.clear();
+      out.q_thresholds.clear();
+      out.q_lut.clear();
+      out.q_feats.clear();
+      out.q_groups.clear();
+      out.view.q_enabled = 0;
+    }
+  }
+  return B2FIL_OK;
 }
 
 }  // namespace b2fil

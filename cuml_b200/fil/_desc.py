@@ -75,6 +75,8 @@ class CCreateOpts(C.Structure):
         ("align_bytes", C.c_int32),
         ("device_id", C.c_int32),
         ("default_chunk_size", C.c_int32),
+        ("row_quantization", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -98,7 +100,7 @@ class CInfo(C.Structure):
         ("n_nodes_packed", C.c_int64),
         ("device_bytes", C.c_int64),
         ("default_chunk_size", C.c_int32),
-        ("reserved", C.c_int32),
+        ("row_quantization", C.c_int32),
     ]
 
 

@@ -40,10 +40,12 @@ class _Forest:
 
     @classmethod
     def create(cls, desc: ForestDesc, precision: int, layout: int, storage: int,
-               align_bytes: int, device_id: int, default_chunk_size: int) -> "_Forest":
+               align_bytes: int, device_id: int, default_chunk_size: int,
+               row_quantization: int = 0) -> "_Forest":
         lib = _lib.load()
         cd = desc.to_c()
-        opts = CCreateOpts(precision, layout, storage, align_bytes, device_id, default_chunk_size)
+        opts = CCreateOpts(precision, layout, storage, align_bytes, device_id, default_chunk_size,
+                           row_quantization, 0)
         out = C.c_void_p()
         _lib.check(lib.b2fil_forest_create(C.byref(cd), C.byref(opts), C.byref(out)))
         return cls(out.value)
@@ -81,6 +83,8 @@ class ForestInference:
     is_classifier : whether `predict` returns classes and `predict_proba` is available.
     storage : 'auto' | 'dense' | 'sparse' - 'dense' pads trees to complete binary trees with
         implicit child indexing; 'auto' chooses it for shallow forests.
+    quantize_rows : dense forests without categorical splits predict on 16-bit per-feature ranks
+        of the inputs (exact: rank(x) <= j  <=>  x < threshold_j); False keeps the raw values.
     device_id : CUDA device that holds the forest.
     output_type : 'input' (same kind of array as X), 'numpy' or 'torch'.
     """
@@ -88,7 +92,8 @@ class ForestInference:
     def __init__(self, *, treelite_model=None, handle=None, output_type: Optional[str] = None,
                  verbose=False, is_classifier: Optional[bool] = None, layout: str = "depth_first",
                  default_chunk_size: Optional[int] = None, align_bytes: Optional[int] = None,
-                 precision: str = "single", device_id: int = 0, storage: str = "auto"):
+                 precision: str = "single", device_id: int = 0, storage: str = "auto",
+                 quantize_rows: bool = True):
         if layout not in LAYOUTS:
             raise ValueError(f"layout must be one of {sorted(LAYOUTS)}, got {layout!r}")
         if precision not in _PRECISIONS:
@@ -104,6 +109,7 @@ class ForestInference:
         self.precision = precision
         self.device_id = int(device_id)
         self.storage = storage
+        self.quantize_rows = bool(quantize_rows)
         self.output_type = output_type or "input"
         self.verbose = verbose
         self.handle = handle
@@ -130,7 +136,8 @@ class ForestInference:
             prec = desc.native_precision
         self._forest = _Forest.create(
             desc, F32 if prec == "single" else F64, LAYOUTS[self.layout], STORAGES[self.storage],
-            int(self.align_bytes or 0), self.device_id, int(self.default_chunk_size or 0))
+            int(self.align_bytes or 0), self.device_id, int(self.default_chunk_size or 0),
+            0 if self.quantize_rows else 1)
 
     @classmethod
     def load_from_treelite_model(cls, tl_model, **kwargs) -> "ForestInference":

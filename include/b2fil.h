@@ -133,6 +133,9 @@ typedef struct b2fil_create_opts {
   int32_t align_bytes; /* 0 or a power of two: pad every tree of a sparse forest to this size    */
   int32_t device_id;   /* CUDA device ordinal that will hold the forest                          */
   int32_t default_chunk_size; /* 0 = choose; else the value predict uses when given chunk_size 0 */
+  int32_t row_quantization;   /* 0 = automatic: dense forests without categorical tests predict on
+                                 16-bit per-feature ranks of the inputs (exact); 1 = never        */
+  int32_t reserved;
 } b2fil_create_opts;
 
 typedef struct b2fil_info {
@@ -146,7 +149,7 @@ typedef struct b2fil_info {
   int64_t n_nodes_packed;  /* nodes stored on the device (with padding)                          */
   int64_t device_bytes;    /* device memory held by the forest                                   */
   int32_t default_chunk_size;
-  int32_t reserved;
+  int32_t row_quantization; /* 1: predictions run on rank-quantised rows                        */
 } b2fil_info;
 
 typedef struct b2fil_forest b2fil_forest; /* opaque */

@@ -160,7 +160,7 @@ def py_predict(desc: ForestDesc, X, precision="single"):
 
 
 def run_pack_check(pack_check, desc: ForestDesc, X, precision="single", layout="depth_first",
-                   storage="auto", align_bytes=0):
+                   storage="auto", align_bytes=0, row_quantization=0):
     """Pack `desc` with the product packer and walk the packed arrays on the host."""
     dt = np.float32 if precision == "single" else np.float64
     X = np.ascontiguousarray(X, dt)
@@ -170,7 +170,7 @@ def run_pack_check(pack_check, desc: ForestDesc, X, precision="single", layout="
     info = np.zeros(8, np.int64)
     cd = desc.to_c()
     opts = CCreateOpts(0 if precision == "single" else 1, LAYOUTS[layout], STORAGES[storage],
-                       align_bytes, 0, 0)
+                       align_bytes, 0, 0, row_quantization, 0)
     rc = pack_check.pack_check(C.byref(cd), C.byref(opts), X.ctypes.data, n, X.shape[1],
                                ids.ctypes.data, pay.ctypes.data, info.ctypes.data)
     return rc, ids, pay, info

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../cuml_b200/csrc/forest.hpp"
 
@@ -115,6 +116,52 @@ void walk(const PackedForest& pf, const T* X, int64_t n_rows, int64_t stride, ui
     }
   }
 }
+// Walk the rank-quantised copy of a dense forest the way quantise_kernel + dense_q_kernel do:
+// rank through the bucket table, then one signed subtraction per test.  Returns the number of
+// (row, tree) pairs whose leaf differs from `ids`.
+template <typename T>
+int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64_t stride,
+                       const uint32_t* ids)
+{
+  const ForestView& v = pf.view;
+  const int D         = v.dense_depth;
+  const int F         = v.n_features;
+  const T* thr        = reinterpret_cast<const T*>(pf.q_thresholds.data());
+  std::vector<uint16_t> q(F);
+  int64_t bad = 0;
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const T* row = X + r * stride;
+    for (int f = 0; f < F; ++f) {
+      const QFeature& qf = pf.q_feats[f];
+      const T x          = row[f];
+      if (x != x) {
+        q[f] = Q_NAN_CODE;
+        continue;
+      }
+      const uint32_t b = q_bucket_host<T>(x, static_cast<T>(qf.scale), static_cast<T>(qf.offset),
+                                          qf.n_buckets);
+      uint32_t lo = pf.q_lut[qf.lut_off + b], hi = pf.q_lut[qf.lut_off + b + 1];
+      while (lo < hi && !(x < thr[qf.t_off + lo])) ++lo;
+      q[f] = static_cast<uint16_t>(lo);
+    }
+    for (int p = 0; p < v.n_trees; ++p) {
+      const uint8_t* t = pf.q_nodes.data() + static_cast<size_t>(v.q_tree_stride) * p;
+      uint32_t i       = 1;
+      for (int l = 0; l < D; ++l) {
+        uint32_t node;
+        std::memcpy(&node, t + i * 4, 4);
+        const uint32_t qq = q[node & Q_FEATURE_MASK];
+        bool right = (static_cast<int32_t>(node) - static_cast<int32_t>(qq << 16)) < 0;
+        if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) == 0u;
+        i = 2 * i + (right ? 1 : 0);
+      }
+      const uint32_t slot = i - (1u << D);
+      const uint32_t id   = pf.leaf_ids[(static_cast<size_t>(p) << D) + slot];
+      if (id != ids[r * v.n_trees + pf.tree_orig[p]]) ++bad;
+    }
+  }
+  return bad;
+}
 }  // namespace
 
 extern "C" {
@@ -122,7 +169,8 @@ const char* pack_check_error() { return g_err.c_str(); }
 
 // Packs `desc` and walks n_rows rows.  ids: leaf id per (row, tree); payload: scalar leaf value
 // (or vector index) per (row, tree).  info[0..5] = format, storage, dense_depth, node_bytes,
-// n_nodes_packed, feat_bits.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
+// n_nodes_packed, feat_bits; info[6] = 1 when a rank-quantised copy was built, info[7] = number of
+// (row, tree) pairs where the walk over that copy reaches another leaf.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
 int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, const void* X,
                int64_t n_rows, int64_t stride, uint32_t* ids, double* payload, int64_t* info)
 {
@@ -135,11 +183,18 @@ int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, con
   info[3] = pf.node_bytes;
   info[4] = pf.n_nodes_packed;
   info[5] = pf.view.feat_bits;
+  info[6] = pf.view.q_enabled;
+  info[7] = 0;
   if (n_rows > 0) {
-    if (opts->precision == B2FIL_F32)
+    if (opts->precision == B2FIL_F32) {
       walk<float>(pf, static_cast<const float*>(X), n_rows, stride, ids, payload);
-    else
+      if (pf.view.q_enabled)
+        info[7] = walk_quantised<float>(pf, static_cast<const float*>(X), n_rows, stride, ids);
+    } else {
       walk<double>(pf, static_cast<const double*>(X), n_rows, stride, ids, payload);
+      if (pf.view.q_enabled)
+        info[7] = walk_quantised<double>(pf, static_cast<const double*>(X), n_rows, stride, ids);
+    }
   }
   return B2FIL_OK;
 }

@@ -32,10 +32,11 @@ def _dev(X, precision):
     return torch.as_tensor(np.ascontiguousarray(X), device="cuda:0").to(dt)
 
 
-def _all_kinds(desc, X, precision, layout, storage, chunk_size=None, host=False):
+def _all_kinds(desc, X, precision, layout, storage, chunk_size=None, host=False,
+               quantize_rows=True):
     """Run every output kind on the GPU and compare with the oracle."""
     fi = ForestInference.load_from_treelite_model(desc, precision=precision, layout=layout,
-                                                  storage=storage)
+                                                  storage=storage, quantize_rows=quantize_rows)
     Xo = np.ascontiguousarray(X, np.float32 if precision == "single" else np.float64)
     Xd = Xo if host else _dev(Xo, precision)
 
@@ -71,6 +72,40 @@ def test_random_forests_operators_nan(layout, storage, precision):
                               postproc="sigmoid")
     X = random_rows(2, 777, desc.n_features, np.float64, nan_frac=0.15, integer=True)
     _all_kinds(desc, X, precision, layout, storage)
+
+
+@pytest.mark.parametrize("precision", ["single", "double"])
+@pytest.mark.parametrize("quantize_rows", [True, False])
+def test_dense_with_and_without_row_quantisation(precision, quantize_rows):
+    # scalar leaves, multi-class scalar leaves and vector leaves through both dense kernels
+    for seed, kw in ((1, dict(postproc="sigmoid")), (2, dict(n_outputs=3, postproc="softmax")),
+                     (3, dict(n_outputs=4, vector=True, average=True))):
+        desc = random_forest_desc(seed, n_trees=21, max_depth=6, mixed_ops=True, **kw)
+        X = random_rows(seed, 900, desc.n_features, np.float64, nan_frac=0.1)
+        fi = _all_kinds(desc, X, precision, "depth_first", "dense", quantize_rows=quantize_rows)
+        assert fi.describe()["row_quantization"] == int(quantize_rows)
+
+
+def test_row_quantisation_edge_values():
+    # rows made of the thresholds themselves, their neighbours, infinities, signed zeros,
+    # denormals and NaN: ranks must reproduce every comparison exactly
+    for prec, dt in (("single", np.float32), ("double", np.float64)):
+        desc = random_forest_desc(21, n_trees=30, n_features=4, max_depth=6, mixed_ops=True)
+        thr = desc.threshold[desc.node_kind == 1].astype(dt)
+        vals = np.concatenate([thr, np.nextafter(thr, dt(np.inf)), np.nextafter(thr, dt(-np.inf)),
+                               np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-45, -1e-45,
+                                         np.finfo(dt).max, np.finfo(dt).min, np.finfo(dt).tiny],
+                                        dt)])
+        X = np.random.default_rng(5).choice(vals, size=(5000, 4)).astype(dt)
+        _all_kinds(desc, X, prec, "depth_first", "dense")
+
+
+def test_row_quantisation_nan_free_and_nan_tiles():
+    # a batch whose first tiles hold no NaN and whose last tiles do: both code paths in one launch
+    desc = random_forest_desc(23, n_trees=40, n_features=9, max_depth=7)
+    X = random_rows(6, 4000, desc.n_features, np.float32, nan_frac=0.0)
+    X[3000:] = random_rows(7, 1000, desc.n_features, np.float32, nan_frac=0.3)
+    _all_kinds(desc, X, "single", "depth_first", "dense")
 
 
 @pytest.mark.parametrize("layout,storage", CONFIGS)

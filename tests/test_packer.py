@@ -20,6 +20,11 @@ def _check(pack_check, desc, X, precision, layout, storage, align=0):
     assert rc == 0, pack_check.pack_check_error()
     want = oracle.predict(desc, X, INFER_LEAF_ID, precision)
     assert np.array_equal(ids, want)
+    # dense forests without categorical tests also carry a rank-quantised copy; the walk over it
+    # must reach exactly the same leaves
+    if info[1] == 1 and desc.cat_ptr is None:
+        assert info[6] == 1
+    assert info[7] == 0
     if desc.leaf_vector_len == 1:
         pt = oracle.predict(desc, X, INFER_PER_TREE, precision)
         assert np.array_equal(pay.astype(pt.dtype), pt)
@@ -151,8 +156,44 @@ def test_bad_options_are_rejected(pack_check):
     desc = _bad({})
     cd = desc.to_c()
     info = np.zeros(8, np.int64)
-    for opts in (CCreateOpts(5, 0, 0, 0, 0, 0), CCreateOpts(0, 9, 0, 0, 0, 0),
-                 CCreateOpts(0, 0, 7, 0, 0, 0), CCreateOpts(0, 0, 0, 48, 0, 0)):
+    for opts in (CCreateOpts(5, 0, 0, 0, 0, 0, 0, 0), CCreateOpts(0, 9, 0, 0, 0, 0, 0, 0),
+                 CCreateOpts(0, 0, 7, 0, 0, 0, 0, 0), CCreateOpts(0, 0, 0, 48, 0, 0, 0, 0)):
         rc = pack_check.pack_check(C.byref(cd), C.byref(opts), None, 0, 2, None, None,
                                    info.ctypes.data)
         assert rc == -1
+
+
+def test_rank_quantisation_edge_values(pack_check):
+    """Ranks are exact at thresholds, next to them, at infinities, zeros of both signs and
+    denormals, in both precisions; rows equal to a threshold are where `<` and `<=` differ."""
+    for prec, dt in (("single", np.float32), ("double", np.float64)):
+        desc = random_forest_desc(21, n_trees=30, n_features=4, max_depth=6, mixed_ops=True)
+        thr = desc.threshold[desc.node_kind == 1].astype(dt)
+        vals = np.concatenate([thr, np.nextafter(thr, dt(np.inf)), np.nextafter(thr, dt(-np.inf)),
+                               np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-45, -1e-45,
+                                         np.finfo(dt).max, np.finfo(dt).min, np.finfo(dt).tiny],
+                                        dt)])
+        rng = np.random.default_rng(5)
+        X = rng.choice(vals, size=(3000, 4)).astype(dt)
+        info = _check(pack_check, desc, X, prec, "depth_first", "dense")
+        assert info[6] == 1
+
+
+def test_rank_quantisation_off_and_limits(pack_check):
+    desc = random_forest_desc(22, n_trees=5, max_depth=4)
+    X = random_rows(1, 50, desc.n_features, np.float32)
+    rc, _, _, info = run_pack_check(pack_check, desc, X, storage="dense", row_quantization=1)
+    assert rc == 0 and info[6] == 0
+    # a feature with one huge threshold and one tiny one, duplicates, and an unused feature
+    from cuml_b200.fil._desc import ForestDesc, NODE_LEAF, NODE_NUMERICAL
+
+    desc = ForestDesc(n_features=3, n_outputs=1, tree_offsets=[0, 7],
+                      node_kind=[1, 1, 1, 0, 0, 0, 0], feature=[0, 0, 2, 0, 0, 0, 0],
+                      threshold=[1e30, 1e-30, 1e-30, 0, 0, 0, 0], left=[1, 3, 5, -1, -1, -1, -1],
+                      right=[2, 4, 6, -1, -1, -1, -1], default_left=[1, 0, 1, 0, 0, 0, 0],
+                      leaf_value=[0, 0, 0, 1.0, 2.0, 3.0, 4.0])
+    X = np.array([[1e30, 0, 1e-30], [9e29, 1, 0], [1e-30, 2, 1e-31], [np.nan, 3, np.nan],
+                  [-1, np.nan, 2e-30], [np.inf, 0, -np.inf]], np.float32)
+    for prec in ("single", "double"):
+        info = _check(pack_check, desc, X, prec, "depth_first", "dense")
+        assert info[6] == 1
