@@ -73,19 +73,36 @@ struct SparseNode16D {  // fp64
 // so a test is one signed subtraction: right <=> int(node) - (rank << 16) < 0.
 // The rank is found through a per-feature bucket table: bucket(x) = clamp(int(fma(x, scale,
 // offset)), 0, n_buckets-1) is monotone in x, lut[b] is the number of thresholds in buckets below
-// b, and only the thresholds of the value's own bucket are compared one by one.
-struct QFeature {
-  uint32_t t_off;      // first threshold of the feature in the threshold table
-  uint32_t lut_off;    // first entry of the feature's bucket table (n_buckets + 1 entries)
+// b (all of them are <= x), thresholds of higher buckets are all > x, so the rank is lut[b] plus
+// the number of thresholds <= x in a window of 2^steps - 1 entries starting at lut[b], found with
+// `steps` branch-free halvings (2^steps exceeds the fullest bucket; the array ends with NaN
+// padding, for which `T <= x` is false).
+struct QFeature {      // host-side table of one feature
+  uint32_t t_off;      // first threshold of the feature in PackedForest::q_thresholds
+  uint32_t lut_off;    // first entry of the feature's bucket table in PackedForest::q_lut
   uint32_t m;          // number of distinct thresholds
   uint32_t n_buckets;
+  uint32_t max_occupancy;  // thresholds in the fullest bucket
+  uint32_t pad;
   double scale;        // bucket(x) = fma(x, scale, offset) evaluated in the forest precision
   double offset;
 };
-struct QGroup {        // consecutive features whose tables share one CTA's shared memory
-  uint32_t f_begin, f_end;
-  uint32_t smem_bytes; // bytes of their tables
+// Device tables are grouped: consecutive features whose tables fit one CTA's shared memory form a
+// group, stored as one contiguous blob that the pre-pass pulls in with a single bulk copy:
+//   [kQMaxGroupFeatures x QFeatRec][per feature: bucket table (uint16), thresholds + NaN padding]
+struct QFeatRec {      // 32 bytes
+  uint32_t lut_off;    // byte offsets from the start of the blob
+  uint32_t thr_off;
+  uint32_t nbm1;       // n_buckets - 1
   uint32_t pad;
+  double scale, offset;
+};
+struct QGroup {        // 32 bytes
+  uint32_t f_begin, f_end;
+  uint32_t blob_off;   // byte offset of the group's blob in ForestView::q_blob (16-byte multiple)
+  uint32_t blob_bytes; // 16-byte multiple
+  uint32_t steps;      // halvings of the window search, shared by the group's features
+  uint32_t pad[3];
 };
 constexpr uint32_t Q_NAN_CODE     = 0x7FFFu;
 constexpr uint32_t Q_MAX_RANK     = 0x7FFEu;
@@ -131,9 +148,8 @@ struct ForestView {
   int32_t q_n_groups;
   int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size), 16-byte multiple
   const void* q_nodes;          // [n_trees] blocks of [2^D nodes uint32][2^D leaf payloads]
-  const void* q_thresholds;     // sorted distinct thresholds of all features, forest precision
-  const uint16_t* q_lut;        // bucket tables of all features
-  const QFeature* q_feats;      // [n_features]
+  int64_t q_max_blob_bytes;     // largest group blob
+  const unsigned char* q_blob;  // group blobs
   const QGroup* q_groups;       // [q_n_groups]
 };
 
@@ -160,6 +176,7 @@ struct PackedForest {
   std::vector<uint16_t> q_lut;
   std::vector<QFeature> q_feats;
   std::vector<QGroup> q_groups;
+  std::vector<uint8_t> q_blob;
 };
 
 // Bucket of a value in a feature's table; the same expression runs on the device
@@ -174,7 +191,7 @@ inline uint32_t q_bucket_host(T x, T scale, T offset, uint32_t n_buckets)
 }
 
 // Shared memory the quantisation kernel may spend on the tables of one feature group.
-constexpr uint32_t kQGroupSmemBudget = 160 * 1024;
+constexpr uint32_t kQGroupSmemBudget = 200 * 1024;
 constexpr uint32_t kQMaxGroupFeatures = 32;
 
 // Validate `desc`, normalise its tests and lay its nodes out.  Returns B2FIL_OK or an error code

@@ -26,15 +26,16 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "kernels.hpp"
 
 namespace b2fil {
 namespace {
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // tries of a bounded mbarrier wait
-constexpr int kBarBytes       = 128;       // room for the mbarriers at the start of shared memory
-constexpr int kMaxStages      = 4;
+constexpr uint32_t kSpinLimit = 1u << 22;  // tries of a bounded mbarrier wait
+constexpr int kBarBytes       = 256;       // room for the mbarriers at the start of shared memory
+constexpr int kMaxStages      = 8;
 
 // ---------------------------------------------------------------------------------------------
 // shared-memory and mbarrier primitives (inline PTX)
@@ -74,7 +75,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the barrier did not complete within kSpinLimit tries.
+// Bounded wait: false when the barrier did not complete within kSpinLimit tries (each try blocks
+// for a hardware-defined short time).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
@@ -565,117 +567,189 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
 // ---------------------------------------------------------------------------------------------
 // RANK QUANTISATION of rows (pre-pass of the quantised dense kernel)
 // ---------------------------------------------------------------------------------------------
-// One CTA owns one feature group (its bucket tables and sorted thresholds sit in shared memory)
-// and loops over row tiles.  Thread (x = feature of the group, y = row stripe) reads one value,
-// finds its rank and parks it in a transposed staging buffer; the buffer is then written out as
-// Q[tile][feature][row in tile] (uint16), the layout the traversal kernel pulls into shared
-// memory with a single bulk copy.  A NaN becomes Q_NAN_CODE and raises the tile's flag.
-struct QFeatS {       // per-feature record in shared memory
-  uint32_t lut;       // shared-memory address of the bucket table
-  uint32_t thr;       // shared-memory address of the sorted thresholds
-  uint32_t nbm1;      // n_buckets - 1
-  uint32_t pad;
-  double scale, offset;
-};
+// One CTA owns one feature group: the group's blob (feature records, bucket tables, sorted
+// thresholds) arrives in shared memory with one bulk copy, then the CTA loops over row tiles.
+// The group size GF is a power of two that divides the thread count, so a thread keeps one
+// feature for good (its record sits in registers) and owns up to U rows of every tile; the
+// loads of the next tile are issued before the current tile is ranked.  Ranks are parked in a
+// transposed staging buffer and written out as Q[tile][feature][row in tile] (uint16): the layout
+// the traversal kernel pulls into shared memory with a single bulk copy.  NaN becomes Q_NAN_CODE
+// and raises the tile's flag.
+// Shared memory: [mbarrier 16 B][blob][staging buffer GF x (R + 2) uint16].
+__device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
+{
+  asm volatile(
+    "{\n"
+    ".reg .u16 h;\n"
+    "cvt.u16.u32 h, %1;\n"
+    "st.shared.u16 [%0], h;\n"
+    "}\n" ::"r"(a),
+    "r"(v)
+    : "memory");
+}
+
+// Rank of one value: bucket table lookup plus STEPS branch-free halvings over the window that
+// starts at the bucket's first threshold (thresholds of lower buckets are all <= x, those of
+// higher buckets all > x, NaN padding compares false).  A NaN input walks the same code (it
+// lands in bucket 0 and every comparison fails) and is replaced by Q_NAN_CODE by the caller.
+template <typename T, int STEPS>
+__device__ __forceinline__ uint32_t rank_of(T x, T scale, T offset, T nbm1, uint32_t lut,
+                                            uint32_t thr_m1, int steps_rt)
+{
+  using TR = Traits<T>;
+  // same expression as q_bucket_host: fma, clamp (NaN becomes 0), truncate
+  T v = fma(x, scale, offset);
+  v   = fmax(v, T(0));
+  v   = fmin(v, nbm1);
+  const uint32_t b = static_cast<uint32_t>(v);
+  uint32_t pos_b   = lds_u16(lut + b * 2u) * TR::ES;  // byte offset of the window's first entry
+  if (STEPS >= 0) {
+#pragma unroll
+    for (int k = STEPS - 1; k >= 0; --k) {
+      const uint32_t s_b = (1u << k) * TR::ES;
+      pos_b += (TR::ld_real(thr_m1 + pos_b + s_b) <= x) ? s_b : 0u;  // entry pos + 2^k - 1
+    }
+  } else {  // very full buckets: the number of halvings is only known at run time
+    for (int k = steps_rt - 1; k >= 0; --k) {
+      const uint32_t s_b = (1u << k) * TR::ES;
+      pos_b += (TR::ld_real(thr_m1 + pos_b + s_b) <= x) ? s_b : 0u;
+    }
+  }
+  return pos_b / TR::ES;
+}
+
+// NU = rows of a tile each thread owns (R * GF / threads, at least 1).
+template <typename T, int STEPS, int NU>
+__device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGroup& grp,
+                                               uint16_t* __restrict__ Q,
+                                               int32_t* __restrict__ tile_flags, int R,
+                                               uint32_t blob_a, const QFeatRec* rec,
+                                               uint32_t qbuf_a)
+{
+  using TR              = Traits<T>;
+  const int GF          = grp.f_end - grp.f_begin;
+  const int F           = p.f.n_features;
+  const int tid         = threadIdx.x;
+  const int nthreads    = blockDim.x;
+  const int i           = tid & (GF - 1);
+  const int gshift      = 31 - __clz(GF);
+  const int r_first     = tid >> gshift;
+  const int r_step      = nthreads >> gshift;
+  const bool active     = r_first < R;  // false only when a tile has fewer values than threads
+  const QFeatRec mine   = rec[i];
+  const T scale         = static_cast<T>(mine.scale);
+  const T offset        = static_cast<T>(mine.offset);
+  const T nbm1          = static_cast<T>(mine.nbm1);
+  const uint32_t lut    = blob_a + mine.lut_off;
+  const uint32_t thr_m1 = blob_a + mine.thr_off - TR::ES;
+  const int qstride     = R + 2;  // uint16 elements between features in the staging buffer
+  const uint32_t q_mine = qbuf_a + (i * qstride + r_first) * 2u;
+  const uint32_t q_step = r_step * 2u;
+  const int64_t n_tiles = (p.n_rows + R - 1) / R;
+  // element offsets inside a tile fit 32 bits (the host sizes row chunks accordingly)
+  const uint32_t e_mine = static_cast<uint32_t>(r_first * p.row_stride + grp.f_begin + i);
+  const uint32_t e_step = static_cast<uint32_t>(r_step * p.row_stride);
+  const T* X            = static_cast<const T*>(p.X);
+  const int hshift      = 30 - __clz(R);  // log2(R / 2)
+  const int half        = R >> 1;
+
+  T xs[NU];
+  auto fetch = [&](int64_t t) {
+    const int64_t row0 = t * R;
+    const T* tb        = X + row0 * p.row_stride;  // same for the whole CTA
+    if (row0 + R <= p.n_rows) {
+#pragma unroll
+      for (int u = 0; u < NU; ++u) xs[u] = active ? __ldg(tb + (e_mine + u * e_step)) : T(0);
+    } else {
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+        const int64_t row = row0 + r_first + u * r_step;
+        xs[u] = (active && row < p.n_rows) ? __ldg(tb + (e_mine + u * e_step)) : T(0);
+      }
+    }
+  };
+  if (blockIdx.x < n_tiles) fetch(blockIdx.x);
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    T cur[NU];
+#pragma unroll
+    for (int u = 0; u < NU; ++u) cur[u] = xs[u];
+    // the loads of the next tile fly while this tile is ranked and written out
+    if (t + gridDim.x < n_tiles) fetch(t + gridDim.x);
+    bool saw_nan = false;
+    if (active) {
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
+        const T x          = cur[u];
+        const uint32_t rk  = rank_of<T, STEPS>(x, scale, offset, nbm1, lut, thr_m1, grp.steps);
+        const bool is_nan  = x != x;
+        saw_nan |= is_nan;
+        sts_u16(q_mine + u * q_step, is_nan ? Q_NAN_CODE : rk);
+      }
+    }
+    if (__any_sync(0xffffffffu, saw_nan) && (tid & 31) == 0) atomicOr(tile_flags + t, 1);
+    __syncthreads();
+    // staging buffer -> Q[tile][feature][row], two rows per 32-bit store
+    uint32_t* out32 =
+      reinterpret_cast<uint32_t*>(Q) + (t * F + grp.f_begin) * static_cast<int64_t>(half);
+    for (int e = tid; e < (GF << hshift); e += nthreads) {
+      const int fi = e >> hshift;
+      const int c  = e & (half - 1);
+      out32[e]     = lds_u32(qbuf_a + (fi * (half + 1) + c) * 4u);
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int STEPS>
+__device__ __forceinline__ void quantise_rows(const PredictParams& p, const QGroup& grp,
+                                              uint16_t* __restrict__ Q,
+                                              int32_t* __restrict__ tile_flags, int R,
+                                              uint32_t blob_a, const QFeatRec* rec,
+                                              uint32_t qbuf_a)
+{
+  const int per_thread = (R * static_cast<int>(grp.f_end - grp.f_begin)) / static_cast<int>(blockDim.x);
+  switch (per_thread) {
+    case 8: quantise_tiles<T, STEPS, 8>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 4: quantise_tiles<T, STEPS, 4>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 2: quantise_tiles<T, STEPS, 2>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    default: quantise_tiles<T, STEPS, 1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+  }
+}
 
 template <typename T>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(1024, 1)
 quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __restrict__ tile_flags,
                 const int R)
 {
-  using TR = Traits<T>;
   extern __shared__ __align__(128) unsigned char smem[];
-  const ForestView& f = p.f;
-  const QGroup grp    = f.q_groups[blockIdx.y];
-  const int GF        = grp.f_end - grp.f_begin;
-  const int F         = f.n_features;
-  const int tid       = threadIdx.y * 32 + threadIdx.x;
-  const int nthreads  = blockDim.y * 32;
-  QFeatS* fs          = reinterpret_cast<QFeatS*>(smem);
-  unsigned char* tab  = smem + kQMaxGroupFeatures * sizeof(QFeatS);
-  const int qstride   = R + 2;  // uint16 elements between features in the staging buffer
-  uint16_t* qbuf      = reinterpret_cast<uint16_t*>(tab + grp.smem_bytes);
-  const T* thr_all    = static_cast<const T*>(f.q_thresholds);
+  const ForestView& f   = p.f;
+  const QGroup grp      = f.q_groups[blockIdx.y];
+  const uint32_t bar    = smem_addr(smem);
+  unsigned char* blob   = smem + 16;
+  const uint32_t blob_a = smem_addr(blob);
+  const uint32_t qbuf_a = blob_a + grp.blob_bytes;
+  const QFeatRec* rec   = reinterpret_cast<const QFeatRec*>(blob);
 
-  // tables of the group -> shared memory
-  if (tid == 0) {
-    uint32_t off = 0;
-    for (int i = 0; i < GF; ++i) {
-      const QFeature qf = f.q_feats[grp.f_begin + i];
-      fs[i].lut         = smem_addr(tab + off);
-      off += ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
-      fs[i].thr = smem_addr(tab + off);
-      off += (qf.m * sizeof(T) + 7) / 8 * 8;
-      fs[i].nbm1   = qf.n_buckets - 1;
-      fs[i].scale  = qf.scale;
-      fs[i].offset = qf.offset;
-    }
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    mbar_expect_tx(bar, grp.blob_bytes);
+    bulk_copy_g2s(blob_a, f.q_blob + grp.blob_off, grp.blob_bytes, bar);
   }
   __syncthreads();
-  for (int i = 0; i < GF; ++i) {
-    const QFeature qf  = f.q_feats[grp.f_begin + i];
-    uint16_t* lut_s    = reinterpret_cast<uint16_t*>(smem + (fs[i].lut - smem_addr(smem)));
-    T* thr_s           = reinterpret_cast<T*>(smem + (fs[i].thr - smem_addr(smem)));
-    for (uint32_t k = tid; k <= qf.n_buckets; k += nthreads) lut_s[k] = f.q_lut[qf.lut_off + k];
-    for (uint32_t k = tid; k < qf.m; k += nthreads) thr_s[k] = thr_all[qf.t_off + k];
+  if (!mbar_wait(bar, 0)) {
+    if (threadIdx.x == 0) atomicExch(p.status, 4);
+    return;
   }
-  __syncthreads();
-
-  const int i           = threadIdx.x;
-  const bool live_lane  = i < GF;
-  const QFeatS my       = fs[live_lane ? i : 0];
-  const T scale         = static_cast<T>(my.scale);
-  const T offset        = static_cast<T>(my.offset);
-  const T nbm1          = static_cast<T>(my.nbm1);
-  const T* X            = static_cast<const T*>(p.X);
-  const int64_t n_tiles = (p.n_rows + R - 1) / R;
-  const int half        = R / 2;
-  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-    const int64_t row0 = t * R;
-    bool saw_nan       = false;
-    if (live_lane) {
-      for (int r = threadIdx.y; r < R; r += blockDim.y) {
-        const int64_t row = row0 + r;
-        uint32_t code     = 0;
-        if (row < p.n_rows) {
-          const T x = __ldg(X + row * p.row_stride + grp.f_begin + i);
-          if (x != x) {
-            code    = Q_NAN_CODE;
-            saw_nan = true;
-          } else {
-            // same expression as q_bucket_host: fma, clamp (NaN from inf * 0 becomes 0), truncate
-            T v = fma(x, scale, offset);
-            v   = fmax(v, T(0));
-            v   = fmin(v, nbm1);
-            const uint32_t b = static_cast<uint32_t>(v);
-            const uint32_t w = lds_u32(my.lut + (b & ~1u) * 2u);
-            uint32_t lo, hi;
-            if (b & 1u) {
-              lo = w >> 16;
-              hi = lds_u16(my.lut + (b + 1u) * 2u);
-            } else {
-              lo = w & 0xFFFFu;
-              hi = w >> 16;
-            }
-            // thresholds of lower buckets are all <= x, those of higher buckets all > x
-            while (lo < hi && !(x < TR::ld_real(my.thr + lo * TR::ES))) ++lo;
-            code = lo;
-          }
-        }
-        qbuf[i * qstride + r] = static_cast<uint16_t>(code);
-      }
-    }
-    if (__any_sync(0xffffffffu, saw_nan) && threadIdx.x == 0) atomicOr(tile_flags + t, 1);
-    __syncthreads();
-    // staging buffer -> Q[tile][feature][row], two rows per 32-bit store
-    const uint32_t* qbuf32 = reinterpret_cast<const uint32_t*>(qbuf);
-    uint32_t* out32 = reinterpret_cast<uint32_t*>(Q) + (t * F + grp.f_begin) * static_cast<int64_t>(half);
-    for (int e = tid; e < GF * half; e += nthreads) {
-      const int fi = e / half;
-      const int c  = e - fi * half;
-      out32[static_cast<int64_t>(fi) * half + c] = qbuf32[fi * (half + 1) + c];
-    }
-    __syncthreads();
+  // the number of halvings is fixed per group: pick the unrolled body once
+  switch (grp.steps) {
+    case 0: quantise_rows<T, 0>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 1: quantise_rows<T, 1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 2: quantise_rows<T, 2>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 3: quantise_rows<T, 3>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 4: quantise_rows<T, 4>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 5: quantise_rows<T, 5>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    default: quantise_rows<T, -1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
   }
 }
 
@@ -689,55 +763,84 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
 constexpr int kBarTileFull  = 2 * kMaxStages;      // mbarrier slots after the stage ring
 constexpr int kBarTileEmpty = 2 * kMaxStages + 1;
 
-template <typename T, int MODE, int NT>
+// q * (-65536) + node in one multiply-add: the sign of (j - rank) lands in bit 31.
+__device__ __forceinline__ uint32_t rank_diff(uint32_t node, uint32_t q)
+{
+  uint32_t d;
+  asm("mad.lo.u32 %0, %1, 0xFFFF0000, %2;" : "=r"(d) : "r"(q), "r"(node));
+  return d;
+}
+
+// DEPTH > 0 fixes the tree depth at compile time (the level loop is fully unrolled); DEPTH == 0
+// reads it from the forest.
+template <typename T, int MODE, int NT, int DEPTH>
 struct DenseQWalker {
   using TR = Traits<T>;
+  // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
+  // trees; the warp waits once per stage and walks its NT trees of every sub-batch.
   template <bool NANS>
-  static __device__ __forceinline__ bool walk(const PredictParams& p, int G, int S, int g, int r,
-                                              int64_t row, int lane, uint32_t bars,
+  static __device__ __forceinline__ bool walk(const PredictParams& p, int G, int S, int K, int g,
+                                              int r, int64_t row, int lane, uint32_t bars,
                                               uint32_t stages, uint32_t stage_bytes,
                                               uint32_t row_addr, uint32_t stride_b, T* acc_group,
                                               int R, uint32_t& it, Running<T>& run)
   {
     const ForestView& f    = p.f;
-    const int D            = f.dense_depth;
+    const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
     const uint32_t width_b = (1u << D) * 4u;
-    const int per_batch    = G * NT;
+    const int per_sub      = G * NT;
+    const int per_batch    = per_sub * K;
     const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
     bool ok                = true;
     for (int b = 0; b < n_batches; ++b, ++it) {
       const uint32_t s = it % S;
       if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
       if (ok) {
-        const int first = b * per_batch + g * NT;
-        const int n_act = min(NT, f.n_trees - first);
-        if (n_act > 0) {
-          uint32_t base[NT], a[NT];
+        const uint32_t stage = stages + s * stage_bytes;
+        for (int kk = 0; kk < K; ++kk) {
+          const int slot0 = kk * per_sub + g * NT;  // first tree of this warp inside the stage
+          const int first = b * per_batch + slot0;
+          const int n_act = min(NT, f.n_trees - first);
+          if (n_act <= 0) break;
+          uint32_t nbase[NT], a[NT];
 #pragma unroll
           for (int k = 0; k < NT; ++k) {
-            const int slot = g * NT + min(k, n_act - 1);
-            base[k]        = stages + s * stage_bytes + slot * tstride;
-            a[k]           = base[k] + 4u;  // heap index 1
+            // slots past the end of the forest repeat the last live tree; results are dropped
+            const uint32_t base = stage + (slot0 + min(k, n_act - 1)) * tstride;
+            nbase[k]            = 0u - base;
+            a[k]                = base + 4u;  // heap index 1
           }
-          for (int lvl = 0; lvl < D; ++lvl) {
+          auto level = [&]() {
 #pragma unroll
             for (int k = 0; k < NT; ++k) {
               const uint32_t node = lds_u32(a[k]);
               const uint32_t q    = lds_u16((node & Q_FEATURE_MASK) * stride_b + row_addr);
-              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
-              bool right = (static_cast<int32_t>(node) - static_cast<int32_t>(q << 16)) < 0;
+              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0;
+              // the sign bit of the difference is the step to the right child
+              uint32_t right = rank_diff(node, q) >> 31;
               if (NANS) {
-                if (q == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) == 0u;
+                if (q == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) ? 0u : 1u;
               }
-              a[k] = 2u * a[k] - base[k] + (right ? 4u : 0u);
+              // address of heap node 2i + right from the address of node i
+              a[k] = (a[k] << 1) + ((right << 2) + nbase[k]);
             }
+          };
+          if (DEPTH > 0) {
+#pragma unroll
+            for (int lvl = 0; lvl < DEPTH; ++lvl) level();
+          } else {
+#pragma unroll 4
+            for (int lvl = 0; lvl < D; ++lvl) level();
           }
 #pragma unroll
           for (int k = 0; k < NT; ++k) {
             if (k < n_act) {
-              const uint32_t slot = (a[k] - base[k]) / 4u - (1u << D);
-              const typename TR::Val payload = TR::ld_val(base[k] + width_b + slot * TR::ES);
+              // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
+              // address of leaf slot j is exactly the address the walk ended on
+              const uint32_t leaf_a = TR::ES == 4 ? a[k] : 2u * a[k] + nbase[k] - width_b;
+              const typename TR::Val payload = TR::ld_val(leaf_a);
+              const uint32_t slot = ((a[k] + nbase[k]) >> 2) - (1u << D);
               take_leaf<T, MODE>(p, first + k, payload,
                                  (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
                                  row, run);
@@ -752,10 +855,11 @@ struct DenseQWalker {
   }
 };
 
-template <typename T, int MODE, int NT>
-__global__ void __launch_bounds__(1056, 1)
+template <typename T, int MODE, int NT, int DEPTH>
+__global__ void __launch_bounds__(1024, 1)
 dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
-               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S)
+               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
+               const int K)
 {
   using TR = Traits<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -778,7 +882,7 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
   const uint32_t tile        = smem_addr(tile_ptr);
   const uint32_t stages      = smem_addr(stage_ptr);
   const uint32_t tstride     = static_cast<uint32_t>(f.q_tree_stride);
-  const int per_batch        = G * NT;
+  const int per_batch        = G * NT * K;
   const uint32_t stage_bytes = per_batch * tstride;
   const int n_batches        = (f.n_trees + per_batch - 1) / per_batch;
   const int64_t n_tiles      = (p.n_rows + R - 1) / R;
@@ -849,13 +953,13 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
     Running<T> run{T(0), 0};
     if (ok) {
       if (nans) {
-        ok = DenseQWalker<T, MODE, NT>::template walk<true>(
-          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run);
+        ok = DenseQWalker<T, MODE, NT, DEPTH>::template walk<true>(
+          p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
+          acc_group, R, it, run);
       } else {
-        ok = DenseQWalker<T, MODE, NT>::template walk<false>(
-          p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run);
+        ok = DenseQWalker<T, MODE, NT, DEPTH>::template walk<false>(
+          p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
+          acc_group, R, it, run);
       }
       if (!ok) atomicExch(p.status, 2);
     }
@@ -1107,7 +1211,8 @@ int launch_sparse_fmt(const PredictParams& p, int mode, int R, int G, int rows_i
   return B2FIL_OK;
 }
 
-size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R, int G, int NT, int S)
+size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R, int G, int NT, int S,
+                    int K)
 {
   const size_t es      = precision == B2FIL_F32 ? 4 : 8;
   const size_t qstride = align16((size_t(1) << depth) * (4 + es));
@@ -1115,7 +1220,7 @@ size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R,
   b += static_cast<size_t>(F) * R * 2;
   if (reduce) b += align16(static_cast<size_t>(G) * NC * R * es);
   b += 16;
-  b += static_cast<size_t>(S) * G * NT * qstride;
+  b += static_cast<size_t>(S) * G * NT * K * qstride;
   return b;
 }
 
@@ -1130,26 +1235,32 @@ bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_
   } else {
     while (want > 32 && n_rows < static_cast<int64_t>(want) * sm_count) want /= 2;
   }
-  if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S"
-    int R, G, NT, S;
-    if (sscanf(e, "%d,%d,%d,%d", &R, &G, &NT, &S) == 4 && R >= 32 && R % 32 == 0 && G >= 1 &&
-        (R / 32) * G <= 32 && (NT == 1 || NT == 2) && S >= 2 && S <= kMaxStages) {
-      const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S);
+  if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S,K"
+    int R, G, NT, S, K;
+    if (sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5 && R >= 32 && R % 32 == 0 &&
+        G >= 1 && (R / 32) * G <= 31 && (NT == 1 || NT == 2) && S >= 2 && S <= kMaxStages &&
+        K >= 1) {
+      const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
-        cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32};
+        cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32, K};
         return true;
       }
     }
   }
   for (int R = want; R >= 32; R /= 2) {
     const int rw = R / 32;
-    for (int G = 32 / rw; G >= 1; G /= 2) {
+    // a CTA holds at most 32 warps and one of them is the producer
+    for (int G = std::min(8, 31 / rw); G >= 1; --G) {
       for (int NT = 2; NT >= 1; --NT) {
-        for (int S = 3; S >= 2; --S) {
-          const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S);
-          if (b <= kMaxSmemBytes) {
-            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32};
-            return true;
+        // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees;
+        // the ring must also cover the bytes in flight over the latency of a bulk copy
+        for (int K = 4; K >= 1; K /= 2) {
+          for (int S = 3; S >= 2; --S) {
+            const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
+            if (b <= kMaxSmemBytes) {
+              cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, K};
+              return true;
+            }
           }
         }
       }
@@ -1163,26 +1274,41 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
                      const int32_t* flags, int grid, cudaStream_t stream, std::string& err)
 {
   int rc;
-#define B2FIL_Q_CASE(M, N)                                                                  \
+#define B2FIL_Q_CASE(M, N, DD)                                                              \
   {                                                                                         \
-    auto k = dense_q_kernel<T, M, N>;                                                       \
+    auto k = dense_q_kernel<T, M, N, DD>;                                                   \
     if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                       \
     k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups, \
-                                                 c.stages);                                 \
+                                                 c.stages, c.sub_batches);                  \
   }
   if (c.trees_in_flight == 2) {
+    // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies
+    if constexpr (std::is_same<T, float>::value) {
+     if (mode == MODE_SCALAR) {
+      switch (p.f.dense_depth) {
+        case 4: B2FIL_Q_CASE(MODE_SCALAR, 2, 4) return B2FIL_OK;
+        case 5: B2FIL_Q_CASE(MODE_SCALAR, 2, 5) return B2FIL_OK;
+        case 6: B2FIL_Q_CASE(MODE_SCALAR, 2, 6) return B2FIL_OK;
+        case 7: B2FIL_Q_CASE(MODE_SCALAR, 2, 7) return B2FIL_OK;
+        case 8: B2FIL_Q_CASE(MODE_SCALAR, 2, 8) return B2FIL_OK;
+        case 9: B2FIL_Q_CASE(MODE_SCALAR, 2, 9) return B2FIL_OK;
+        case 10: B2FIL_Q_CASE(MODE_SCALAR, 2, 10) return B2FIL_OK;
+        default: break;
+      }
+     }
+    }
     switch (mode) {
-      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 2) break;
-      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 2) break;
-      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 2) break;
-      default: B2FIL_Q_CASE(MODE_LEAFID, 2) break;
+      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 2, 0) break;
+      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 2, 0) break;
+      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 2, 0) break;
+      default: B2FIL_Q_CASE(MODE_LEAFID, 2, 0) break;
     }
   } else {
     switch (mode) {
-      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 1) break;
-      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 1) break;
-      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 1) break;
-      default: B2FIL_Q_CASE(MODE_LEAFID, 1) break;
+      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 1, 0) break;
+      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 1, 0) break;
+      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 1, 0) break;
+      default: B2FIL_Q_CASE(MODE_LEAFID, 1, 0) break;
     }
   }
 #undef B2FIL_Q_CASE
@@ -1224,13 +1350,8 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   }
   uint16_t* Q    = reinterpret_cast<uint16_t*>(scratch);
   int32_t* flags = reinterpret_cast<int32_t*>(scratch + q_bytes);
-  // shared memory of the pre-pass: feature records, the largest group's tables, staging buffer
-  uint32_t max_tab = 0;
-  {
-    // group table sizes live on the device; the packer bounds them by kQGroupSmemBudget
-    max_tab = kQGroupSmemBudget;
-  }
-  const size_t q_smem = kQMaxGroupFeatures * sizeof(QFeatS) + max_tab +
+  // shared memory of the pre-pass: mbarrier, the largest group blob, staging buffer
+  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes) +
                         static_cast<size_t>(kQMaxGroupFeatures) * (R + 2) * 2;
   int rc = B2FIL_OK;
   const size_t out_row_b =
@@ -1255,7 +1376,7 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
     const int gx = static_cast<int>(std::min<int64_t>(
       n_tiles, std::max(1, (2 * sm_count + f.q_n_groups - 1) / f.q_n_groups)));
     const dim3 qgrid(gx, f.q_n_groups);
-    const dim3 qblock(32, 16);
+    const dim3 qblock(1024);
     if (precision == B2FIL_F32) {
       auto k = quantise_kernel<float>;
       if ((rc = set_smem(k, q_smem, err)) != B2FIL_OK) break;
@@ -1297,7 +1418,7 @@ bool dense_config(int depth, int precision, int n_features, int n_outputs, bool 
           const size_t b =
             dense_smem(depth, precision, n_features, n_outputs, reduce_kind, R, G, NT, S);
           if (b <= kMaxSmemBytes) {
-            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32};
+            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, 1};
             return true;
           }
         }
@@ -1335,7 +1456,9 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
   }
   const bool reduce = mode <= MODE_VECTOR;
   int rc            = B2FIL_OK;
-  if ((f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled) {
+  // the pre-pass indexes a row tile with 32-bit element offsets
+  if ((f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled &&
+      p.row_stride < (int64_t(1) << 22)) {
     rc = launch_dense_q(p, mode, chunk_size, sm_count, stream, pool, err, launches);
     if (rc != B2FIL_OK) return rc;
     const cudaError_t e = cudaGetLastError();

@@ -29,6 +29,7 @@ struct DenseCfg {
   int stages;          // S: depth of the tree pipeline
   size_t smem_bytes;
   int threads;
+  int sub_batches;     // K: sub-batches of G * NT trees per stage (quantised kernel)
 };
 
 // Largest dynamic shared memory a CTA may use on sm_100 (227 KiB).

@@ -456,29 +456,80 @@ struct Packer {
                                             static_cast<T>(qf.offset), qf.n_buckets);
         ++count[b + 1];  // lut[b'] counts thresholds in buckets below b'
       }
-      uint32_t run = 0;
+      uint32_t run = 0, occ = 0;
       for (uint32_t b = 0; b <= qf.n_buckets; ++b) {
         run += count[b];
+        occ = std::max(occ, count[b]);
         out.q_lut[qf.lut_off + b] = static_cast<uint16_t>(run);
       }
+      out.q_feats[f].max_occupancy = occ;
     }
-    // 2. feature groups whose tables fit the quantisation kernel's shared memory
-    auto feat_bytes = [&](int f) {
+    // 2. feature groups whose tables fit the quantisation kernel's shared memory, one blob each
+    auto steps_for = [](uint32_t occ) {
+      uint32_t k = 0;
+      while ((1u << k) <= occ) ++k;  // 2^k > occ
+      return k;
+    };
+    auto feat_bytes = [&](int f, uint32_t steps) {
       const QFeature& qf = out.q_feats[f];
       const uint32_t lut = ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
-      return lut + static_cast<uint32_t>((qf.m * sizeof(T) + 7) / 8 * 8);
+      return lut + static_cast<uint32_t>(((qf.m + (1u << steps)) * sizeof(T) + 7) / 8 * 8);
     };
     out.q_groups.clear();
+    out.q_blob.clear();
+    const uint32_t rec_bytes = kQMaxGroupFeatures * sizeof(QFeatRec);
     for (int f = 0; f < F;) {
-      QGroup g{static_cast<uint32_t>(f), static_cast<uint32_t>(f), 0, 0};
-      while (f < F && g.f_end - g.f_begin < kQMaxGroupFeatures &&
-             g.smem_bytes + feat_bytes(f) <= kQGroupSmemBudget) {
-        g.smem_bytes += feat_bytes(f);
-        ++g.f_end;
-        ++f;
+      // the largest power-of-two run of features whose blob (with the window padding of its
+      // fullest bucket) fits; a power of two lets every thread of the pre-pass keep one feature
+      int end        = f;
+      uint32_t steps = 0;
+      for (int want = static_cast<int>(kQMaxGroupFeatures); want >= 1; want /= 2) {
+        const int stop = std::min(F, f + want);
+        uint32_t st    = 0;
+        for (int g = f; g < stop; ++g) st = std::max(st, steps_for(out.q_feats[g].max_occupancy));
+        uint32_t bytes = rec_bytes;
+        for (int g = f; g < stop; ++g) bytes += feat_bytes(g, st);
+        if (bytes <= kQGroupSmemBudget && (stop - f == want || want == 1 || stop == F)) {
+          // a short tail group is rounded down to a power of two as well
+          int n = stop - f;
+          while (n & (n - 1)) n &= n - 1;
+          end   = f + n;
+          steps = st;
+          break;
+        }
       }
-      if (g.f_end == g.f_begin) return false;  // one feature alone exceeds the budget
+      if (end == f) return false;  // one feature alone exceeds the budget
+      QGroup g{};
+      g.f_begin  = static_cast<uint32_t>(f);
+      g.f_end    = static_cast<uint32_t>(end);
+      g.steps    = steps;
+      g.blob_off = static_cast<uint32_t>(out.q_blob.size());
+      std::vector<uint8_t> blob(rec_bytes, 0);
+      for (int h = f; h < end; ++h) {
+        const QFeature& qf = out.q_feats[h];
+        QFeatRec rec{};
+        rec.nbm1   = qf.n_buckets - 1;
+        rec.scale  = qf.scale;
+        rec.offset = qf.offset;
+        rec.lut_off = static_cast<uint32_t>(blob.size());
+        blob.resize(blob.size() + ((qf.n_buckets + 1) * 2 + 7) / 8 * 8, 0);
+        std::memcpy(blob.data() + rec.lut_off, out.q_lut.data() + qf.lut_off,
+                    (qf.n_buckets + 1) * 2);
+        rec.thr_off = static_cast<uint32_t>(blob.size());
+        const size_t n_pad = qf.m + (size_t(1) << steps);
+        blob.resize(blob.size() + (n_pad * sizeof(T) + 7) / 8 * 8, 0);
+        std::memcpy(blob.data() + rec.thr_off, out.q_thresholds.data() + qf.t_off * sizeof(T),
+                    qf.m * sizeof(T));
+        const T nan = std::numeric_limits<T>::quiet_NaN();
+        for (size_t k = qf.m; k < n_pad; ++k) put(blob, rec.thr_off + k * sizeof(T), nan);
+        std::memcpy(blob.data() + (h - f) * sizeof(QFeatRec), &rec, sizeof(rec));
+      }
+      blob.resize((blob.size() + 15) / 16 * 16, 0);
+      g.blob_bytes = static_cast<uint32_t>(blob.size());
+      out.q_blob.insert(out.q_blob.end(), blob.begin(), blob.end());
+      out.view.q_max_blob_bytes = std::max<int64_t>(out.view.q_max_blob_bytes, g.blob_bytes);
       out.q_groups.push_back(g);
+      f = end;
     }
     // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node
     const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
@@ -741,7 +792,9 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
       out.q_lut.clear();
       out.q_feats.clear();
       out.q_groups.clear();
-      out.view.q_enabled = 0;
+      out.q_blob.clear();
+      out.view.q_enabled        = 0;
+      out.view.q_max_blob_bytes = 0;
     }
   }
   return B2FIL_OK;

@@ -126,23 +126,31 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
   const ForestView& v = pf.view;
   const int D         = v.dense_depth;
   const int F         = v.n_features;
-  const T* thr        = reinterpret_cast<const T*>(pf.q_thresholds.data());
   std::vector<uint16_t> q(F);
   int64_t bad = 0;
   for (int64_t r = 0; r < n_rows; ++r) {
     const T* row = X + r * stride;
-    for (int f = 0; f < F; ++f) {
-      const QFeature& qf = pf.q_feats[f];
-      const T x          = row[f];
-      if (x != x) {
-        q[f] = Q_NAN_CODE;
-        continue;
+    for (const QGroup& g : pf.q_groups) {
+      const uint8_t* blob = pf.q_blob.data() + g.blob_off;
+      for (uint32_t f = g.f_begin; f < g.f_end; ++f) {
+        QFeatRec rec;
+        std::memcpy(&rec, blob + (f - g.f_begin) * sizeof(QFeatRec), sizeof(rec));
+        const T x = row[f];
+        if (x != x) {
+          q[f] = Q_NAN_CODE;
+          continue;
+        }
+        const uint32_t b = q_bucket_host<T>(x, static_cast<T>(rec.scale),
+                                            static_cast<T>(rec.offset), rec.nbm1 + 1);
+        uint16_t lo16;
+        std::memcpy(&lo16, blob + rec.lut_off + b * 2, 2);
+        const T* thr = reinterpret_cast<const T*>(blob + rec.thr_off);
+        uint32_t pos = lo16;
+        for (uint32_t s2 = (1u << g.steps) >> 1; s2 >= 1; s2 >>= 1) {
+          if (thr[pos + s2 - 1] <= x) pos += s2;
+        }
+        q[f] = static_cast<uint16_t>(pos);
       }
-      const uint32_t b = q_bucket_host<T>(x, static_cast<T>(qf.scale), static_cast<T>(qf.offset),
-                                          qf.n_buckets);
-      uint32_t lo = pf.q_lut[qf.lut_off + b], hi = pf.q_lut[qf.lut_off + b + 1];
-      while (lo < hi && !(x < thr[qf.t_off + lo])) ++lo;
-      q[f] = static_cast<uint16_t>(lo);
     }
     for (int p = 0; p < v.n_trees; ++p) {
       const uint8_t* t = pf.q_nodes.data() + static_cast<size_t>(v.q_tree_stride) * p;

@@ -333,11 +333,17 @@ def test_status_word_and_launch_counter(lib):
     import ctypes as C
 
     desc = random_forest_desc(60, n_trees=5)
-    fi = ForestInference.load_from_treelite_model(desc, storage="dense")
+    fi = ForestInference.load_from_treelite_model(desc, storage="dense", quantize_rows=False)
     before = lib.b2fil_kernel_launches()
     fi.apply(_dev(random_rows(1, 100, desc.n_features), "single"))
     _torch().cuda.synchronize()
     assert lib.b2fil_kernel_launches() == before + 1
+    # with rank quantisation a prediction is a pre-pass plus a traversal kernel per row chunk
+    fq = ForestInference.load_from_treelite_model(desc, storage="dense")
+    before = lib.b2fil_kernel_launches()
+    fq.apply(_dev(random_rows(1, 100, desc.n_features), "single"))
+    _torch().cuda.synchronize()
+    assert lib.b2fil_kernel_launches() == before + 2
     st = C.c_int32(-1)
     assert lib.b2fil_forest_status(fi.forest.handle, C.byref(st)) == 0 and st.value == 0
 
