@@ -1373,8 +1373,9 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
       rc  = B2FIL_ERR_CUDA;
       break;
     }
-    const int gx = static_cast<int>(std::min<int64_t>(
-      n_tiles, std::max(1, (2 * sm_count + f.q_n_groups - 1) / f.q_n_groups)));
+    // one wave of persistent CTAs: every CTA loads its group's tables once
+    const int gx = static_cast<int>(
+      std::min<int64_t>(n_tiles, std::max(1, sm_count / f.q_n_groups)));
     const dim3 qgrid(gx, f.q_n_groups);
     const dim3 qblock(1024);
     if (precision == B2FIL_F32) {
