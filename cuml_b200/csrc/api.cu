@@ -395,6 +395,33 @@ int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int6
                  static_cast<cudaStream_t>(cuda_stream));
 }
 
+int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const void* X_dev,
+                                int64_t n_rows, int64_t row_stride, void* out_dev, int chunk_size,
+                                double threshold, void* cuda_stream)
+{
+  int rc = check_predict_args(f, infer_kind, X_dev, n_rows, row_stride, out_dev);
+  if (rc != B2FIL_OK) return rc;
+  DeviceGuard guard(f->device);
+  if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+  PredictParams p{};
+  p.f          = f->view;
+  p.X          = X_dev;
+  p.n_rows     = n_rows;
+  p.row_stride = row_stride;
+  p.out        = out_dev;
+  p.kind       = infer_kind;
+  p.threshold  = threshold;
+  p.status     = f->status;
+  std::string err;
+  int64_t n = 0;
+  rc = launch_predict_fixed_scratch(p, chunk_size > 0 ? chunk_size : f->default_chunk,
+                                    f->sm_count, f->device,
+                                    static_cast<cudaStream_t>(cuda_stream), err, &n);
+  g_launches += n;
+  if (rc != B2FIL_OK) return set_error(rc, err);
+  return B2FIL_OK;
+}
+
 int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int64_t n_rows,
                        int64_t row_stride, void* out_host, int chunk_size, double threshold)
 {

@@ -26,6 +26,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "kernels.hpp"
@@ -1396,6 +1397,42 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   return rc;
 }
 
+// ---------------------------------------------------------------------------------------------
+// prediction on rank-quantised rows with a fixed, preallocated scratch array
+// ---------------------------------------------------------------------------------------------
+// The rank image of a batch normally lives in stream-ordered scratch taken from a memory pool.
+// This array replaces it for callers that must not allocate while they predict.  It is part of
+// the library image: every GPU that loads the library holds it until the process exits.
+constexpr size_t kFixedScratchBytes = B2FIL_FIXED_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_fixed_mu;
+void* g_fixed_ptr[kMaxDevices] = {};
+
+// Device address of g_fixed_scratch on the current device (`device` is its ordinal).  In host
+// code the array's name is only a handle for the runtime, not an address a kernel can use, so the
+// address is asked for once per device and cached.
+int fixed_scratch_address(int device, void** out, std::string& err)
+{
+  if (device < 0 || device >= kMaxDevices) {
+    err = "device ordinal beyond the fixed-scratch table";
+    return B2FIL_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_fixed_mu);
+  if (!g_fixed_ptr[device]) {
+    void* ptr           = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
+    if (e != cudaSuccess || !ptr) {
+      err = std::string("cudaGetSymbolAddress(fixed scratch): ") + cudaGetErrorString(e);
+      return B2FIL_ERR_CUDA;
+    }
+    g_fixed_ptr[device] = ptr;
+  }
+  *out = g_fixed_ptr[device];
+  return B2FIL_OK;
+}
+
 int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
 {
   if (chunk_size > 0) return std::min(128, std::max(32, 32 * chunk_size));
@@ -1537,6 +1574,92 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
     return B2FIL_ERR_CUDA;
   }
   if (launches) ++*launches;
+  return B2FIL_OK;
+}
+
+
+int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_count, int device,
+                                 cudaStream_t stream, std::string& err, int64_t* launches)
+{
+  const ForestView& f = p.f;
+  if (p.n_rows == 0) return B2FIL_OK;
+  const bool quantised = (f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled &&
+                         p.row_stride < (int64_t(1) << 22);
+  // forests that predict without scratch take the ordinary path, which allocates nothing for them
+  if (!quantised) return launch_predict(p, chunk_size, sm_count, stream, nullptr, err, launches);
+  int mode;
+  switch (p.kind) {
+    case B2FIL_INFER_DEFAULT:
+    case B2FIL_INFER_CLASS: mode = f.leaf_vector_len > 1 ? MODE_VECTOR : MODE_SCALAR; break;
+    case B2FIL_INFER_PROBA2:
+      if (f.n_outputs != 1) {
+        err = "B2FIL_INFER_PROBA2 needs a forest with one output";
+        return B2FIL_ERR_INVALID_ARG;
+      }
+      mode = MODE_SCALAR;
+      break;
+    case B2FIL_INFER_PER_TREE: mode = MODE_PERTREE; break;
+    case B2FIL_INFER_LEAF_ID: mode = MODE_LEAFID; break;
+    default: err = "unknown infer_kind"; return B2FIL_ERR_INVALID_ARG;
+  }
+  const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
+  DenseCfg c;
+  if (!dense_q_config(f.dense_depth, precision, f.n_features, f.n_outputs, mode <= MODE_VECTOR,
+                      p.n_rows, chunk_size, sm_count, c)) {
+    err = "no quantised launch shape fits shared memory";
+    return B2FIL_ERR_UNSUPPORTED;
+  }
+  const int R           = c.rows_per_tile;
+  const size_t tile_b   = static_cast<size_t>(f.n_features) * R * 2;
+  const int64_t n_tiles = (p.n_rows + R - 1) / R;
+  const size_t q_bytes  = static_cast<size_t>(n_tiles) * tile_b;
+  const size_t fl_bytes = (static_cast<size_t>(n_tiles) * 4 + 255) / 256 * 256;
+  if (q_bytes + fl_bytes > kFixedScratchBytes) {
+    const size_t per_row = static_cast<size_t>(f.n_features) * 2 + 1;
+    err = "batch too large for the fixed scratch array: " + std::to_string(p.n_rows) +
+          " rows of " + std::to_string(f.n_features) + " features need " +
+          std::to_string(q_bytes + fl_bytes) + " bytes, the array holds " +
+          std::to_string(kFixedScratchBytes) + " (about " +
+          std::to_string(kFixedScratchBytes / per_row / 256 * 256) + " rows per call)";
+    return B2FIL_ERR_TOO_LARGE;
+  }
+  void* base = nullptr;
+  int rc     = fixed_scratch_address(device, &base, err);
+  if (rc != B2FIL_OK) return rc;
+  uint16_t* Q    = reinterpret_cast<uint16_t*>(base);
+  int32_t* flags = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(base) + q_bytes);
+  // the array keeps what the previous call left in it: the NaN flags of the tiles are
+  // accumulated with atomicOr and must start at zero (the ranks themselves are fully rewritten)
+  cudaError_t e = cudaMemsetAsync(flags, 0, static_cast<size_t>(n_tiles) * 4, stream);
+  if (e != cudaSuccess) {
+    err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
+  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes) +
+                        static_cast<size_t>(kQMaxGroupFeatures) * (R + 2) * 2;
+  const int gx = static_cast<int>(
+    std::min<int64_t>(n_tiles, std::max(1, sm_count / f.q_n_groups)));
+  const dim3 qgrid(gx, f.q_n_groups);
+  const dim3 qblock(1024);
+  if (precision == B2FIL_F32) {
+    auto k = quantise_kernel<float>;
+    if ((rc = set_smem(k, q_smem, err)) != B2FIL_OK) return rc;
+    k<<<qgrid, qblock, q_smem, stream>>>(p, Q, flags, R);
+  } else {
+    auto k = quantise_kernel<double>;
+    if ((rc = set_smem(k, q_smem, err)) != B2FIL_OK) return rc;
+    k<<<qgrid, qblock, q_smem, stream>>>(p, Q, flags, R);
+  }
+  const int grid = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
+  rc = precision == B2FIL_F32 ? launch_dense_q_t<float>(p, mode, c, Q, flags, grid, stream, err)
+                              : launch_dense_q_t<double>(p, mode, c, Q, flags, grid, stream, err);
+  if (rc != B2FIL_OK) return rc;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    err = std::string("kernel launch: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
+  if (launches) *launches += 2;
   return B2FIL_OK;
 }
 

@@ -48,4 +48,10 @@ bool dense_ok(int depth, int precision, int n_features, int n_outputs);
 int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
                    cudaMemPool_t pool, std::string& err, int64_t* launches);
 
+// Same as launch_predict for forests that predict on rank-quantised rows, except that the rank
+// image goes into a fixed device array inside the library instead of pool memory: nothing is
+// allocated.  `device` is the ordinal of the current device.  The whole batch must fit the array.
+int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_count, int device,
+                                 cudaStream_t stream, std::string& err, int64_t* launches);
+
 }  // namespace b2fil

@@ -57,6 +57,8 @@ def load() -> C.CDLL:
     lib.b2fil_output_elems_per_row.argtypes = [vp, i32]
     lib.b2fil_predict.restype = i32
     lib.b2fil_predict.argtypes = [vp, i32, vp, i64, i64, vp, i32, C.c_double, vp]
+    lib.b2fil_predict_fixed_scratch.restype = i32
+    lib.b2fil_predict_fixed_scratch.argtypes = [vp, i32, vp, i64, i64, vp, i32, C.c_double, vp]
     lib.b2fil_predict_host.restype = i32
     lib.b2fil_predict_host.argtypes = [vp, i32, vp, i64, i64, vp, i32, C.c_double]
     lib.b2fil_predict_sharded.restype = i32

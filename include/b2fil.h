@@ -204,6 +204,35 @@ int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int6
                   int64_t row_stride, void* out_dev, int chunk_size, double threshold,
                   void* cuda_stream);
 
+/* Size of the fixed scratch array used by b2fil_predict_fixed_scratch (32 MiB per GPU). */
+#define B2FIL_FIXED_SCRATCH_BYTES 33554432
+
+/* Batched prediction, device buffers, for callers that must not allocate device memory while
+ * they predict.  It has no counterpart in the reference.
+ *
+ * b2fil_predict keeps the 16-bit rank image of the batch (forests with row_quantization = 1) in
+ * scratch that it takes from a CUDA memory pool.  A process whose GPU memory is handed out in
+ * full to its own allocator at start-up, or a serving loop that cannot afford the lock and the
+ * possible failure of an allocation in the middle of a request, cannot accept that.  For them this
+ * call writes the rank image into a B2FIL_FIXED_SCRATCH_BYTES array that is part of the library
+ * image on every GPU that loads the library; it calls no cudaMalloc / cudaFree and no allocating
+ * library routine.
+ *
+ * Arguments, outputs and errors are those of b2fil_predict, with these differences:
+ *  - the whole batch must fit the array: ceil(n_rows / T) * T * n_features * 2 bytes plus four
+ *    bytes per tile of T rows (T <= 256) may not exceed B2FIL_FIXED_SCRATCH_BYTES, i.e. about
+ *    B2FIL_FIXED_SCRATCH_BYTES / (2 * n_features) rows per call (about 65,000 rows of 256 features);
+ *    larger batches return B2FIL_ERR_TOO_LARGE with the numbers in the message: split them;
+ *  - all calls on one GPU share the array: two calls whose kernels can overlap on the GPU (two
+ *    streams, two threads) race on it; issue them on one stream or serialise them yourself;
+ *  - the first call on each device looks up the array's device address (with that device current)
+ *    and caches it; make that first call before any stream capture is started;
+ *  - forests that predict without scratch (sparse storage, categorical tests, row_quantization =
+ *    0) are simply forwarded to the ordinary path, which allocates nothing for them. */
+int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const void* X_dev,
+                                int64_t n_rows, int64_t row_stride, void* out_dev, int chunk_size,
+                                double threshold, void* cuda_stream);
+
 /* Batched prediction, host buffers: copies row blocks to the device, predicts and copies results
  * back, with copies and kernels overlapped on two internal streams.  Pinned host memory gives
  * full copy bandwidth; pageable memory works.  Synchronous: returns when out_host is complete.
