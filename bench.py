@@ -102,6 +102,20 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def max_over_ranks(t, world: int) -> float:
+    """Largest value of a one-element tensor over all ranks (the job ends with its slowest rank)."""
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rows_per_s(rows_per_rank: int, world: int, ms_per_step: float) -> float:
+    """Rows all ranks processed in one step over the time of the slowest rank."""
+    return rows_per_rank * world / (ms_per_step * 1e-3)
+
+
 def build_forest_desc():
     from cuml_b200.fil import synthetic_complete_forest
 
@@ -192,10 +206,7 @@ def measure_e2e(fi, X, out, n, world, dev, barrier, args):
     for _ in range(e2e_steps):
         fi.predict_proba(Xh_np, preds=oh_np)
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_s = float(te.item())
+    e2e_s = max_over_ranks(torch.tensor([e2e_s], device=dev, dtype=torch.float64), world)
     e2e_ok = bool(np.allclose(oh_np[:1000], out[:1000].cpu().numpy(), rtol=1e-6, atol=1e-7))
 
     return {"value": e2e_rows * world / e2e_s, "unit": "rows/s",
@@ -257,12 +268,9 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_start.elapsed_time(t_end)
     kernel_ms = [a.elapsed_time(b) for a, b in ev]
-    tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    total_ms = float(tt.item())
+    total_ms = max_over_ranks(torch.tensor([total_ms], device=dev, dtype=torch.float64), world)
     ms_per_step = total_ms / args.steps
-    value = n * world / (ms_per_step * 1e-3)
+    value = whole_job_rows_per_s(n, world, ms_per_step)
 
     e2e = None
     if not args.no_e2e:

@@ -198,7 +198,9 @@ int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind);
  * b2fil_output_elems_per_row() elements (precision type; uint32 for LEAF_ID, int32 for CLASS).
  * chunk_size 0 = the forest's default.  `threshold` is the binary decision threshold of
  * B2FIL_INFER_CLASS for one-output classifiers.  Enqueues on cuda_stream (NULL = default stream)
- * of the forest's device; allocates nothing.
+ * of the forest's device and does not synchronise.  Forests with row_quantization = 1 keep the
+ * 16-bit rank image of the batch in stream-ordered scratch from a memory pool owned by the forest
+ * (cached between calls); other forests use no scratch.
  * Replaces forest_model.predict(...) (cpp/tests/sg/rf_test.cu:268-275). */
 int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int64_t n_rows,
                   int64_t row_stride, void* out_dev, int chunk_size, double threshold,

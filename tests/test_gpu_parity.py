@@ -357,3 +357,25 @@ def test_pickle_round_trip():
     a = fi.predict_proba(X).cpu().numpy()
     fi2 = pickle.loads(pickle.dumps(fi))
     assert np.array_equal(a, fi2.predict_proba(X).cpu().numpy())
+
+
+def test_sharded_prediction_over_available_gpus():
+    """Model replicated, rows sharded, results gathered on the first device by peer copies."""
+    torch = _torch()
+    from cuml_b200.fil.multi_gpu import ShardedForestInference
+
+    n_dev = min(torch.cuda.device_count(), 4)
+    desc = random_forest_desc(80, n_trees=31, n_features=10, max_depth=6, n_outputs=3,
+                              postproc="softmax")
+    fi = ForestInference.load_from_treelite_model(desc, device_id=0)
+    sh = ShardedForestInference(fi, list(range(n_dev)))
+    X = random_rows(9, 5003, 10, np.float32, nan_frac=0.05)
+    shards = sh.scatter(X)
+    assert sum(s.shape[0] for s in shards) == 5003
+    proba = sh.predict_proba(shards).cpu().numpy()
+    np.testing.assert_allclose(proba, oracle.predict(desc, X, INFER_DEFAULT, "single"),
+                               rtol=1e-5, atol=1e-6)
+    ids = sh.apply(shards).cpu().numpy()
+    assert np.array_equal(ids.astype(np.uint32), oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+    cls = sh.predict(shards).cpu().numpy()
+    assert np.array_equal(cls, np.argmax(proba, axis=1))
