@@ -182,6 +182,28 @@ def run_reference(args):
                 "installed; this arm times the CPU oracle port"}))
 
 
+def measure_latency(fi, X, dev, batches=(1, 1024, 65536), calls=300):
+    """p50 / p99 wall-clock latency (ms) of one `predict_proba` call on device rows, synchronised."""
+    import torch
+
+    res = {}
+    for b in batches:
+        xb = X[:b]
+        ob = torch.empty((b, 2), device=dev, dtype=torch.float32)
+        for _ in range(20):
+            fi.predict_proba(xb, preds=ob)
+        torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(calls):
+            t0 = time.perf_counter()
+            fi.predict_proba(xb, preds=ob)
+            torch.cuda.synchronize(dev)
+            ts.append((time.perf_counter() - t0) * 1e3)
+        ts.sort()
+        res[str(b)] = {"p50_ms": ts[len(ts) // 2], "p99_ms": ts[min(len(ts) - 1, int(len(ts) * 0.99))]}
+    return res
+
+
 def measure_e2e(fi, X, out, n, world, dev, barrier, args):
     """Rows/s through `predict_proba` on pinned host arrays: copies inside the timed region."""
     import numpy as np
@@ -293,12 +315,14 @@ def run_ours(args):
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * n
                                      if NCU_TRAFFIC_BYTES_PER_ROW else None),
-                         "kernel": "dense_kernel<float,false,MODE_SCALAR,2>",
+                         "kernel": "quantise_kernel<float> + dense_q_kernel<float,MODE_SCALAR,2,8>",
                          "kernel_ms": k_ms, "algorithmic_bytes_per_row": BYTES_PER_ROW},
             "e2e": e2e,
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if world == 1 and not args.no_latency:
+            line["latency"] = measure_latency(fi, X, dev)
         if world == 1 and not args.no_cpu:
             v, cores, sample_n = cpu_rows_per_s(desc, 15.0)
             line["cpu_baseline"] = {
@@ -318,6 +342,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling)")
+    ap.add_argument("--no-latency", action="store_true", help="skip the small-batch latency leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
