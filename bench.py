@@ -34,9 +34,11 @@ N_TREES, DEPTH, N_FEATURES = 1000, 8, 256
 ROWS_PER_GPU = 10_000_000
 BYTES_PER_ROW = N_FEATURES * 4 + 2 * 4
 WORKLOAD = "gbdt_1000x_depth8_256f_fp32_sigmoid_10M_rows"
-# DRAM bytes per launch of the dense kernel from an ncu capture, scaled to the full batch
-# (profiles/); None until a capture exists
-NCU_TRAFFIC_BYTES_PER_ROW = None
+# dram__bytes_read.sum + dram__bytes_write.sum per row of the two kernels of a prediction, from
+# the ncu captures of a 1 M-row case summarised under profiles/ (quantise 1332 B + dense_q 533 B;
+# ncu flushes L2 before every launch, so this is an upper bound); traffic grows in proportion to
+# the rows, so it is scaled to the batch
+NCU_TRAFFIC_BYTES_PER_ROW = 1865
 
 
 def measured_peak():

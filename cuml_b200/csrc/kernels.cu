@@ -26,7 +26,9 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <utility>
 #include <type_traits>
 
 #include "kernels.hpp"
@@ -1148,15 +1150,32 @@ size_t dense_smem(int depth, int precision, int F, int NC, bool reduce, int R, i
   return b;
 }
 
+// Raise a kernel's dynamic shared-memory limit to `bytes`.  The limit is a per-device attribute
+// of the kernel: it is set once per (device, kernel) and only raised afterwards, so the steady
+// state of a serving loop pays a table lookup instead of a driver call.
+std::mutex g_smem_mu;
+std::map<std::pair<int, const void*>, size_t> g_smem_set;
+
 template <typename K>
 int set_smem(K kernel, size_t bytes, std::string& err)
 {
+  int device = 0;
+  cudaGetDevice(&device);
+  const auto key = std::make_pair(device, reinterpret_cast<const void*>(kernel));
+  {
+    std::lock_guard<std::mutex> lock(g_smem_mu);
+    const auto it = g_smem_set.find(key);
+    if (it != g_smem_set.end() && it->second >= bytes) return B2FIL_OK;
+  }
   const cudaError_t e = cudaFuncSetAttribute(
     kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
   if (e != cudaSuccess) {
     err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
     return B2FIL_ERR_CUDA;
   }
+  std::lock_guard<std::mutex> lock(g_smem_mu);
+  size_t& have = g_smem_set[key];
+  have         = std::max(have, bytes);
   return B2FIL_OK;
 }
 

@@ -7,6 +7,7 @@
 // pad trees to `align_bytes`, produce one contiguous node array.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <numeric>
@@ -411,125 +412,145 @@ struct Packer {
         if (!std::isnan(thr)) per[d.feature[g]].push_back(thr);
       }
     }
-    size_t total_thr = 0, total_lut = 0;
-    out.q_feats.assign(F, QFeature{});
-    for (int f = 0; f < F; ++f) {
-      auto& v = per[f];
-      std::sort(v.begin(), v.end());
-      v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
-      if (v.size() > Q_MAX_RANK) return false;
-      QFeature& qf = out.q_feats[f];
-      qf.m         = static_cast<uint32_t>(v.size());
-      uint32_t nb  = 16;
-      while (nb < 2 * qf.m && nb < 4096) nb *= 2;
-      qf.n_buckets = qf.m == 0 ? 1 : nb;
-      // bucket grid over the finite thresholds
-      T scale = 0, offset = 0;
-      size_t lo = 0, hi = v.size();
-      while (lo < hi && !std::isfinite(v[lo])) ++lo;
-      while (hi > lo && !std::isfinite(v[hi - 1])) --hi;
-      if (hi - lo >= 2) {
-        const double range = static_cast<double>(v[hi - 1]) - static_cast<double>(v[lo]);
-        const T sc         = static_cast<T>(static_cast<double>(qf.n_buckets) / range);
-        const T of         = static_cast<T>(-static_cast<double>(v[lo]) * static_cast<double>(sc));
-        if (std::isfinite(sc) && std::isfinite(of) && sc > T(0)) {
-          scale  = sc;
-          offset = of;
+    // tables and groups for a given number of buckets per threshold; returns the number of
+    // groups, or -1 when a limit is exceeded
+    auto build_tables = [&](uint32_t bucket_factor) -> int {
+      out.q_groups.clear();
+      out.q_blob.clear();
+      out.view.q_max_blob_bytes = 0;
+      size_t total_thr = 0, total_lut = 0;
+      out.q_feats.assign(F, QFeature{});
+      for (int f = 0; f < F; ++f) {
+        auto& v = per[f];
+        std::sort(v.begin(), v.end());
+        v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
+        if (v.size() > Q_MAX_RANK) return -1;
+        QFeature& qf = out.q_feats[f];
+        qf.m         = static_cast<uint32_t>(v.size());
+        uint32_t nb  = 16;
+        while (nb < bucket_factor * qf.m && nb < 4096) nb *= 2;
+        qf.n_buckets = qf.m == 0 ? 1 : nb;
+        // bucket grid over the finite thresholds
+        T scale = 0, offset = 0;
+        size_t lo = 0, hi = v.size();
+        while (lo < hi && !std::isfinite(v[lo])) ++lo;
+        while (hi > lo && !std::isfinite(v[hi - 1])) --hi;
+        if (hi - lo >= 2) {
+          const double range = static_cast<double>(v[hi - 1]) - static_cast<double>(v[lo]);
+          const T sc         = static_cast<T>(static_cast<double>(qf.n_buckets) / range);
+          const T of         = static_cast<T>(-static_cast<double>(v[lo]) * static_cast<double>(sc));
+          if (std::isfinite(sc) && std::isfinite(of) && sc > T(0)) {
+            scale  = sc;
+            offset = of;
+          }
         }
+        qf.scale   = static_cast<double>(scale);
+        qf.offset  = static_cast<double>(offset);
+        qf.t_off   = static_cast<uint32_t>(total_thr);
+        qf.lut_off = static_cast<uint32_t>(total_lut);
+        total_thr += v.size();
+        total_lut += qf.n_buckets + 1;
       }
-      qf.scale   = static_cast<double>(scale);
-      qf.offset  = static_cast<double>(offset);
-      qf.t_off   = static_cast<uint32_t>(total_thr);
-      qf.lut_off = static_cast<uint32_t>(total_lut);
-      total_thr += v.size();
-      total_lut += qf.n_buckets + 1;
-    }
-    out.q_thresholds.assign(total_thr * sizeof(T), 0);
-    out.q_lut.assign(total_lut, 0);
-    for (int f = 0; f < F; ++f) {
-      const QFeature& qf = out.q_feats[f];
-      const auto& v      = per[f];
-      std::vector<uint32_t> count(qf.n_buckets + 1, 0);
-      for (size_t i = 0; i < v.size(); ++i) {
-        put(out.q_thresholds, (qf.t_off + i) * sizeof(T), v[i]);
-        const uint32_t b = q_bucket_host<T>(v[i], static_cast<T>(qf.scale),
-                                            static_cast<T>(qf.offset), qf.n_buckets);
-        ++count[b + 1];  // lut[b'] counts thresholds in buckets below b'
-      }
-      uint32_t run = 0, occ = 0;
-      for (uint32_t b = 0; b <= qf.n_buckets; ++b) {
-        run += count[b];
-        occ = std::max(occ, count[b]);
-        out.q_lut[qf.lut_off + b] = static_cast<uint16_t>(run);
-      }
-      out.q_feats[f].max_occupancy = occ;
-    }
-    // 2. feature groups whose tables fit the quantisation kernel's shared memory, one blob each
-    auto steps_for = [](uint32_t occ) {
-      uint32_t k = 0;
-      while ((1u << k) <= occ) ++k;  // 2^k > occ
-      return k;
-    };
-    auto feat_bytes = [&](int f, uint32_t steps) {
-      const QFeature& qf = out.q_feats[f];
-      const uint32_t lut = ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
-      return lut + static_cast<uint32_t>(((qf.m + (1u << steps)) * sizeof(T) + 7) / 8 * 8);
-    };
-    out.q_groups.clear();
-    out.q_blob.clear();
-    const uint32_t rec_bytes = kQMaxGroupFeatures * sizeof(QFeatRec);
-    for (int f = 0; f < F;) {
-      // the largest power-of-two run of features whose blob (with the window padding of its
-      // fullest bucket) fits; a power of two lets every thread of the pre-pass keep one feature
-      int end        = f;
-      uint32_t steps = 0;
-      for (int want = static_cast<int>(kQMaxGroupFeatures); want >= 1; want /= 2) {
-        const int stop = std::min(F, f + want);
-        uint32_t st    = 0;
-        for (int g = f; g < stop; ++g) st = std::max(st, steps_for(out.q_feats[g].max_occupancy));
-        uint32_t bytes = rec_bytes;
-        for (int g = f; g < stop; ++g) bytes += feat_bytes(g, st);
-        if (bytes <= kQGroupSmemBudget && (stop - f == want || want == 1 || stop == F)) {
-          // a short tail group is rounded down to a power of two as well
-          int n = stop - f;
-          while (n & (n - 1)) n &= n - 1;
-          end   = f + n;
-          steps = st;
-          break;
+      out.q_thresholds.assign(total_thr * sizeof(T), 0);
+      out.q_lut.assign(total_lut, 0);
+      for (int f = 0; f < F; ++f) {
+        const QFeature& qf = out.q_feats[f];
+        const auto& v      = per[f];
+        std::vector<uint32_t> count(qf.n_buckets + 1, 0);
+        for (size_t i = 0; i < v.size(); ++i) {
+          put(out.q_thresholds, (qf.t_off + i) * sizeof(T), v[i]);
+          const uint32_t b = q_bucket_host<T>(v[i], static_cast<T>(qf.scale),
+                                              static_cast<T>(qf.offset), qf.n_buckets);
+          ++count[b + 1];  // lut[b'] counts thresholds in buckets below b'
         }
+        uint32_t run = 0, occ = 0;
+        for (uint32_t b = 0; b <= qf.n_buckets; ++b) {
+          run += count[b];
+          occ = std::max(occ, count[b]);
+          out.q_lut[qf.lut_off + b] = static_cast<uint16_t>(run);
+        }
+        out.q_feats[f].max_occupancy = occ;
       }
-      if (end == f) return false;  // one feature alone exceeds the budget
-      QGroup g{};
-      g.f_begin  = static_cast<uint32_t>(f);
-      g.f_end    = static_cast<uint32_t>(end);
-      g.steps    = steps;
-      g.blob_off = static_cast<uint32_t>(out.q_blob.size());
-      std::vector<uint8_t> blob(rec_bytes, 0);
-      for (int h = f; h < end; ++h) {
-        const QFeature& qf = out.q_feats[h];
-        QFeatRec rec{};
-        rec.nbm1   = qf.n_buckets - 1;
-        rec.scale  = qf.scale;
-        rec.offset = qf.offset;
-        rec.lut_off = static_cast<uint32_t>(blob.size());
-        blob.resize(blob.size() + ((qf.n_buckets + 1) * 2 + 7) / 8 * 8, 0);
-        std::memcpy(blob.data() + rec.lut_off, out.q_lut.data() + qf.lut_off,
-                    (qf.n_buckets + 1) * 2);
-        rec.thr_off = static_cast<uint32_t>(blob.size());
-        const size_t n_pad = qf.m + (size_t(1) << steps);
-        blob.resize(blob.size() + (n_pad * sizeof(T) + 7) / 8 * 8, 0);
-        std::memcpy(blob.data() + rec.thr_off, out.q_thresholds.data() + qf.t_off * sizeof(T),
-                    qf.m * sizeof(T));
-        const T nan = std::numeric_limits<T>::quiet_NaN();
-        for (size_t k = qf.m; k < n_pad; ++k) put(blob, rec.thr_off + k * sizeof(T), nan);
-        std::memcpy(blob.data() + (h - f) * sizeof(QFeatRec), &rec, sizeof(rec));
+      // 2. feature groups whose tables fit the quantisation kernel's shared memory, one blob each
+      auto steps_for = [](uint32_t occ) {
+        uint32_t k = 0;
+        while ((1u << k) <= occ) ++k;  // 2^k > occ
+        return k;
+      };
+      auto feat_bytes = [&](int f, uint32_t steps) {
+        const QFeature& qf = out.q_feats[f];
+        const uint32_t lut = ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
+        return lut + static_cast<uint32_t>(((qf.m + (1u << steps)) * sizeof(T) + 7) / 8 * 8);
+      };
+      out.q_groups.clear();
+      out.q_blob.clear();
+      const uint32_t rec_bytes = kQMaxGroupFeatures * sizeof(QFeatRec);
+      for (int f = 0; f < F;) {
+        // the largest power-of-two run of features whose blob (with the window padding of its
+        // fullest bucket) fits; a power of two lets every thread of the pre-pass keep one feature
+        int end        = f;
+        uint32_t steps = 0;
+        for (int want = static_cast<int>(kQMaxGroupFeatures); want >= 1; want /= 2) {
+          const int stop = std::min(F, f + want);
+          uint32_t st    = 0;
+          for (int g = f; g < stop; ++g) st = std::max(st, steps_for(out.q_feats[g].max_occupancy));
+          uint32_t bytes = rec_bytes;
+          for (int g = f; g < stop; ++g) bytes += feat_bytes(g, st);
+          if (bytes <= kQGroupSmemBudget && (stop - f == want || want == 1 || stop == F)) {
+            // a short tail group is rounded down to a power of two as well
+            int n = stop - f;
+            while (n & (n - 1)) n &= n - 1;
+            end   = f + n;
+            steps = st;
+            break;
+          }
+        }
+        if (end == f) return -1;  // one feature alone exceeds the budget
+        QGroup g{};
+        g.f_begin  = static_cast<uint32_t>(f);
+        g.f_end    = static_cast<uint32_t>(end);
+        g.steps    = steps;
+        g.blob_off = static_cast<uint32_t>(out.q_blob.size());
+        std::vector<uint8_t> blob(rec_bytes, 0);
+        for (int h = f; h < end; ++h) {
+          const QFeature& qf = out.q_feats[h];
+          QFeatRec rec{};
+          rec.nbm1   = qf.n_buckets - 1;
+          rec.scale  = qf.scale;
+          rec.offset = qf.offset;
+          rec.lut_off = static_cast<uint32_t>(blob.size());
+          blob.resize(blob.size() + ((qf.n_buckets + 1) * 2 + 7) / 8 * 8, 0);
+          std::memcpy(blob.data() + rec.lut_off, out.q_lut.data() + qf.lut_off,
+                      (qf.n_buckets + 1) * 2);
+          rec.thr_off = static_cast<uint32_t>(blob.size());
+          const size_t n_pad = qf.m + (size_t(1) << steps);
+          blob.resize(blob.size() + (n_pad * sizeof(T) + 7) / 8 * 8, 0);
+          std::memcpy(blob.data() + rec.thr_off, out.q_thresholds.data() + qf.t_off * sizeof(T),
+                      qf.m * sizeof(T));
+          const T nan = std::numeric_limits<T>::quiet_NaN();
+          for (size_t k = qf.m; k < n_pad; ++k) put(blob, rec.thr_off + k * sizeof(T), nan);
+          std::memcpy(blob.data() + (h - f) * sizeof(QFeatRec), &rec, sizeof(rec));
+        }
+        blob.resize((blob.size() + 15) / 16 * 16, 0);
+        g.blob_bytes = static_cast<uint32_t>(blob.size());
+        out.q_blob.insert(out.q_blob.end(), blob.begin(), blob.end());
+        out.view.q_max_blob_bytes = std::max<int64_t>(out.view.q_max_blob_bytes, g.blob_bytes);
+        out.q_groups.push_back(g);
+        f = end;
       }
-      blob.resize((blob.size() + 15) / 16 * 16, 0);
-      g.blob_bytes = static_cast<uint32_t>(blob.size());
-      out.q_blob.insert(out.q_blob.end(), blob.begin(), blob.end());
-      out.view.q_max_blob_bytes = std::max<int64_t>(out.view.q_max_blob_bytes, g.blob_bytes);
-      out.q_groups.push_back(g);
-      f = end;
+      return static_cast<int>(out.q_groups.size());
+    };
+    // two buckets per threshold keep the search windows short (measured on the 1000-tree
+    // depth-8 forest: the pre-pass takes 120 us per 114 k rows with two buckets per threshold and
+    // 16-feature groups, 196 us with one bucket per threshold and 32-feature groups); the coarser
+    // table is only the fallback when the finer one does not fit shared memory at all
+    {
+      uint32_t factor = 2;
+      if (const char* e = std::getenv("B2FIL_Q_BUCKETS")) {  // tuning aid: force 1 or 2
+        const int forced = std::atoi(e);
+        if (forced == 1 || forced == 2) factor = static_cast<uint32_t>(forced);
+      }
+      if (build_tables(factor) < 0 && (factor == 1 || build_tables(1) < 0)) return false;
     }
     // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node
     const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
