@@ -79,11 +79,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok != 0;
 }
 // Bounded wait: false when the barrier did not complete within kSpinLimit tries (each try blocks
-// for a hardware-defined short time).
+// for a hardware-defined short time, then the warp sleeps briefly).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    // a waiting warp must not compete for issue slots with the warps that are walking trees
+    __nanosleep(256);
   }
   return false;
 }
@@ -106,15 +108,8 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t a)
 }
 __device__ __forceinline__ uint32_t lds_u16(uint32_t a)
 {
-  uint32_t v;
-  asm volatile(
-    "{\n"
-    ".reg .u16 h;\n"
-    "ld.shared.u16 h, [%1];\n"
-    "cvt.u32.u16 %0, h;\n"
-    "}\n"
-    : "=r"(v)
-    : "r"(a));
+  uint32_t v;  // a 16-bit load into a 32-bit register zero-extends
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
   return v;
 }
 // Barrier among the consumer threads only (the producer warp never joins it).
@@ -575,8 +570,8 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
 // The group size GF is a power of two that divides the thread count, so a thread keeps one
 // feature for good (its record sits in registers) and owns up to U rows of every tile; the
 // loads of the next tile are issued before the current tile is ranked.  Ranks are parked in a
-// transposed staging buffer and written out as Q[tile][feature][row in tile] (uint16): the layout
-// the traversal kernel pulls into shared memory with a single bulk copy.  NaN becomes Q_NAN_CODE
+// transposed staging buffer and written out as Q[tile][feature][q_slot(row in tile)] (uint16): the
+// layout the traversal kernel pulls into shared memory with a single bulk copy.  NaN becomes Q_NAN_CODE
 // and raises the tile's flag.
 // Shared memory: [mbarrier 16 B][blob][staging buffer GF x (R + 2) uint16].
 __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
@@ -589,6 +584,15 @@ __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
     "}\n" ::"r"(a),
     "r"(v)
     : "memory");
+}
+
+// Position of row r among the R uint16 entries of one feature in a rank tile.  Rows r and r + 32
+// share a 32-bit word, so the 32 consecutive rows of a warp sit in 32 different banks whatever
+// feature each lane reads (with the plain order two neighbouring rows share a bank and collide
+// as soon as they read different features).  Tiles of 32 rows keep the plain order.
+__device__ __forceinline__ uint32_t q_slot(uint32_t r, int R)
+{
+  return R >= 64 ? (((r & 31u) << 1) | ((r >> 5) & 1u) | ((r >> 6) << 6)) : r;
 }
 
 // Rank of one value: bucket table lookup plus STEPS branch-free halvings over the window that
@@ -646,8 +650,7 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
   const uint32_t lut    = blob_a + mine.lut_off;
   const uint32_t thr_m1 = blob_a + mine.thr_off - TR::ES;
   const int qstride     = R + 2;  // uint16 elements between features in the staging buffer
-  const uint32_t q_mine = qbuf_a + (i * qstride + r_first) * 2u;
-  const uint32_t q_step = r_step * 2u;
+  const uint32_t q_feat = qbuf_a + i * qstride * 2u;
   const int64_t n_tiles = (p.n_rows + R - 1) / R;
   // element offsets inside a tile fit 32 bits (the host sizes row chunks accordingly)
   const uint32_t e_mine = static_cast<uint32_t>(r_first * p.row_stride + grp.f_begin + i);
@@ -686,7 +689,7 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
         const uint32_t rk  = rank_of<T, STEPS>(x, scale, offset, nbm1, lut, thr_m1, grp.steps);
         const bool is_nan  = x != x;
         saw_nan |= is_nan;
-        sts_u16(q_mine + u * q_step, is_nan ? Q_NAN_CODE : rk);
+        sts_u16(q_feat + q_slot(r_first + u * r_step, R) * 2u, is_nan ? Q_NAN_CODE : rk);
       }
     }
     if (__any_sync(0xffffffffu, saw_nan) && (tid & 31) == 0) atomicOr(tile_flags + t, 1);
@@ -806,27 +809,28 @@ struct DenseQWalker {
           const int first = b * per_batch + slot0;
           const int n_act = min(NT, f.n_trees - first);
           if (n_act <= 0) break;
-          uint32_t nbase[NT], a[NT];
+          uint32_t base[NT], idx[NT], a[NT];
 #pragma unroll
           for (int k = 0; k < NT; ++k) {
             // slots past the end of the forest repeat the last live tree; results are dropped
-            const uint32_t base = stage + (slot0 + min(k, n_act - 1)) * tstride;
-            nbase[k]            = 0u - base;
-            a[k]                = base + 4u;  // heap index 1
+            base[k] = stage + (slot0 + min(k, n_act - 1)) * tstride;
+            idx[k]  = 1u;  // heap index of the root
+            a[k]    = base[k] + 4u;
           }
           auto level = [&]() {
 #pragma unroll
             for (int k = 0; k < NT; ++k) {
               const uint32_t node = lds_u32(a[k]);
               const uint32_t q    = lds_u16((node & Q_FEATURE_MASK) * stride_b + row_addr);
-              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0;
+              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0:
               // the sign bit of the difference is the step to the right child
-              uint32_t right = rank_diff(node, q) >> 31;
+              uint32_t d = rank_diff(node, q);
               if (NANS) {
-                if (q == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) ? 0u : 1u;
+                if (q == Q_NAN_CODE) d = (node & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
               }
-              // address of heap node 2i + right from the address of node i
-              a[k] = (a[k] << 1) + ((right << 2) + nbase[k]);
+              // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
+              idx[k] = __funnelshift_l(d, idx[k], 1);
+              a[k]   = idx[k] * 4u + base[k];
             }
           };
           if (DEPTH > 0) {
@@ -841,9 +845,9 @@ struct DenseQWalker {
             if (k < n_act) {
               // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
               // address of leaf slot j is exactly the address the walk ended on
-              const uint32_t leaf_a = TR::ES == 4 ? a[k] : 2u * a[k] + nbase[k] - width_b;
+              const uint32_t slot   = idx[k] - (1u << D);
+              const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
               const typename TR::Val payload = TR::ld_val(leaf_a);
-              const uint32_t slot = ((a[k] + nbase[k]) >> 2) - (1u << D);
               take_leaf<T, MODE>(p, first + k, payload,
                                  (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
                                  row, run);
@@ -941,7 +945,7 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
   const int g             = warp / rw;
   const int r             = (warp % rw) * 32 + lane;
   T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
-  const uint32_t row_addr = tile + r * 2u;
+  const uint32_t row_addr = tile + q_slot(r, R) * 2u;
   uint32_t it             = 0;
   uint32_t n_done         = 0;
   bool ok                 = true;
@@ -1258,8 +1262,8 @@ bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_
   if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S,K"
     int R, G, NT, S, K;
     if (sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5 && R >= 32 && R % 32 == 0 &&
-        G >= 1 && (R / 32) * G <= 31 && (NT == 1 || NT == 2) && S >= 2 && S <= kMaxStages &&
-        K >= 1) {
+        G >= 1 && (R / 32) * G <= 31 && (NT == 1 || NT == 2 || NT == 4) && S >= 2 &&
+        S <= kMaxStages && K >= 1) {
       const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
         cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32, K};
@@ -1271,10 +1275,10 @@ bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_
     const int rw = R / 32;
     // a CTA holds at most 32 warps and one of them is the producer
     for (int G = std::min(8, 31 / rw); G >= 1; --G) {
-      for (int NT = 2; NT >= 1; --NT) {
+      for (int NT = 4; NT >= 1; NT /= 2) {
         // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees;
         // the ring must also cover the bytes in flight over the latency of a bulk copy
-        for (int K = 4; K >= 1; K /= 2) {
+        for (int K = 2; K >= 1; K /= 2) {
           for (int S = 3; S >= 2; --S) {
             const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
             if (b <= kMaxSmemBytes) {
@@ -1301,22 +1305,29 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
     k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups, \
                                                  c.stages, c.sub_batches);                  \
   }
-  if (c.trees_in_flight == 2) {
+  if (c.trees_in_flight == 4) {
     // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies
     if constexpr (std::is_same<T, float>::value) {
-     if (mode == MODE_SCALAR) {
-      switch (p.f.dense_depth) {
-        case 4: B2FIL_Q_CASE(MODE_SCALAR, 2, 4) return B2FIL_OK;
-        case 5: B2FIL_Q_CASE(MODE_SCALAR, 2, 5) return B2FIL_OK;
-        case 6: B2FIL_Q_CASE(MODE_SCALAR, 2, 6) return B2FIL_OK;
-        case 7: B2FIL_Q_CASE(MODE_SCALAR, 2, 7) return B2FIL_OK;
-        case 8: B2FIL_Q_CASE(MODE_SCALAR, 2, 8) return B2FIL_OK;
-        case 9: B2FIL_Q_CASE(MODE_SCALAR, 2, 9) return B2FIL_OK;
-        case 10: B2FIL_Q_CASE(MODE_SCALAR, 2, 10) return B2FIL_OK;
-        default: break;
+      if (mode == MODE_SCALAR) {
+        switch (p.f.dense_depth) {
+          case 4: B2FIL_Q_CASE(MODE_SCALAR, 4, 4) return B2FIL_OK;
+          case 5: B2FIL_Q_CASE(MODE_SCALAR, 4, 5) return B2FIL_OK;
+          case 6: B2FIL_Q_CASE(MODE_SCALAR, 4, 6) return B2FIL_OK;
+          case 7: B2FIL_Q_CASE(MODE_SCALAR, 4, 7) return B2FIL_OK;
+          case 8: B2FIL_Q_CASE(MODE_SCALAR, 4, 8) return B2FIL_OK;
+          case 9: B2FIL_Q_CASE(MODE_SCALAR, 4, 9) return B2FIL_OK;
+          case 10: B2FIL_Q_CASE(MODE_SCALAR, 4, 10) return B2FIL_OK;
+          default: break;
+        }
       }
-     }
     }
+    switch (mode) {
+      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 4, 0) break;
+      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 4, 0) break;
+      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 4, 0) break;
+      default: B2FIL_Q_CASE(MODE_LEAFID, 4, 0) break;
+    }
+  } else if (c.trees_in_flight == 2) {
     switch (mode) {
       case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 2, 0) break;
       case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 2, 0) break;
