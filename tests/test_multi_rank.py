@@ -2,7 +2,6 @@
 predictor, and the per-rank bookkeeping of the benchmark (row shards per rank, max-over-ranks time,
 whole-job throughput) with two `gloo` ranks."""
 import os
-import socket
 import subprocess
 import sys
 
@@ -35,8 +34,9 @@ import os, sys, json
 sys.path.insert(0, sys.argv[1])
 import torch, torch.distributed as dist
 import bench
-dist.init_process_group("gloo")
-rank, world = dist.get_rank(), dist.get_world_size()
+rank, world = int(sys.argv[3]), 2
+# a file store needs no network port
+dist.init_process_group("gloo", init_method="file://" + sys.argv[2], rank=rank, world_size=world)
 # every rank owns its rows; the job's time is the slowest rank's and the throughput counts all rows
 ms = torch.tensor([10.0 + 5.0 * rank], dtype=torch.float64)
 total = bench.max_over_ranks(ms, world)
@@ -48,21 +48,18 @@ dist.destroy_process_group()
 
 
 def test_two_gloo_ranks_reduce_time_and_throughput(tmp_path):
-    script = tmp_path / "worker.py"
-    script.write_text(WORKER)
-    env = dict(os.environ, OMP_NUM_THREADS="1")
-    for attempt in range(3):  # a freshly probed port can be taken by the time torchrun binds it
-        with socket.socket() as s:
-            s.bind(("127.0.0.1", 0))
-            port = s.getsockname()[1]
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node",
-               "2", "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT]
-        out = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
-        if out.returncode == 0:
-            break
-    assert out.returncode == 0, out.stderr[-2000:]
-    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
-    assert len(lines) == 2
     import json
 
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    store = tmp_path / "store"
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(store), str(r)],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+             for r in range(2)]
+    outs = [p.communicate(timeout=240) for p in procs]
+    for p, (out, err) in zip(procs, outs):
+        assert p.returncode == 0, err[-2000:]
+    lines = [ln for out, _ in outs for ln in out.splitlines() if ln.startswith("{")]
+    assert len(lines) == 2
     assert all(json.loads(ln)["ok"] for ln in lines)
