@@ -69,8 +69,14 @@ struct SparseNode16D {  // fp64
 //     x < T[j]  <=>  r(x) <= j.
 // A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x7FFF); the traversal kernel
 // then reads 2-byte values and 4-byte nodes
-//     bits 31..16: j (0xFFFF = never left)   bit 15: missing goes left   bits 14..0: feature
+//     bits 31..16: j (0xFFFF = never left)   bit 15: missing goes left   bit 14: categorical
+//     bits 13..0: feature
 // so a test is one signed subtraction: right <=> int(node) - (rank << 16) < 0.
+// Categorical features (every test on them is categorical, every listed category below 32) keep
+// their place in the same scheme: the "rank" of a value is its category (Q_NO_CATEGORY when it is
+// negative, fractional-truncated out of range or too large), and a categorical node looks its
+// 32-bit category set up in a third per-tree array indexed like the nodes; a set bit sends the
+// row right.
 // The rank is found through a per-feature bucket table: bucket(x) = clamp(int(fma(x, scale,
 // offset)), 0, n_buckets-1) is monotone in x, lut[b] is the number of thresholds in buckets below
 // b (all of them are <= x), thresholds of higher buckets are all > x, so the rank is lut[b] plus
@@ -83,7 +89,7 @@ struct QFeature {      // host-side table of one feature
   uint32_t m;          // number of distinct thresholds
   uint32_t n_buckets;
   uint32_t max_occupancy;  // thresholds in the fullest bucket
-  uint32_t pad;
+  uint32_t is_cat;         // categorical feature: no tables
   double scale;        // bucket(x) = fma(x, scale, offset) evaluated in the forest precision
   double offset;
 };
@@ -94,7 +100,7 @@ struct QFeatRec {      // 32 bytes
   uint32_t lut_off;    // byte offsets from the start of the blob
   uint32_t thr_off;
   uint32_t nbm1;       // n_buckets - 1
-  uint32_t pad;
+  uint32_t is_cat;     // 1: the value's code is its category, no table lookup
   double scale, offset;
 };
 struct QGroup {        // 32 bytes
@@ -106,7 +112,9 @@ struct QGroup {        // 32 bytes
 };
 constexpr uint32_t Q_NAN_CODE     = 0x7FFFu;
 constexpr uint32_t Q_MAX_RANK     = 0x7FFEu;
-constexpr uint32_t Q_FEATURE_MASK = 0x7FFFu;
+constexpr uint32_t Q_NO_CATEGORY  = 0x7FFEu;
+constexpr uint32_t Q_FEATURE_MASK = 0x3FFFu;
+constexpr uint32_t Q_CATEGORICAL  = 0x4000u;
 constexpr uint32_t Q_DEFAULT_LEFT = 0x8000u;
 
 enum NodeFormat : int32_t {
@@ -146,8 +154,11 @@ struct ForestView {
   // rank-quantised copy of a dense forest (q_enabled != 0)
   int32_t q_enabled;
   int32_t q_n_groups;
-  int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size), 16-byte multiple
+  int32_t q_has_cat;            // 1: tree blocks carry a third array of 32-bit category sets
+  int32_t q_pad;
+  int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size [+ 4]), 16-byte multiple
   const void* q_nodes;          // [n_trees] blocks of [2^D nodes uint32][2^D leaf payloads]
+                                //           [2^D category sets uint32, when q_has_cat]
   int64_t q_max_blob_bytes;     // largest group blob
   const unsigned char* q_blob;  // group blobs
   const QGroup* q_groups;       // [q_n_groups]

@@ -595,36 +595,6 @@ __device__ __forceinline__ uint32_t q_slot(uint32_t r, int R)
   return R >= 64 ? (((r & 31u) << 1) | ((r >> 5) & 1u) | ((r >> 6) << 6)) : r;
 }
 
-// Rank of one value: bucket table lookup plus STEPS branch-free halvings over the window that
-// starts at the bucket's first threshold (thresholds of lower buckets are all <= x, those of
-// higher buckets all > x, NaN padding compares false).  A NaN input walks the same code (it
-// lands in bucket 0 and every comparison fails) and is replaced by Q_NAN_CODE by the caller.
-template <typename T, int STEPS>
-__device__ __forceinline__ uint32_t rank_of(T x, T scale, T offset, T nbm1, uint32_t lut,
-                                            uint32_t thr_m1, int steps_rt)
-{
-  using TR = Traits<T>;
-  // same expression as q_bucket_host: fma, clamp (NaN becomes 0), truncate
-  T v = fma(x, scale, offset);
-  v   = fmax(v, T(0));
-  v   = fmin(v, nbm1);
-  const uint32_t b = static_cast<uint32_t>(v);
-  uint32_t pos_b   = lds_u16(lut + b * 2u) * TR::ES;  // byte offset of the window's first entry
-  if (STEPS >= 0) {
-#pragma unroll
-    for (int k = STEPS - 1; k >= 0; --k) {
-      const uint32_t s_b = (1u << k) * TR::ES;
-      pos_b += (TR::ld_real(thr_m1 + pos_b + s_b) <= x) ? s_b : 0u;  // entry pos + 2^k - 1
-    }
-  } else {  // very full buckets: the number of halvings is only known at run time
-    for (int k = steps_rt - 1; k >= 0; --k) {
-      const uint32_t s_b = (1u << k) * TR::ES;
-      pos_b += (TR::ld_real(thr_m1 + pos_b + s_b) <= x) ? s_b : 0u;
-    }
-  }
-  return pos_b / TR::ES;
-}
-
 // NU = rows of a tile each thread owns (R * GF / threads, at least 1).
 template <typename T, int STEPS, int NU>
 __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGroup& grp,
@@ -683,13 +653,52 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
     if (t + gridDim.x < n_tiles) fetch(t + gridDim.x);
     bool saw_nan = false;
     if (active) {
+      // rank of the NU values, step by step across all of them so that the dependent
+      // shared-memory lookups of different values overlap.  A NaN walks the same code (bucket 0,
+      // every comparison false) and is replaced by Q_NAN_CODE at the end.
+      uint32_t pos_b[NU];
+      if (mine.is_cat) {
+        // categorical feature: the code is the category itself (truncated value); negative and
+        // huge values match no listed category
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+          const bool in_range = (cur[u] >= T(0)) && (cur[u] < T(Q_NO_CATEGORY));
+          pos_b[u] = (in_range ? static_cast<uint32_t>(cur[u]) : Q_NO_CATEGORY) * TR::ES;
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+          // same expression as q_bucket_host: fma, clamp (NaN becomes 0), truncate
+          T v = fma(cur[u], scale, offset);
+          v   = fmax(v, T(0));
+          v   = fmin(v, nbm1);
+          pos_b[u] = lds_u16(lut + static_cast<uint32_t>(v) * 2u) * TR::ES;
+        }
+        if (STEPS >= 0) {
+#pragma unroll
+          for (int k = STEPS - 1; k >= 0; --k) {
+            const uint32_t s_b = (1u << k) * TR::ES;
+            T thr[NU];
+#pragma unroll
+            for (int u = 0; u < NU; ++u) thr[u] = TR::ld_real(thr_m1 + pos_b[u] + s_b);
+#pragma unroll
+            for (int u = 0; u < NU; ++u) pos_b[u] += (thr[u] <= cur[u]) ? s_b : 0u;
+          }
+        } else {  // very full buckets: the number of halvings is only known at run time
+          for (int k = static_cast<int>(grp.steps) - 1; k >= 0; --k) {
+            const uint32_t s_b = (1u << k) * TR::ES;
+#pragma unroll
+            for (int u = 0; u < NU; ++u)
+              pos_b[u] += (TR::ld_real(thr_m1 + pos_b[u] + s_b) <= cur[u]) ? s_b : 0u;
+          }
+        }
+      }
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
-        const T x          = cur[u];
-        const uint32_t rk  = rank_of<T, STEPS>(x, scale, offset, nbm1, lut, thr_m1, grp.steps);
-        const bool is_nan  = x != x;
+        const bool is_nan = cur[u] != cur[u];
         saw_nan |= is_nan;
-        sts_u16(q_feat + q_slot(r_first + u * r_step, R) * 2u, is_nan ? Q_NAN_CODE : rk);
+        sts_u16(q_feat + q_slot(r_first + u * r_step, R) * 2u,
+                is_nan ? Q_NAN_CODE : pos_b[u] / TR::ES);
       }
     }
     if (__any_sync(0xffffffffu, saw_nan) && (tid & 31) == 0) atomicOr(tile_flags + t, 1);
@@ -779,7 +788,7 @@ __device__ __forceinline__ uint32_t rank_diff(uint32_t node, uint32_t q)
 
 // DEPTH > 0 fixes the tree depth at compile time (the level loop is fully unrolled); DEPTH == 0
 // reads it from the forest.
-template <typename T, int MODE, int NT, int DEPTH>
+template <typename T, int MODE, int NT, int DEPTH, bool CAT>
 struct DenseQWalker {
   using TR = Traits<T>;
   // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
@@ -795,6 +804,7 @@ struct DenseQWalker {
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
     const uint32_t width_b = (1u << D) * 4u;
+    const uint32_t cat_off = (1u << D) * (4u + TR::ES);  // node address -> its category set
     const int per_sub      = G * NT;
     const int per_batch    = per_sub * K;
     const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
@@ -817,16 +827,29 @@ struct DenseQWalker {
             idx[k]  = 1u;  // heap index of the root
             a[k]    = base[k] + 4u;
           }
+          // the NT walks are independent: all node loads are issued first, then all rank loads,
+          // so that their shared-memory latencies overlap inside one warp
           auto level = [&]() {
+            uint32_t node[NT], q[NT];
+#pragma unroll
+            for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
+#pragma unroll
+            for (int k = 0; k < NT; ++k)
+              q[k] = lds_u16((node[k] & Q_FEATURE_MASK) * stride_b + row_addr);
 #pragma unroll
             for (int k = 0; k < NT; ++k) {
-              const uint32_t node = lds_u32(a[k]);
-              const uint32_t q    = lds_u16((node & Q_FEATURE_MASK) * stride_b + row_addr);
               // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0:
               // the sign bit of the difference is the step to the right child
-              uint32_t d = rank_diff(node, q);
+              uint32_t d = rank_diff(node[k], q[k]);
+              if (CAT) {
+                if (node[k] & Q_CATEGORICAL) {
+                  // the code of a categorical value is its category: a set bit sends it right
+                  const uint32_t bits = lds_u32(a[k] + cat_off);
+                  d = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
+                }
+              }
               if (NANS) {
-                if (q == Q_NAN_CODE) d = (node & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
+                if (q[k] == Q_NAN_CODE) d = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
               }
               // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
               idx[k] = __funnelshift_l(d, idx[k], 1);
@@ -862,7 +885,7 @@ struct DenseQWalker {
   }
 };
 
-template <typename T, int MODE, int NT, int DEPTH>
+template <typename T, int MODE, int NT, int DEPTH, bool CAT>
 __global__ void __launch_bounds__(1024, 1)
 dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
                const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
@@ -960,11 +983,11 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
     Running<T> run{T(0), 0};
     if (ok) {
       if (nans) {
-        ok = DenseQWalker<T, MODE, NT, DEPTH>::template walk<true>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<true>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, it, run);
       } else {
-        ok = DenseQWalker<T, MODE, NT, DEPTH>::template walk<false>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<false>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, it, run);
       }
@@ -1235,12 +1258,11 @@ int launch_sparse_fmt(const PredictParams& p, int mode, int R, int G, int rows_i
   return B2FIL_OK;
 }
 
-size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R, int G, int NT, int S,
-                    int K)
+size_t dense_q_smem(size_t qstride, int precision, int F, int NC, bool reduce, int R, int G, int NT,
+                    int S, int K)
 {
-  const size_t es      = precision == B2FIL_F32 ? 4 : 8;
-  const size_t qstride = align16((size_t(1) << depth) * (4 + es));
-  size_t b             = kBarBytes;
+  const size_t es = precision == B2FIL_F32 ? 4 : 8;
+  size_t b        = kBarBytes;
   b += static_cast<size_t>(F) * R * 2;
   if (reduce) b += align16(static_cast<size_t>(G) * NC * R * es);
   b += 16;
@@ -1250,8 +1272,8 @@ size_t dense_q_smem(int depth, int precision, int F, int NC, bool reduce, int R,
 
 // Launch shape of the quantised dense kernel: the largest row tile that fits, then as many warps
 // as fit (32 consumer warps at most), two trees in flight per warp and a three-stage tree ring.
-bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_t n_rows,
-                    int chunk_size, int sm_count, DenseCfg& cfg)
+bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bool reduce,
+                    int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
 {
   int want = 256;
   if (chunk_size > 0) {
@@ -1263,8 +1285,8 @@ bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_
     int R, G, NT, S, K;
     if (sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5 && R >= 32 && R % 32 == 0 &&
         G >= 1 && (R / 32) * G <= 31 && (NT == 1 || NT == 2 || NT == 4) && S >= 2 &&
-        S <= kMaxStages && K >= 1) {
-      const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
+        S <= kMaxStages && K >= 1 && NT <= max_nt) {
+      const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
         cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32, K};
         return true;
@@ -1275,12 +1297,12 @@ bool dense_q_config(int depth, int precision, int F, int NC, bool reduce, int64_
     const int rw = R / 32;
     // a CTA holds at most 32 warps and one of them is the producer
     for (int G = std::min(8, 31 / rw); G >= 1; --G) {
-      for (int NT = 4; NT >= 1; NT /= 2) {
+      for (int NT = max_nt; NT >= 1; NT /= 2) {
         // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees;
         // the ring must also cover the bytes in flight over the latency of a bulk copy
         for (int K = 2; K >= 1; K /= 2) {
           for (int S = 3; S >= 2; --S) {
-            const size_t b = dense_q_smem(depth, precision, F, NC, reduce, R, G, NT, S, K);
+            const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
             if (b <= kMaxSmemBytes) {
               cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, K};
               return true;
@@ -1298,12 +1320,32 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
                      const int32_t* flags, int grid, cudaStream_t stream, std::string& err)
 {
   int rc;
-#define B2FIL_Q_CASE(M, N, DD)                                                              \
+#define B2FIL_Q_CASE(M, N, DD) B2FIL_Q_CASE_CAT(M, N, DD, false)
+#define B2FIL_Q_CASE_CAT(M, N, DD, CC)                                                      \
   {                                                                                         \
-    auto k = dense_q_kernel<T, M, N, DD>;                                                   \
+    auto k = dense_q_kernel<T, M, N, DD, CC>;                                               \
     if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                       \
     k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups, \
                                                  c.stages, c.sub_batches);                  \
+  }
+  if (p.f.q_has_cat) {
+    // forests with categorical tests: two trees in flight at most (dense_q_config honours it)
+    if (c.trees_in_flight == 2) {
+      switch (mode) {
+        case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, 2, 0, true) break;
+        case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, 2, 0, true) break;
+        case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, 2, 0, true) break;
+        default: B2FIL_Q_CASE_CAT(MODE_LEAFID, 2, 0, true) break;
+      }
+    } else {
+      switch (mode) {
+        case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, 1, 0, true) break;
+        case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, 1, 0, true) break;
+        case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, 1, 0, true) break;
+        default: B2FIL_Q_CASE_CAT(MODE_LEAFID, 1, 0, true) break;
+      }
+    }
+    return B2FIL_OK;
   }
   if (c.trees_in_flight == 4) {
     // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies
@@ -1343,6 +1385,7 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
     }
   }
 #undef B2FIL_Q_CASE
+#undef B2FIL_Q_CASE_CAT
   return B2FIL_OK;
 }
 
@@ -1356,8 +1399,8 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
   const bool reduce   = mode <= MODE_VECTOR;
   DenseCfg c;
-  if (!dense_q_config(f.dense_depth, precision, f.n_features, f.n_outputs, reduce, p.n_rows,
-                      chunk_size, sm_count, c)) {
+  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), f.q_has_cat ? 2 : 4, precision,
+                      f.n_features, f.n_outputs, reduce, p.n_rows, chunk_size, sm_count, c)) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }
@@ -1634,8 +1677,9 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
   }
   const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
   DenseCfg c;
-  if (!dense_q_config(f.dense_depth, precision, f.n_features, f.n_outputs, mode <= MODE_VECTOR,
-                      p.n_rows, chunk_size, sm_count, c)) {
+  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), f.q_has_cat ? 2 : 4, precision,
+                      f.n_features, f.n_outputs, mode <= MODE_VECTOR, p.n_rows, chunk_size,
+                      sm_count, c)) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }

@@ -398,19 +398,28 @@ struct Packer {
   bool build_quantised(int D)
   {
     const int F = d.n_features;
-    if (has_cat || F > static_cast<int>(Q_FEATURE_MASK) + 1) return false;
+    if (F > static_cast<int>(Q_FEATURE_MASK) + 1) return false;
+    if (has_cat && !cat_inline) return false;  // category sets must fit 32 bits
     const int nt = d.n_trees;
-    // 1. distinct thresholds per feature, in the forest precision, after normalisation to `<`
+    // 1. distinct thresholds per feature, in the forest precision, after normalisation to `<`;
+    //    a feature is either numerical or categorical in the whole forest
     std::vector<std::vector<T>> per(F);
+    std::vector<uint8_t> used_num(F, 0), used_cat(F, 0);
     for (int t = 0; t < nt; ++t) {
       const int64_t base = d.tree_offsets[t];
       const int64_t n    = d.tree_offsets[t + 1] - base;
       for (int64_t r = 0; r < n; ++r) {
         const int64_t g = base + r;
-        if (depth_of[g] < 0 || d.node_kind[g] != B2FIL_NODE_NUMERICAL) continue;
+        if (depth_of[g] < 0) continue;
+        if (d.node_kind[g] == B2FIL_NODE_CATEGORICAL) used_cat[d.feature[g]] = 1;
+        if (d.node_kind[g] != B2FIL_NODE_NUMERICAL) continue;
+        used_num[d.feature[g]] = 1;
         const T thr = static_cast<T>(normalise(d, g, precision).thr);
         if (!std::isnan(thr)) per[d.feature[g]].push_back(thr);
       }
+    }
+    for (int f = 0; f < F; ++f) {
+      if (used_num[f] && used_cat[f]) return false;
     }
     // tables and groups for a given number of buckets per threshold; returns the number of
     // groups, or -1 when a limit is exceeded
@@ -426,6 +435,7 @@ struct Packer {
         v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
         if (v.size() > Q_MAX_RANK) return -1;
         QFeature& qf = out.q_feats[f];
+        qf.is_cat    = used_cat[f];
         qf.m         = static_cast<uint32_t>(v.size());
         uint32_t nb  = 16;
         while (nb < bucket_factor * qf.m && nb < 4096) nb *= 2;
@@ -515,6 +525,7 @@ struct Packer {
         for (int h = f; h < end; ++h) {
           const QFeature& qf = out.q_feats[h];
           QFeatRec rec{};
+          rec.is_cat = qf.is_cat;
           rec.nbm1   = qf.n_buckets - 1;
           rec.scale  = qf.scale;
           rec.offset = qf.offset;
@@ -552,36 +563,47 @@ struct Packer {
       }
       if (build_tables(factor) < 0 && (factor == 1 || build_tables(1) < 0)) return false;
     }
-    // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node
+    // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node; forests with
+    //    categorical tests carry a third array with the 32-bit category set of every node
     const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
     const size_t es      = sizeof(T);
     const int64_t width  = int64_t(1) << D;
-    int64_t qstride      = width * static_cast<int64_t>(4 + es);
+    int64_t qstride      = width * static_cast<int64_t>(4 + es + (has_cat ? 4 : 0));
     qstride              = (qstride + 15) / 16 * 16;
     out.q_nodes.assign(static_cast<size_t>(qstride) * nt, 0);
     for (int p = 0; p < nt; ++p) {
       const uint8_t* src = out.nodes.data() + static_cast<size_t>(out.view.tree_stride) * p;
       uint8_t* dst       = out.q_nodes.data() + static_cast<size_t>(qstride) * p;
+      uint8_t* sets      = dst + width * (4 + es);
       for (int64_t i = 1; i < width; ++i) {
         T thr;
         uint32_t meta;
         std::memcpy(&thr, src + i * nb, sizeof(T));
         std::memcpy(&meta, src + i * nb + sizeof(T), 4);
         const uint32_t feat = meta & 0x3FFFFFFFu;
-        uint32_t j;
-        if (std::isnan(thr)) {
-          j = 0xFFFFu;  // x < NaN never holds: always right
+        uint32_t node       = ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | feat;
+        if (meta & META_CATEGORICAL) {
+          uint32_t bits;  // the inline category set sits in the low word of the value slot
+          std::memcpy(&bits, src + i * nb, 4);
+          std::memcpy(sets + i * 4, &bits, 4);
+          node |= Q_CATEGORICAL;
         } else {
-          const auto& v = per[feat];
-          const auto it = std::lower_bound(v.begin(), v.end(), thr);
-          // filler tests (both subtrees equal) need no real threshold
-          j = (it != v.end() && *it == thr) ? static_cast<uint32_t>(it - v.begin()) : 0u;
+          uint32_t j;
+          if (std::isnan(thr)) {
+            j = 0xFFFFu;  // x < NaN never holds: always right
+          } else {
+            const auto& v = per[feat];
+            const auto it = std::lower_bound(v.begin(), v.end(), thr);
+            // filler tests (both subtrees equal) need no real threshold
+            j = (it != v.end() && *it == thr) ? static_cast<uint32_t>(it - v.begin()) : 0u;
+          }
+          node |= j << 16;
         }
-        const uint32_t node = (j << 16) | ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | feat;
         std::memcpy(dst + i * 4, &node, 4);
       }
       std::memcpy(dst + width * 4, src + width * nb, static_cast<size_t>(width) * es);
     }
+    out.view.q_has_cat     = has_cat ? 1 : 0;
     out.view.q_enabled     = 1;
     out.view.q_n_groups    = static_cast<int32_t>(out.q_groups.size());
     out.view.q_tree_stride = qstride;

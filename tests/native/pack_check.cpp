@@ -140,6 +140,11 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
           q[f] = Q_NAN_CODE;
           continue;
         }
+        if (rec.is_cat) {  // the code of a categorical value is its category
+          const bool in_range = (x >= T(0)) && (x < T(Q_NO_CATEGORY));
+          q[f] = in_range ? static_cast<uint16_t>(static_cast<uint32_t>(x)) : Q_NO_CATEGORY;
+          continue;
+        }
         const uint32_t b = q_bucket_host<T>(x, static_cast<T>(rec.scale),
                                             static_cast<T>(rec.offset), rec.nbm1 + 1);
         uint16_t lo16;
@@ -160,6 +165,12 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
         std::memcpy(&node, t + i * 4, 4);
         const uint32_t qq = q[node & Q_FEATURE_MASK];
         bool right = (static_cast<int32_t>(node) - static_cast<int32_t>(qq << 16)) < 0;
+        if (node & Q_CATEGORICAL) {
+          const size_t es = sizeof(T);
+          uint32_t bits;
+          std::memcpy(&bits, t + (size_t(1) << D) * (4 + es) + i * 4, 4);
+          right = qq < 32u && ((bits >> qq) & 1u);
+        }
         if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) == 0u;
         i = 2 * i + (right ? 1 : 0);
       }

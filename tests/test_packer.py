@@ -73,6 +73,9 @@ def test_complete_forest_dense(pack_check, op):
     info = _check(pack_check, desc, X, "single", "depth_first", "auto")
     assert info[1] == 1 and info[2] == 6  # dense storage, depth 6
     assert info[4] == 20 * 2 * 64
+    # categorical features with small category sets keep the rank-quantised copy: the code of a
+    # categorical value is its category (rows hold negative, fractional and too-large categories)
+    assert info[6] == 1
 
 
 def test_golden_forests_all_layouts(pack_check):
