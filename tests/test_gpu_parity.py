@@ -379,3 +379,65 @@ def test_sharded_prediction_over_available_gpus():
     assert np.array_equal(ids.astype(np.uint32), oracle.predict(desc, X, INFER_LEAF_ID, "single"))
     cls = sh.predict(shards).cpu().numpy()
     assert np.array_equal(cls, np.argmax(proba, axis=1))
+
+
+def test_quantised_categorical_edge_values():
+    """Categorical features on the rank-quantised path: categories that are negative, fractional
+    (truncated), beyond the 32-bit set, huge, infinite or NaN must route like the oracle says."""
+    desc = synthetic_complete_forest(40, 5, 12, seed=9, n_classes=3, n_categorical=4,
+                                     n_categories=32)
+    rng = np.random.default_rng(10)
+    n = 6000
+    X = rng.standard_normal((n, 12)).astype(np.float32)
+    cats = np.array([-1.0, -0.5, 0.0, 0.9, 1.0, 1.5, 30.99, 31.0, 31.5, 32.0, 33.0, 1e6, 4e4,
+                     np.inf, -np.inf, np.nan, 16777216.0, 3e9], np.float32)
+    X[:, :4] = rng.choice(cats, size=(n, 4))
+    X[rng.random((n, 12)) < 0.03] = np.nan
+    for precision in ("single", "double"):
+        fi = _all_kinds(desc, X, precision, "depth_first", "dense")
+        assert fi.describe()["row_quantization"] == 1
+        _all_kinds(desc, X, precision, "depth_first", "dense", quantize_rows=False)
+
+
+def test_load_from_model_files(tmp_path):
+    import json
+
+    from cuml_b200.fil.loaders import save_desc
+    from cuml_b200.fil.treelite_json import to_treelite_json
+
+    desc = random_forest_desc(90, n_trees=12, n_features=7, max_depth=5, categorical=True,
+                              n_outputs=3, postproc="softmax")
+    X = random_rows(11, 400, 7, np.float32, categories=22)
+    want = oracle.predict(desc, X, INFER_DEFAULT, "single")
+    p1 = tmp_path / "forest.npz"
+    save_desc(desc, str(p1))
+    p2 = tmp_path / "treelite_dump.json"
+    p2.write_text(json.dumps(to_treelite_json(desc)))
+    for path, kind in ((p1, None), (p2, "treelite_json"), (p2, None)):
+        fi = ForestInference.load(str(path), model_type=kind, is_classifier=True)
+        np.testing.assert_allclose(fi.predict_proba(X), want, rtol=1e-5, atol=1e-6)
+
+
+def test_optimize_picks_a_chunk_size_and_keeps_results():
+    desc = random_forest_desc(91, n_trees=30, n_features=8, max_depth=6, postproc="sigmoid")
+    fi = ForestInference.load_from_treelite_model(desc, is_classifier=True)
+    X = _dev(random_rows(12, 2000, 8, np.float32), "single")
+    before = fi.predict_proba(X).cpu().numpy()
+    best = fi.optimize(batch_size=512, unique_batches=2, timeout=0.05)
+    assert best in (1, 2, 4, 8, 16, 32) and fi.default_chunk_size == best
+    after = fi.predict_proba(X).cpu().numpy()
+    np.testing.assert_allclose(after, before, rtol=1e-6, atol=1e-7)
+
+
+def test_module_level_constructor_matches_reference_call():
+    # the call cuML makes: python/cuml/cuml/ensemble/randomforest_common.pyx:402-409
+    from cuml_b200 import fil as nvforest
+
+    desc, X, exp = load_golden("rfc_depth8")
+    m = nvforest.load_from_treelite_model(tl_model=desc, device="gpu", layout="breadth_first",
+                                          default_chunk_size=4, align_bytes=128, handle=None)
+    assert "ForestInferenceClassifier" in type(m).__name__
+    assert m.forest.get_dtype() == np.float32
+    np.testing.assert_allclose(m.predict_proba(X), exp["proba"], rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        nvforest.load_from_treelite_model(tl_model=desc, device="cpu")
