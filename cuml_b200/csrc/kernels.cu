@@ -400,16 +400,16 @@ struct DenseWalker {
                                               int64_t row, int lane, uint32_t bars,
                                               uint32_t stages, uint32_t stage_bytes,
                                               uint32_t row_addr, uint32_t stride_b, T* acc_group,
-                                              int R, uint32_t& it, Running<T>& run)
+                                              int R, uint32_t& it, Running<T>& run, int b_begin,
+                                              int b_end)
   {
     const ForestView& f    = p.f;
     const int D            = f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.tree_stride);
     const uint32_t width_b = (1u << D) * TR::NB;  // bytes of the node array of one tree
     const int per_batch    = G * NT;
-    const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
     bool ok                = true;
-    for (int b = 0; b < n_batches; ++b, ++it) {
+    for (int b = b_begin; b < b_end; ++b, ++it) {
       const uint32_t s = it % S;
       if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
       if (ok) {
@@ -458,7 +458,8 @@ struct DenseWalker {
 
 template <typename T, bool CAT, int MODE, int NT>
 __global__ void __launch_bounds__(544, 1)
-dense_kernel(const PredictParams p, const int R, const int G, const int S)
+dense_kernel(const PredictParams p, const int R, const int G, const int S, const int n_splits,
+             T* __restrict__ partial)
 {
   using TR = Traits<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -485,6 +486,10 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
   const int per_batch       = G * NT;
   const uint32_t stage_bytes = per_batch * tstride;
   const int n_batches       = (f.n_trees + per_batch - 1) / per_batch;
+  // small batches split the forest over blockIdx.y: every CTA streams and walks only its share
+  // of the tree batches and leaves raw partial sums for finish_kernel
+  const int b_begin = static_cast<int>(static_cast<int64_t>(n_batches) * blockIdx.y / n_splits);
+  const int b_end   = static_cast<int>(static_cast<int64_t>(n_batches) * (blockIdx.y + 1) / n_splits);
   const int64_t n_tiles     = (p.n_rows + R - 1) / R;
 
   if (threadIdx.x == 0) {
@@ -504,7 +509,7 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
       const unsigned char* src = static_cast<const unsigned char*>(f.nodes);
       uint32_t it              = 0;
       for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-        for (int b = 0; b < n_batches; ++b, ++it) {
+        for (int b = b_begin; b < b_end; ++b, ++it) {
           const uint32_t s   = it % S;
           const uint32_t use = it / S;
           if (use > 0 && !mbar_wait(bars + 8u * (kMaxStages + s), (use - 1) & 1u)) {
@@ -544,22 +549,46 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S)
       if (CAT || nans) {
         ok = DenseWalker<T, CAT, MODE, NT>::template walk<true>(
           p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run);
+          R, it, run, b_begin, b_end);
       } else {
         ok = DenseWalker<T, CAT, MODE, NT>::template walk<false>(
           p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run);
+          R, it, run, b_begin, b_end);
       }
       if (!ok) atomicExch(p.status, 2);
     }
     if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
     consumer_sync(n_ct);
     if (MODE <= MODE_VECTOR) {
-      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+      if (threadIdx.x < R) {
+        if (n_splits == 1) {
+          finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+        } else if (row0 + threadIdx.x < p.n_rows) {
+          // raw sums of this CTA's trees, laid out [split][output][row]
+          for (int c = 0; c < NC; ++c) {
+            T sum = acc[c * R + threadIdx.x];
+            for (int gg = 1; gg < G; ++gg) sum += acc[(gg * NC + c) * R + threadIdx.x];
+            partial[(static_cast<int64_t>(blockIdx.y) * NC + c) * p.n_rows + row0 + threadIdx.x] = sum;
+          }
+        }
+      }
     }
     if (threadIdx.x == 0) flags[0] = 0;
     consumer_sync(n_ct);
   }
+}
+
+// Second step of a split prediction: one thread per row adds the partial sums of the splits in
+// a fixed order and applies averaging, base score, postprocessor and the output conversion.
+// `partial` is laid out [split][output][row], which is the accumulator layout finish_row expects
+// with the row count as the row stride.
+template <typename T>
+__global__ void __launch_bounds__(256)
+finish_kernel(const PredictParams p, T* __restrict__ partial, const int n_splits)
+{
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= p.n_rows) return;
+  finish_row<T>(p, partial, static_cast<int>(p.n_rows), n_splits, static_cast<int>(row), row);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1207,31 +1236,42 @@ int set_smem(K kernel, size_t bytes, std::string& err)
 }
 
 template <typename T, bool CAT, int MODE>
-int launch_dense_mode(const PredictParams& p, const DenseCfg& c, int grid, cudaStream_t stream,
-                      std::string& err)
+int launch_dense_mode(const PredictParams& p, const DenseCfg& c, dim3 grid, int n_splits,
+                      void* partial, cudaStream_t stream, std::string& err)
 {
   int rc;
+  T* part = static_cast<T*>(partial);
   if (c.trees_in_flight == 2) {
     auto k = dense_kernel<T, CAT, MODE, 2>;
     if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;
-    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
+                                                 n_splits, part);
   } else {
     auto k = dense_kernel<T, CAT, MODE, 1>;
     if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;
-    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
+                                                 n_splits, part);
+  }
+  if (n_splits > 1 && MODE <= MODE_VECTOR) {
+    const int blocks = static_cast<int>((p.n_rows + 255) / 256);
+    finish_kernel<T><<<blocks, 256, 0, stream>>>(p, part, n_splits);
   }
   return B2FIL_OK;
 }
 
 template <typename T, bool CAT>
-int launch_dense_cat(const PredictParams& p, int mode, const DenseCfg& c, int grid,
-                     cudaStream_t stream, std::string& err)
+int launch_dense_cat(const PredictParams& p, int mode, const DenseCfg& c, dim3 grid, int n_splits,
+                     void* partial, cudaStream_t stream, std::string& err)
 {
   switch (mode) {
-    case MODE_SCALAR: return launch_dense_mode<T, CAT, MODE_SCALAR>(p, c, grid, stream, err);
-    case MODE_VECTOR: return launch_dense_mode<T, CAT, MODE_VECTOR>(p, c, grid, stream, err);
-    case MODE_PERTREE: return launch_dense_mode<T, CAT, MODE_PERTREE>(p, c, grid, stream, err);
-    default: return launch_dense_mode<T, CAT, MODE_LEAFID>(p, c, grid, stream, err);
+    case MODE_SCALAR:
+      return launch_dense_mode<T, CAT, MODE_SCALAR>(p, c, grid, n_splits, partial, stream, err);
+    case MODE_VECTOR:
+      return launch_dense_mode<T, CAT, MODE_VECTOR>(p, c, grid, n_splits, partial, stream, err);
+    case MODE_PERTREE:
+      return launch_dense_mode<T, CAT, MODE_PERTREE>(p, c, grid, n_splits, partial, stream, err);
+    default:
+      return launch_dense_mode<T, CAT, MODE_LEAFID>(p, c, grid, n_splits, partial, stream, err);
   }
 }
 
@@ -1520,7 +1560,11 @@ int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
 bool dense_config(int depth, int precision, int n_features, int n_outputs, bool reduce_kind,
                   int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
 {
-  const int want = pick_rows_per_tile(n_rows, chunk_size, sm_count);
+  int want = pick_rows_per_tile(n_rows, chunk_size, sm_count);
+  // small batches get their parallelism from splitting the forest across CTAs, not from many
+  // small row tiles: every tile has to stream the trees it walks, so fewer, larger tiles win
+  if (chunk_size <= 0 && n_rows <= static_cast<int64_t>(64) * sm_count)
+    want = n_rows <= 32 ? 32 : (n_rows <= 64 ? 64 : 128);
   for (int R = want; R >= 32; R /= 2) {
     const int rw = R / 32;
     for (int G = 16 / rw; G >= 1; G /= 2) {
@@ -1568,8 +1612,11 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
   const bool reduce = mode <= MODE_VECTOR;
   int rc            = B2FIL_OK;
   // the pre-pass indexes a row tile with 32-bit element offsets
+  // (small batches skip the pre-pass: with fewer 128-row tiles than half the SMs the forest is
+  // split across CTAs of the plain dense kernel instead, which is what bounds their latency)
   if ((f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled &&
-      p.row_stride < (int64_t(1) << 22)) {
+      p.row_stride < (int64_t(1) << 22) &&
+      pool != nullptr && (chunk_size > 0 || (p.n_rows + 127) / 128 * 2 > sm_count)) {
     rc = launch_dense_q(p, mode, chunk_size, sm_count, stream, pool, err, launches);
     if (rc != B2FIL_OK) return rc;
     const cudaError_t e = cudaGetLastError();
@@ -1588,14 +1635,40 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
       return B2FIL_ERR_UNSUPPORTED;
     }
     const int64_t n_tiles = (p.n_rows + c.rows_per_tile - 1) / c.rows_per_tile;
-    const int grid        = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
-    if (precision == B2FIL_F32) {
-      rc = f.has_categorical ? launch_dense_cat<float, true>(p, mode, c, grid, stream, err)
-                             : launch_dense_cat<float, false>(p, mode, c, grid, stream, err);
-    } else {
-      rc = f.has_categorical ? launch_dense_cat<double, true>(p, mode, c, grid, stream, err)
-                             : launch_dense_cat<double, false>(p, mode, c, grid, stream, err);
+    const int gx          = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
+    // batches with fewer row tiles than SMs split the forest across CTAs (blockIdx.y): a CTA then
+    // streams only its share of the trees; reduced outputs take a tiny second kernel
+    const int per_batch = c.tree_groups * c.trees_in_flight;
+    const int n_batches = (f.n_trees + per_batch - 1) / per_batch;
+    int n_splits        = 1;
+    if (n_tiles * 2 <= sm_count && (pool != nullptr || !reduce)) {  // no pool: never allocate
+      // one wave of CTAs: tiles x splits fills the SMs once
+      n_splits = static_cast<int>(std::min<int64_t>(n_batches, sm_count / n_tiles));
+      n_splits = std::max(1, n_splits);
     }
+    void* partial = nullptr;
+    if (n_splits > 1 && reduce) {
+      const size_t es    = precision == B2FIL_F32 ? 4 : 8;
+      const size_t bytes = static_cast<size_t>(n_splits) * f.n_outputs * p.n_rows * es;
+      const cudaError_t e = cudaMallocFromPoolAsync(&partial, bytes, pool, stream);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        err = std::string("scratch allocation for split prediction failed: ") + cudaGetErrorString(e);
+        return e == cudaErrorMemoryAllocation ? B2FIL_ERR_NO_MEMORY : B2FIL_ERR_CUDA;
+      }
+    }
+    const dim3 grid(gx, n_splits);
+    if (precision == B2FIL_F32) {
+      rc = f.has_categorical
+             ? launch_dense_cat<float, true>(p, mode, c, grid, n_splits, partial, stream, err)
+             : launch_dense_cat<float, false>(p, mode, c, grid, n_splits, partial, stream, err);
+    } else {
+      rc = f.has_categorical
+             ? launch_dense_cat<double, true>(p, mode, c, grid, n_splits, partial, stream, err)
+             : launch_dense_cat<double, false>(p, mode, c, grid, n_splits, partial, stream, err);
+    }
+    if (partial) cudaFreeAsync(partial, stream);
+    if (launches && n_splits > 1 && reduce) ++*launches;
   } else {
     const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
     int R           = pick_rows_per_tile(p.n_rows, chunk_size, sm_count);

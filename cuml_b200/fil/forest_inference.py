@@ -250,7 +250,7 @@ class ForestInference:
             tdt = torch.float32 if dt == np.float32 else torch.float64
             if X.device.index != f.info.device_id:
                 raise ValueError(f"X is on {X.device}, the forest on cuda:{f.info.device_id}")
-            Xd = X.to(tdt)
+            Xd = X if X.dtype == tdt else X.to(tdt)
             if Xd.stride(1) != 1:
                 Xd = Xd.contiguous()
             todt = {np.int32: torch.int32, np.float32: torch.float32,
@@ -262,10 +262,12 @@ class ForestInference:
                     raise ValueError("preds has the wrong type, shape, dtype or layout")
             else:
                 out = torch.empty(shape, dtype=todt, device=X.device)
-            with torch.cuda.device(X.device):
-                stream = torch.cuda.current_stream().cuda_stream
-                _lib.check(lib.b2fil_predict(f.handle, kind, Xd.data_ptr(), n, Xd.stride(0),
-                                             out.data_ptr(), cs, float(threshold), stream))
+            # the library makes the forest's device current itself; only the stream is needed
+            stream = torch.cuda.current_stream(X.device).cuda_stream
+            rc = lib.b2fil_predict(f.handle, kind, Xd.data_ptr(), n, Xd.stride(0),
+                                   out.data_ptr(), cs, float(threshold), stream)
+            if rc != 0:
+                _lib.check(rc)
             if want == "numpy":
                 return out.cpu().numpy()
             return out

@@ -198,9 +198,10 @@ int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind);
  * b2fil_output_elems_per_row() elements (precision type; uint32 for LEAF_ID, int32 for CLASS).
  * chunk_size 0 = the forest's default.  `threshold` is the binary decision threshold of
  * B2FIL_INFER_CLASS for one-output classifiers.  Enqueues on cuda_stream (NULL = default stream)
- * of the forest's device and does not synchronise.  Forests with row_quantization = 1 keep the
- * 16-bit rank image of the batch in stream-ordered scratch from a memory pool owned by the forest
- * (cached between calls); other forests use no scratch.
+ * of the forest's device and does not synchronise.  Two cases take stream-ordered scratch from a
+ * memory pool owned by the forest (cached between calls): forests with row_quantization = 1 keep
+ * the 16-bit rank image of the batch there, and small batches of dense forests (fewer 128-row
+ * tiles than half the SMs) keep the partial sums of the CTAs that share the forest there.
  * Replaces forest_model.predict(...) (cpp/tests/sg/rf_test.cu:268-275). */
 int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int64_t n_rows,
                   int64_t row_stride, void* out_dev, int chunk_size, double threshold,
@@ -229,8 +230,9 @@ int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int6
  *    streams, two threads) race on it; issue them on one stream or serialise them yourself;
  *  - the first call on each device looks up the array's device address (with that device current)
  *    and caches it; make that first call before any stream capture is started;
- *  - forests that predict without scratch (sparse storage, categorical tests, row_quantization =
- *    0) are simply forwarded to the ordinary path, which allocates nothing for them. */
+ *  - forests that predict without rank scratch (sparse storage, row_quantization = 0) are
+ *    forwarded to the ordinary kernels with the forest-splitting of small batches switched off,
+ *    so nothing is allocated for them either. */
 int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const void* X_dev,
                                 int64_t n_rows, int64_t row_stride, void* out_dev, int chunk_size,
                                 double threshold, void* cuda_stream);

@@ -152,7 +152,7 @@ def test_postprocessors_multiclass(post):
         _all_kinds(desc, X, "single", "depth_first", storage)
 
 
-@pytest.mark.parametrize("n_rows", [0, 1, 31, 32, 33, 127, 129, 1000])
+@pytest.mark.parametrize("n_rows", [0, 1, 31, 32, 33, 127, 129, 1000, 2368, 2369, 2400, 5000])
 def test_ragged_batch_sizes(n_rows):
     desc = random_forest_desc(50, n_trees=9, max_depth=5, n_outputs=2, postproc="softmax")
     X = random_rows(7, max(n_rows, 1), desc.n_features, np.float32)[:n_rows]
@@ -341,9 +341,15 @@ def test_status_word_and_launch_counter(lib):
     # with rank quantisation a prediction is a pre-pass plus a traversal kernel per row chunk
     fq = ForestInference.load_from_treelite_model(desc, storage="dense")
     before = lib.b2fil_kernel_launches()
-    fq.apply(_dev(random_rows(1, 100, desc.n_features), "single"))
+    fq.apply(_dev(random_rows(1, 20000, desc.n_features), "single"))
     _torch().cuda.synchronize()
     assert lib.b2fil_kernel_launches() == before + 2
+    # a small batch splits the forest over CTAs: walk + finish kernel for reduced outputs
+    before = lib.b2fil_kernel_launches()
+    fq.predict_proba(_dev(random_rows(1, 100, desc.n_features), "single")) if fq.is_classifier \
+        else fq.predict(_dev(random_rows(1, 100, desc.n_features), "single"))
+    _torch().cuda.synchronize()
+    assert lib.b2fil_kernel_launches() in (before + 1, before + 2)
     st = C.c_int32(-1)
     assert lib.b2fil_forest_status(fi.forest.handle, C.byref(st)) == 0 and st.value == 0
 
@@ -441,3 +447,32 @@ def test_module_level_constructor_matches_reference_call():
     np.testing.assert_allclose(m.predict_proba(X), exp["proba"], rtol=1e-5, atol=1e-6)
     with pytest.raises(ValueError):
         nvforest.load_from_treelite_model(tl_model=desc, device="cpu")
+
+
+def test_more_than_2_to_31_input_elements():
+    """1,000,000 x 2,150 fp32 inputs hold more than 2^31 elements; the reference runs this shape
+    only to see that nothing overflows (cpp/tests/sg/rf_test.cu:908-955).  Here a sample of rows
+    from the far end of the batch is also checked against the oracle."""
+    torch = _torch()
+    n, nf = 1_000_000, 2150
+    desc = random_forest_desc(95, n_trees=10, n_features=nf, max_depth=6, n_outputs=2,
+                              vector=True, average=True)
+    X = torch.empty((n, nf), device="cuda:0", dtype=torch.float32)
+    g = torch.Generator(device="cuda:0")
+    g.manual_seed(1)
+    for b in range(0, n, 100_000):
+        X[b:b + 100_000] = torch.randn((100_000, nf), generator=g, device="cuda:0")
+    for quantize_rows in (True, False):
+        fi = ForestInference.load_from_treelite_model(desc, quantize_rows=quantize_rows)
+        proba = fi.predict_proba(X)
+        ids = fi.apply(X)
+        idx = torch.cat([torch.arange(0, 64), torch.arange(n - 64, n)]).to("cuda:0")
+        Xs = X[idx].cpu().numpy()
+        np.testing.assert_allclose(proba[idx].cpu().numpy(),
+                                   oracle.predict(desc, Xs, INFER_DEFAULT, "single"),
+                                   rtol=1e-5, atol=1e-6)
+        assert np.array_equal(ids[idx].cpu().numpy().astype(np.uint32),
+                              oracle.predict(desc, Xs, INFER_LEAF_ID, "single"))
+        del proba, ids
+    del X
+    torch.cuda.empty_cache()
