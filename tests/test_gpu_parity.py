@@ -432,7 +432,8 @@ def test_optimize_picks_a_chunk_size_and_keeps_results():
     best = fi.optimize(batch_size=512, unique_batches=2, timeout=0.05)
     assert best in (1, 2, 4, 8, 16, 32) and fi.default_chunk_size == best
     after = fi.predict_proba(X).cpu().numpy()
-    np.testing.assert_allclose(after, before, rtol=1e-6, atol=1e-7)
+    # another chunk size means another tile shape and summation order: same tolerance as parity
+    np.testing.assert_allclose(after, before, rtol=1e-5, atol=1e-6)
 
 
 def test_module_level_constructor_matches_reference_call():
