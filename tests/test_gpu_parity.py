@@ -477,3 +477,61 @@ def test_more_than_2_to_31_input_elements():
         del proba, ids
     del X
     torch.cuda.empty_cache()
+
+
+def test_estimator_style_callers_against_sklearn():
+    """The wrappers that use the library the way cuML's estimators do: labels, log-probabilities,
+    scores, out-of-bag votes through predict_per_tree, isolation-forest scores."""
+    import pickle
+
+    from sklearn.datasets import make_classification, make_regression
+    from sklearn.ensemble import IsolationForest as SkIF
+    from sklearn.ensemble import RandomForestClassifier as SkRFC
+    from sklearn.ensemble import RandomForestRegressor as SkRFR
+
+    from cuml_b200.ensemble import IsolationForest, RandomForestClassifier, RandomForestRegressor
+
+    X, y = make_classification(n_samples=1500, n_features=12, n_informative=6, n_classes=3,
+                               random_state=0)
+    X = X.astype(np.float32)
+    y = np.array(["a", "b", "c"])[y]
+    sk = SkRFC(n_estimators=25, max_depth=7, random_state=0).fit(X, y)
+    m = RandomForestClassifier.from_sklearn(sk)
+    proba = sk.predict_proba(X)
+    np.testing.assert_allclose(m.predict_proba(X), proba, rtol=1e-5, atol=1e-6)
+    top2 = np.sort(proba, axis=1)[:, -2:]
+    safe = top2[:, 1] - top2[:, 0] > 1e-4
+    assert np.array_equal(m.predict(X)[safe], sk.predict(X)[safe])
+    with np.errstate(divide="ignore"):
+        np.testing.assert_allclose(m.predict_log_proba(X), np.log(proba), rtol=1e-4, atol=1e-5)
+    assert abs(m.score(X, y) - sk.score(X, y)) < 5e-3
+    assert np.array_equal(m.predict(X, layout="breadth_first", default_chunk_size=2)[safe],
+                          sk.predict(X)[safe])
+    m2 = pickle.loads(pickle.dumps(m))
+    np.testing.assert_allclose(m2.predict_proba(X), proba, rtol=1e-5, atol=1e-6)
+    # out-of-bag: with no row in any bag the OOB vote is the plain forest average
+    oob = m.oob_decision_function(X, np.zeros((25, X.shape[0]), bool))
+    np.testing.assert_allclose(oob, proba, rtol=1e-5, atol=1e-6)
+
+    Xr, yr = make_regression(n_samples=1200, n_features=10, noise=0.1, random_state=0)
+    Xr = Xr.astype(np.float32)
+    skr = SkRFR(n_estimators=20, max_depth=9, random_state=0).fit(Xr, yr)
+    r = RandomForestRegressor.from_sklearn(skr, precision="double")
+    pred = r.predict(Xr.astype(np.float64))
+    assert pred.ndim == 1
+    np.testing.assert_allclose(pred, skr.predict(Xr), rtol=1e-10, atol=1e-10)
+    assert abs(r.score(Xr.astype(np.float64), yr) - skr.score(Xr, yr)) < 1e-9
+
+    rng = np.random.default_rng(0)
+    Xi = rng.standard_normal((800, 6)).astype(np.float32)
+    Xi[:20] += 6.0
+    ski = SkIF(n_estimators=50, random_state=0).fit(Xi)
+    iso = IsolationForest.from_sklearn(ski)
+    # the reference's own boundary test uses rtol=1e-5, atol=1e-6
+    # (python/cuml/tests/test_isolation_forest.py:751-762)
+    np.testing.assert_allclose(iso.score_samples(Xi), ski.score_samples(Xi), rtol=1e-5, atol=1e-6)
+    d = ski.decision_function(Xi)
+    safe = np.abs(d) > 1e-5
+    assert np.array_equal(iso.predict(Xi)[safe], ski.predict(Xi)[safe])
+    one = iso.score_samples(Xi[:1])  # single-sample edge case (test_isolation_forest.py:765-776)
+    np.testing.assert_allclose(one, ski.score_samples(Xi[:1]), rtol=1e-5, atol=1e-6)
