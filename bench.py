@@ -35,10 +35,10 @@ ROWS_PER_GPU = 10_000_000
 BYTES_PER_ROW = N_FEATURES * 4 + 2 * 4
 WORKLOAD = "gbdt_1000x_depth8_256f_fp32_sigmoid_10M_rows"
 # dram__bytes_read.sum + dram__bytes_write.sum per row of the two kernels of a prediction, from
-# the ncu captures of a 1 M-row case summarised under profiles/ (quantise 1332 B + dense_q 533 B;
-# ncu flushes L2 before every launch, so this is an upper bound); traffic grows in proportion to
+# the ncu captures of a 1 M-row case summarised under profiles/ (quantise 1697 B + dense_q 525 B;
+# the rank image of a chunk is larger than L2 and goes through HBM); traffic grows in proportion to
 # the rows, so it is scaled to the batch
-NCU_TRAFFIC_BYTES_PER_ROW = 1865
+NCU_TRAFFIC_BYTES_PER_ROW = 2222
 
 
 def measured_peak():
@@ -317,7 +317,7 @@ def run_ours(args):
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * n
                                      if NCU_TRAFFIC_BYTES_PER_ROW else None),
-                         "kernel": "quantise_kernel<float> + dense_q_kernel<float,MODE_SCALAR,2,8>",
+                         "kernel": "quantise_kernel<float> + dense_q_kernel<float,MODE_SCALAR,4,8,false>",
                          "kernel_ms": k_ms, "algorithmic_bytes_per_row": BYTES_PER_ROW},
             "e2e": e2e,
             "gpu_launches": int(launches),
