@@ -213,10 +213,11 @@ def measure_e2e(fi, X, out, n, world, dev, barrier, args):
     import torch
     import torch.distributed as dist
 
+    # every rank pins its own host copy: keep it below a quarter of the rank's share of free RAM
     e2e_rows = n
     need = e2e_rows * N_FEATURES * 4
     avail = psutil.virtual_memory().available / max(1, world)
-    while need * 2 > avail and e2e_rows > 100_000:
+    while need * 4 > avail and e2e_rows > 100_000:
         e2e_rows //= 2
         need = e2e_rows * N_FEATURES * 4
     Xh = torch.empty((e2e_rows, N_FEATURES), dtype=torch.float32, pin_memory=True)
