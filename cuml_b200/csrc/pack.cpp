@@ -399,6 +399,7 @@ struct Packer {
   {
     const int F = d.n_features;
     if (F > static_cast<int>(Q_FEATURE_MASK) + 1) return false;
+    if (D < 1) return false;  // forests of single leaves have nothing to rank
     if (has_cat && !cat_inline) return false;  // category sets must fit 32 bits
     const int nt = d.n_trees;
     // 1. distinct thresholds per feature, in the forest precision, after normalisation to `<`;
