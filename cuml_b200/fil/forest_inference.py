@@ -138,6 +138,16 @@ class ForestInference:
             desc, F32 if prec == "single" else F64, LAYOUTS[self.layout], STORAGES[self.storage],
             int(self.align_bytes or 0), self.device_id, int(self.default_chunk_size or 0),
             0 if self.quantize_rows else 1)
+        self._cache_facts()
+
+    def _cache_facts(self):
+        """Plain-Python copies of what every call needs (ctypes field reads are slow)."""
+        i = self._forest.info
+        self._nf, self._nt, self._k = int(i.n_features), int(i.n_trees), int(i.n_outputs)
+        self._vec = int(i.leaf_vector_len) > 1
+        self._dev = int(i.device_id)
+        self._np_dt = np.float32 if i.precision == F32 else np.float64
+        self._torch_dt = None  # filled on the first device call (torch is imported lazily)
 
     @classmethod
     def load_from_treelite_model(cls, tl_model, **kwargs) -> "ForestInference":
@@ -174,7 +184,7 @@ class ForestInference:
 
     @property
     def n_outputs(self) -> int:
-        return int(self.forest.info.n_outputs)
+        return self._k if self._forest is not None else int(self.forest.info.n_outputs)
 
     @property
     def n_trees(self) -> int:
@@ -200,15 +210,14 @@ class ForestInference:
 
     def __setstate__(self, st):
         self.__dict__.update(st)
+        self._torch_dt = None
         if st.get("_desc") is not None:
             self._desc = ForestDesc.from_dict(st["_desc"])
             self._build()
 
     # -- prediction -----------------------------------------------------------------------------
     def _out_spec(self, kind: int, n: int):
-        f = self.forest
-        k, nt = f.info.n_outputs, f.info.n_trees
-        dt = f.get_dtype()
+        k, nt, dt = self._k, self._nt, self._np_dt
         if kind == INFER_LEAF_ID:
             return (n, nt), np.int32
         if kind == INFER_CLASS:
@@ -216,13 +225,13 @@ class ForestInference:
         if kind == INFER_PROBA2:
             return (n, 2), dt
         if kind == INFER_PER_TREE:
-            return ((n, nt, k) if f.info.leaf_vector_len > 1 else (n, nt)), dt
+            return ((n, nt, k) if self._vec else (n, nt)), dt
         return (n, k), dt
 
     def _run(self, X, kind: int, chunk_size: Optional[int], threshold: float = 0.5, preds=None):
         lib = _lib.load()
         f = self.forest
-        dt = f.get_dtype()
+        dt = self._np_dt
         cs = int(chunk_size or self.default_chunk_size or 0)
         if cs and (cs < 1 or cs & (cs - 1)):
             raise ValueError("chunk_size must be a positive power of two")
@@ -233,28 +242,30 @@ class ForestInference:
             if isinstance(X, torch.Tensor):
                 is_torch = True
             elif hasattr(X, "__cuda_array_interface__"):
-                X = torch.as_tensor(X, device=f"cuda:{f.info.device_id}")
+                X = torch.as_tensor(X, device=f"cuda:{self._dev}")
                 is_torch = True
             else:
                 X = np.asarray(X)
         if X.ndim == 1:
             X = X.reshape(1, -1)
-        if X.ndim != 2 or X.shape[1] != f.info.n_features:
-            raise ValueError(f"X must have shape (n_rows, {f.info.n_features}), got {tuple(X.shape)}")
+        if X.ndim != 2 or X.shape[1] != self._nf:
+            raise ValueError(f"X must have shape (n_rows, {self._nf}), got {tuple(X.shape)}")
         n = int(X.shape[0])
         shape, odt = self._out_spec(kind, n)
         want = self.output_type
         if is_torch and X.is_cuda:
             # device path: cast / make row-major like check_inputs(order="C") of the reference
             # (python/cuml/cuml/ensemble/randomforestclassifier.py:330-336)
-            tdt = torch.float32 if dt == np.float32 else torch.float64
-            if X.device.index != f.info.device_id:
-                raise ValueError(f"X is on {X.device}, the forest on cuda:{f.info.device_id}")
+            if self._torch_dt is None:
+                self._torch_dt = {np.float32: torch.float32, np.float64: torch.float64,
+                                  np.int32: torch.int32}
+            tdt = self._torch_dt[dt]
+            if X.get_device() != self._dev:
+                raise ValueError(f"X is on {X.device}, the forest on cuda:{self._dev}")
             Xd = X if X.dtype == tdt else X.to(tdt)
             if Xd.stride(1) != 1:
                 Xd = Xd.contiguous()
-            todt = {np.int32: torch.int32, np.float32: torch.float32,
-                    np.float64: torch.float64}[odt]
+            todt = self._torch_dt[odt]
             if preds is not None:
                 out = preds
                 if (not isinstance(out, torch.Tensor) or tuple(out.shape) != shape or
