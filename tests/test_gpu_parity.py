@@ -563,3 +563,20 @@ def test_estimator_style_callers_against_sklearn():
     assert np.array_equal(iso.predict(Xi)[safe], ski.predict(Xi)[safe])
     one = iso.score_samples(Xi[:1])  # single-sample edge case (test_isolation_forest.py:765-776)
     np.testing.assert_allclose(one, ski.score_samples(Xi[:1]), rtol=1e-5, atol=1e-6)
+
+
+def test_graph_replay_of_a_small_batch():
+    """A small batch recorded once as a CUDA graph and replayed gives the same answers as direct
+    calls, for new inputs written into the graph's static buffer."""
+    torch = _torch()
+    desc = synthetic_complete_forest(200, 6, 32, seed=11)
+    fi = ForestInference.load_from_treelite_model(desc)
+    graphed = fi.capture_graph(512, "predict_proba")
+    for seed in (1, 2, 3):
+        X = torch.as_tensor(random_rows(seed, 512, 32, np.float32, nan_frac=0.02), device="cuda:0")
+        got = graphed(X).clone()
+        want = fi.predict_proba(X)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), rtol=1e-6, atol=1e-7)
+    with pytest.raises(ValueError):
+        graphed(torch.zeros((100, 32), device="cuda:0"))
