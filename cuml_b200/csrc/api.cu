@@ -485,6 +485,12 @@ int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer
                                       row_stride, out_dev0);
     if (rc != B2FIL_OK) return rc;
   }
+  for (int i = 0; i < n_devices; ++i) {
+    for (int j = 0; j < i; ++j) {
+      if (forests[i] == forests[j] || forests[i]->device == forests[j]->device)
+        return set_error(B2FIL_ERR_INVALID_ARG, "every shard needs its own forest on its own device");
+    }
+  }
   b2fil_forest* f0       = forests[0];
   const size_t out_row_b = static_cast<size_t>(out_elems(f0, infer_kind)) * out_elem_bytes(f0, infer_kind);
   // every device predicts its shard on its own stream; shards of devices other than the first
