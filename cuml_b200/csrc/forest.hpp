@@ -67,11 +67,14 @@ struct SparseNode16D {  // fp64
 // For every feature the distinct thresholds of the forest are sorted: T[0] < T[1] < ...  The rank
 // of a value, r(x) = #{i : T[i] <= x}, decides every test on that feature exactly:
 //     x < T[j]  <=>  r(x) <= j.
-// A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x7FFF); the traversal kernel
+// A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x3FFF); the traversal kernel
 // then reads 2-byte values and 4-byte nodes
-//     bits 31..16: j (0xFFFF = never left)   bit 15: missing goes left   bit 14: categorical
-//     bits 13..0: feature
-// so a test is one signed subtraction: right <=> int(node) - (rank << 16) < 0.
+//     bits 31..17: j (0x7FFF = never left)   bit 16: missing goes left
+//     bits 15..2: feature                    bit 0: categorical
+// so a test is one signed subtraction: right <=> int(node) - (rank << 17) < 0 (the flag in bit 16
+// is below the weight of one rank and cannot change the sign), and the low half is the feature
+// times four: one 16-bit x 8-bit dot-product instruction scales it by a quarter of the byte
+// stride between features and adds the row's address.
 // Categorical features (every test on them is categorical, every listed category below 32) keep
 // their place in the same scheme: the "rank" of a value is its category (Q_NO_CATEGORY when it is
 // negative, fractional-truncated out of range or too large), and a categorical node looks its
@@ -93,12 +96,17 @@ struct QFeature {      // host-side table of one feature
   double scale;        // bucket(x) = fma(x, scale, offset) evaluated in the forest precision
   double offset;
 };
-// Device tables are grouped: consecutive features whose tables fit one CTA's shared memory form a
-// group, stored as one contiguous blob that the pre-pass pulls in with a single bulk copy:
-//   [kQMaxGroupFeatures x QFeatRec][per feature: bucket table (uint16), thresholds + NaN padding]
+// Device tables are grouped: a power-of-two run of GF consecutive features whose tables fit one
+// CTA's shared memory forms a group, stored as one contiguous blob that the pre-pass pulls in with
+// a single bulk copy:
+//   [kQMaxGroupFeatures x QFeatRec][bucket tables (uint16)][thresholds + NaN padding]
+// Both tables are interleaved across the group: entry k of the group's i-th feature sits at
+// element k * GF + i, and every feature's columns are padded to the longest table of the group
+// (zeros / NaN).  The lanes of a warp hold one feature each, so whatever entries they probe they
+// read different shared-memory banks.
 struct QFeatRec {      // 32 bytes
-  uint32_t lut_off;    // byte offsets from the start of the blob
-  uint32_t thr_off;
+  uint32_t lut_off;    // byte offset of entry 0 from the start of the blob; entry k: + k * GF * 2
+  uint32_t thr_off;    // same for the thresholds; entry k: + k * GF * sizeof(T)
   uint32_t nbm1;       // n_buckets - 1
   uint32_t is_cat;     // 1: the value's code is its category, no table lookup
   double scale, offset;
@@ -110,12 +118,16 @@ struct QGroup {        // 32 bytes
   uint32_t steps;      // halvings of the window search, shared by the group's features
   uint32_t pad[3];
 };
-constexpr uint32_t Q_NAN_CODE     = 0x7FFFu;
-constexpr uint32_t Q_MAX_RANK     = 0x7FFEu;
-constexpr uint32_t Q_NO_CATEGORY  = 0x7FFEu;
-constexpr uint32_t Q_FEATURE_MASK = 0x3FFFu;
-constexpr uint32_t Q_CATEGORICAL  = 0x4000u;
-constexpr uint32_t Q_DEFAULT_LEFT = 0x8000u;
+constexpr uint32_t Q_NAN_CODE      = 0x3FFFu;
+constexpr uint32_t Q_MAX_RANK      = 0x3FFEu;
+constexpr uint32_t Q_NO_CATEGORY   = 0x3FFEu;
+constexpr uint32_t Q_MAX_FEATURES  = 0x4000u;
+constexpr uint32_t Q_FEATURE_FIELD = 0xFFFCu;  // feature << 2
+constexpr uint32_t Q_FEATURE_SHIFT = 2;
+constexpr uint32_t Q_CATEGORICAL   = 0x1u;
+constexpr uint32_t Q_DEFAULT_LEFT  = 0x10000u;
+constexpr uint32_t Q_RANK_SHIFT    = 17;
+constexpr uint32_t Q_NEVER_LEFT    = 0x7FFFu;  // j of a test that no value passes
 
 enum NodeFormat : int32_t {
   FMT_DENSE_F   = 0,
@@ -202,7 +214,7 @@ inline uint32_t q_bucket_host(T x, T scale, T offset, uint32_t n_buckets)
 }
 
 // Shared memory the quantisation kernel may spend on the tables of one feature group.
-constexpr uint32_t kQGroupSmemBudget = 200 * 1024;
+constexpr uint32_t kQGroupSmemBudget = 208 * 1024;
 constexpr uint32_t kQMaxGroupFeatures = 32;
 
 // Validate `desc`, normalise its tests and lay its nodes out.  Returns B2FIL_OK or an error code

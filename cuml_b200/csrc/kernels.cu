@@ -36,6 +36,9 @@
 namespace b2fil {
 namespace {
 
+#ifndef B2FIL_SPIN_NS
+#define B2FIL_SPIN_NS 256  // sleep between two tries of a bounded mbarrier wait
+#endif
 constexpr uint32_t kSpinLimit = 1u << 22;  // tries of a bounded mbarrier wait
 constexpr int kBarBytes       = 256;       // room for the mbarriers at the start of shared memory
 constexpr int kMaxStages      = 8;
@@ -85,10 +88,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     // a waiting warp must not compete for issue slots with the warps that are walking trees
-    __nanosleep(256);
+#if B2FIL_SPIN_NS > 0
+    __nanosleep(B2FIL_SPIN_NS);
+#endif
   }
   return false;
 }
+// Position in a ring of S stages: the stage index and the parity of its current use, advanced
+// without a division.
+struct RingPos {
+  uint32_t stage = 0, phase = 0;
+  __device__ __forceinline__ void advance(int S)
+  {
+    if (++stage == static_cast<uint32_t>(S)) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
 // Bulk asynchronous copy global -> shared memory of this CTA, completing `bytes` on `bar`.
 // Both addresses are 16-byte aligned and `bytes` is a multiple of 16.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
@@ -139,6 +157,20 @@ struct Traits<float> {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
   }
+  template <uint32_t OFF>
+  static __device__ __forceinline__ float ld_real_at(uint32_t a)  // [a + OFF], OFF an immediate
+  {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
+    return v;
+  }
+  // a += inc when t <= x (false for NaN), as one predicated add
+  static __device__ __forceinline__ void add_if_le(uint32_t& a, float t, float x, uint32_t inc)
+  {
+    asm("{\n.reg .pred p;\nsetp.le.f32 p, %1, %2;\n@p add.u32 %0, %0, %3;\n}"
+        : "+r"(a)
+        : "f"(t), "f"(x), "r"(inc));
+  }
   static __device__ __forceinline__ void st_real(uint32_t a, float v)
   {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
@@ -172,6 +204,19 @@ struct Traits<double> {
     double v;
     asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(a));
     return v;
+  }
+  template <uint32_t OFF>
+  static __device__ __forceinline__ double ld_real_at(uint32_t a)
+  {
+    double v;
+    asm volatile("ld.shared.f64 %0, [%1+%2];" : "=d"(v) : "r"(a), "n"(OFF));
+    return v;
+  }
+  static __device__ __forceinline__ void add_if_le(uint32_t& a, double t, double x, uint32_t inc)
+  {
+    asm("{\n.reg .pred p;\nsetp.le.f64 p, %1, %2;\n@p add.u32 %0, %0, %3;\n}"
+        : "+r"(a)
+        : "d"(t), "d"(x), "r"(inc));
   }
   static __device__ __forceinline__ void st_real(uint32_t a, double v)
   {
@@ -400,7 +445,7 @@ struct DenseWalker {
                                               int64_t row, int lane, uint32_t bars,
                                               uint32_t stages, uint32_t stage_bytes,
                                               uint32_t row_addr, uint32_t stride_b, T* acc_group,
-                                              int R, uint32_t& it, Running<T>& run, int b_begin,
+                                              int R, RingPos& pos, Running<T>& run, int b_begin,
                                               int b_end)
   {
     const ForestView& f    = p.f;
@@ -409,9 +454,9 @@ struct DenseWalker {
     const uint32_t width_b = (1u << D) * TR::NB;  // bytes of the node array of one tree
     const int per_batch    = G * NT;
     bool ok                = true;
-    for (int b = b_begin; b < b_end; ++b, ++it) {
-      const uint32_t s = it % S;
-      if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
+    for (int b = b_begin; b < b_end; ++b) {
+      const uint32_t s = pos.stage;
+      if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
       if (ok) {
         const int first = b * per_batch + g * NT;
         const int n_act = min(NT, f.n_trees - first);
@@ -451,6 +496,7 @@ struct DenseWalker {
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
+      pos.advance(S);
     }
     return ok;
   }
@@ -507,12 +553,12 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
     // ---- producer: one thread streams tree batches into the stage ring ----------------------
     if (lane == 0) {
       const unsigned char* src = static_cast<const unsigned char*>(f.nodes);
-      uint32_t it              = 0;
+      RingPos pos;
+      bool primed = false;  // every stage has been filled once
       for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-        for (int b = b_begin; b < b_end; ++b, ++it) {
-          const uint32_t s   = it % S;
-          const uint32_t use = it / S;
-          if (use > 0 && !mbar_wait(bars + 8u * (kMaxStages + s), (use - 1) & 1u)) {
+        for (int b = b_begin; b < b_end; ++b) {
+          const uint32_t s = pos.stage;
+          if (primed && !mbar_wait(bars + 8u * (kMaxStages + s), pos.phase ^ 1u)) {
             atomicExch(p.status, 1);
             return;
           }
@@ -522,6 +568,8 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
           mbar_expect_tx(bars + 8u * s, bytes);
           bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
                         bytes, bars + 8u * s);
+          pos.advance(S);
+          if (pos.stage == 0) primed = true;
         }
       }
     }
@@ -533,7 +581,7 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
   const int r           = (warp % rw) * 32 + lane;
   T* acc_group          = acc + static_cast<size_t>(g) * NC * R;
   const uint32_t row_addr = tile + r * TR::ES;
-  uint32_t it           = 0;
+  RingPos pos;
   bool ok               = true;
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     const int64_t row0 = t * R;
@@ -549,11 +597,11 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
       if (CAT || nans) {
         ok = DenseWalker<T, CAT, MODE, NT>::template walk<true>(
           p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run, b_begin, b_end);
+          R, pos, run, b_begin, b_end);
       } else {
         ok = DenseWalker<T, CAT, MODE, NT>::template walk<false>(
           p, G, S, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b, acc_group,
-          R, it, run, b_begin, b_end);
+          R, pos, run, b_begin, b_end);
       }
       if (!ok) atomicExch(p.status, 2);
     }
@@ -594,15 +642,14 @@ finish_kernel(const PredictParams p, T* __restrict__ partial, const int n_splits
 // ---------------------------------------------------------------------------------------------
 // RANK QUANTISATION of rows (pre-pass of the quantised dense kernel)
 // ---------------------------------------------------------------------------------------------
-// One CTA owns one feature group: the group's blob (feature records, bucket tables, sorted
-// thresholds) arrives in shared memory with one bulk copy, then the CTA loops over row tiles.
-// The group size GF is a power of two that divides the thread count, so a thread keeps one
-// feature for good (its record sits in registers) and owns up to U rows of every tile; the
-// loads of the next tile are issued before the current tile is ranked.  Ranks are parked in a
-// transposed staging buffer and written out as Q[tile][feature][q_slot(row in tile)] (uint16): the
-// layout the traversal kernel pulls into shared memory with a single bulk copy.  NaN becomes Q_NAN_CODE
-// and raises the tile's flag.
-// Shared memory: [mbarrier 16 B][blob][staging buffer GF x (R + 2) uint16].
+// Calls f(std::integral_constant<int, K>) for K = 0, 1, ...: a loop whose counter is a constant
+// expression inside the body.
+template <typename F, int... Ks>
+__device__ __forceinline__ void for_each_constant(F&& f, std::integer_sequence<int, Ks...>)
+{
+  (f(std::integral_constant<int, Ks>{}), ...);
+}
+
 __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
 {
   asm volatile(
@@ -615,6 +662,19 @@ __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
     : "memory");
 }
 
+// One CTA owns one feature group: the group's blob (feature records, bucket tables, sorted
+// thresholds, both tables interleaved across the group's features) arrives in shared memory with
+// one bulk copy, then the CTA loops over row tiles.  The group size GF is a power of two that
+// divides the thread count, so a thread keeps one feature for good (its record sits in registers)
+// and with 32-feature groups a warp reads 128 contiguous bytes of one row per load and its 32
+// table lookups never share a bank.  A thread owns NU consecutive slots of the rank tile (slot =
+// q_slot(row)); it ranks them four at a time while the loads of the next four are in flight,
+// packs the ranks two per word and writes its piece of Q[tile][feature][slot] (uint16) with one
+// vector store, the layout the traversal kernel pulls into shared memory with a single bulk
+// copy.  Nothing is exchanged between threads, so the tile loop has no barrier.  NaN becomes
+// Q_NAN_CODE and raises the tile's flag.
+// Shared memory: [mbarrier 16 B][blob].
+
 // Position of row r among the R uint16 entries of one feature in a rank tile.  Rows r and r + 32
 // share a 32-bit word, so the 32 consecutive rows of a warp sit in 32 different banks whatever
 // feature each lane reads (with the plain order two neighbouring rows share a bank and collide
@@ -623,124 +683,171 @@ __device__ __forceinline__ uint32_t q_slot(uint32_t r, int R)
 {
   return R >= 64 ? (((r & 31u) << 1) | ((r >> 5) & 1u) | ((r >> 6) << 6)) : r;
 }
+// The row that sits in slot s (inverse of q_slot).
+__device__ __forceinline__ uint32_t q_row_of_slot(uint32_t s, int R)
+{
+  return R >= 64 ? (((s >> 6) << 6) | ((s & 63u) >> 1) | ((s & 1u) << 5)) : s;
+}
 
-// NU = rows of a tile each thread owns (R * GF / threads, at least 1).
-template <typename T, int STEPS, int NU>
+// NU = slots of a tile each thread owns (R * GF / threads, at least 1).  GFC > 0 fixes the group
+// size at compile time (table strides become immediates), GFC == 0 reads it from the group.
+template <typename T, int STEPS, int NU, int GFC>
 __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGroup& grp,
                                                uint16_t* __restrict__ Q,
                                                int32_t* __restrict__ tile_flags, int R,
-                                               uint32_t blob_a, const QFeatRec* rec,
-                                               uint32_t qbuf_a)
+                                               uint32_t blob_a, const QFeatRec* rec)
 {
-  using TR              = Traits<T>;
-  const int GF          = grp.f_end - grp.f_begin;
-  const int F           = p.f.n_features;
-  const int tid         = threadIdx.x;
-  const int nthreads    = blockDim.x;
-  const int i           = tid & (GF - 1);
-  const int gshift      = 31 - __clz(GF);
-  const int r_first     = tid >> gshift;
-  const int r_step      = nthreads >> gshift;
-  const bool active     = r_first < R;  // false only when a tile has fewer values than threads
-  const QFeatRec mine   = rec[i];
-  const T scale         = static_cast<T>(mine.scale);
-  const T offset        = static_cast<T>(mine.offset);
-  const T nbm1          = static_cast<T>(mine.nbm1);
-  const uint32_t lut    = blob_a + mine.lut_off;
-  const uint32_t thr_m1 = blob_a + mine.thr_off - TR::ES;
-  const int qstride     = R + 2;  // uint16 elements between features in the staging buffer
-  const uint32_t q_feat = qbuf_a + i * qstride * 2u;
-  const int64_t n_tiles = (p.n_rows + R - 1) / R;
-  // element offsets inside a tile fit 32 bits (the host sizes row chunks accordingly)
-  const uint32_t e_mine = static_cast<uint32_t>(r_first * p.row_stride + grp.f_begin + i);
-  const uint32_t e_step = static_cast<uint32_t>(r_step * p.row_stride);
-  const T* X            = static_cast<const T*>(p.X);
-  const int hshift      = 30 - __clz(R);  // log2(R / 2)
-  const int half        = R >> 1;
+  using TR               = Traits<T>;
+  constexpr int CH       = NU < 4 ? NU : 4;  // values ranked side by side
+  constexpr int NCH      = NU / CH;
+  const int GF           = GFC > 0 ? GFC : static_cast<int>(grp.f_end - grp.f_begin);
+  const int tid          = threadIdx.x;
+  const int gshift       = 31 - __clz(GF);
+  const int i            = tid & (GF - 1);
+  const uint32_t s0      = static_cast<uint32_t>(tid >> gshift) * NU;  // first slot of the thread
+  const bool active      = s0 < static_cast<uint32_t>(R);  // false only when a tile has fewer values than threads
+  const QFeatRec mine    = rec[i];
+  const T scale          = static_cast<T>(mine.scale);
+  const T offset         = static_cast<T>(mine.offset);
+  const T nbm1           = static_cast<T>(mine.nbm1);
+  const uint32_t lut_row = static_cast<uint32_t>(GF) * 2u;      // bytes between table entries
+  const uint32_t thr_row = static_cast<uint32_t>(GF) * TR::ES;  // bytes between thresholds
+  const int eshift       = gshift + (TR::ES == 4 ? 2 : 3);      // log2(thr_row)
+  const uint32_t lut     = blob_a + mine.lut_off;
+  const uint32_t thr_m1  = blob_a + mine.thr_off - thr_row;
+  const bool any_cat     = __any_sync(0xffffffffu, mine.is_cat != 0);
+  const int64_t tile_elems = static_cast<int64_t>(p.f.n_features) * R;  // ranks per tile
+  const uint32_t q_mine  = (grp.f_begin + i) * static_cast<uint32_t>(R) + s0;  // thread's first rank in a tile
+  const int64_t n_tiles  = (p.n_rows + R - 1) / R;
+  // slots s0 + j, j = 0..NU-1, hold rows b + (j >> 1) + 32 * (j & 1) (NU >= 2 implies R >= 64 and
+  // an even s0); element offsets inside a tile fit 32 bits (the host sizes row chunks accordingly)
+  const uint32_t b       = q_row_of_slot(s0, R);
+  const uint32_t e1      = static_cast<uint32_t>(p.row_stride);
+  const uint32_t e32     = e1 * 32u;
+  const uint32_t e_mine  = b * e1 + grp.f_begin + i;
+  const T* X             = static_cast<const T*>(p.X);
 
-  T xs[NU];
-  auto fetch = [&](int64_t t) {
+  T xs[CH];
+  // loads chunk c (slots s0 + c * CH ...) of tile t
+  auto fetch = [&](int64_t t, int c) {
     const int64_t row0 = t * R;
     const T* tb        = X + row0 * p.row_stride;  // same for the whole CTA
+    const uint32_t cb  = e_mine + static_cast<uint32_t>(c * (CH / 2)) * e1;
     if (row0 + R <= p.n_rows) {
 #pragma unroll
-      for (int u = 0; u < NU; ++u) xs[u] = active ? __ldg(tb + (e_mine + u * e_step)) : T(0);
+      for (int u = 0; u < CH; ++u)
+        xs[u] = active ? __ldg(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
     } else {
 #pragma unroll
-      for (int u = 0; u < NU; ++u) {
-        const int64_t row = row0 + r_first + u * r_step;
-        xs[u] = (active && row < p.n_rows) ? __ldg(tb + (e_mine + u * e_step)) : T(0);
+      for (int u = 0; u < CH; ++u) {
+        const int64_t row = row0 + b + c * (CH / 2) + (u >> 1) + 32 * (u & 1);
+        xs[u] = (active && row < p.n_rows) ? __ldg(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
       }
     }
   };
-  if (blockIdx.x < n_tiles) fetch(blockIdx.x);
+  if (blockIdx.x < n_tiles) fetch(blockIdx.x, 0);
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-    T cur[NU];
-#pragma unroll
-    for (int u = 0; u < NU; ++u) cur[u] = xs[u];
-    // the loads of the next tile fly while this tile is ranked and written out
-    if (t + gridDim.x < n_tiles) fetch(t + gridDim.x);
+    uint32_t packed[NU > 1 ? NU / 2 : 1];
     bool saw_nan = false;
-    if (active) {
-      // rank of the NU values, step by step across all of them so that the dependent
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      T cur[CH];
+#pragma unroll
+      for (int u = 0; u < CH; ++u) cur[u] = xs[u];
+      // the loads of the next chunk fly while this one is ranked
+      if (c + 1 < NCH) {
+        fetch(t, c + 1);
+      } else if (t + gridDim.x < n_tiles) {
+        fetch(t + gridDim.x, 0);
+      }
+      // rank of the CH values, step by step across all of them so that the dependent
       // shared-memory lookups of different values overlap.  A NaN walks the same code (bucket 0,
-      // every comparison false) and is replaced by Q_NAN_CODE at the end.
-      uint32_t pos_b[NU];
-      if (mine.is_cat) {
-        // categorical feature: the code is the category itself (truncated value); negative and
-        // huge values match no listed category
+      // every comparison false) and is replaced by Q_NAN_CODE at the end; so does a categorical
+      // value (its feature has empty tables), replaced by its category.
+      uint32_t a[CH];  // address of the threshold below the current window
 #pragma unroll
-        for (int u = 0; u < NU; ++u) {
+      for (int u = 0; u < CH; ++u) {
+        // same expression as q_bucket_host: fma, clamp (NaN becomes 0), truncate
+        T v = fma(cur[u], scale, offset);
+        v   = fmax(v, T(0));
+        v   = fmin(v, nbm1);
+        a[u] = (lds_u16(lut + static_cast<uint32_t>(v) * lut_row) << eshift) + thr_m1;
+      }
+      if (STEPS > 0 && GFC > 0) {
+        // group size and step count known: the probe offsets are immediates of the loads
+        for_each_constant(
+          [&](auto kc) {
+            constexpr int k        = (STEPS > 0 ? STEPS : 1) - 1 - decltype(kc)::value;
+            constexpr uint32_t S_B = (static_cast<uint32_t>(GFC > 0 ? GFC : 1) * TR::ES) << k;
+            T thr[CH];
+#pragma unroll
+            for (int u = 0; u < CH; ++u) thr[u] = TR::template ld_real_at<S_B>(a[u]);
+#pragma unroll
+            for (int u = 0; u < CH; ++u) TR::add_if_le(a[u], thr[u], cur[u], S_B);
+          },
+          std::make_integer_sequence<int, (STEPS > 0 ? STEPS : 0)>{});
+      } else if (STEPS >= 0) {
+#pragma unroll
+        for (int k = STEPS - 1; k >= 0; --k) {
+          const uint32_t s_b = thr_row << k;
+          T thr[CH];
+#pragma unroll
+          for (int u = 0; u < CH; ++u) thr[u] = TR::ld_real(a[u] + s_b);
+#pragma unroll
+          for (int u = 0; u < CH; ++u) TR::add_if_le(a[u], thr[u], cur[u], s_b);
+        }
+      } else {  // very full buckets: the number of halvings is only known at run time
+        for (int k = static_cast<int>(grp.steps) - 1; k >= 0; --k) {
+          const uint32_t s_b = thr_row << k;
+#pragma unroll
+          for (int u = 0; u < CH; ++u) TR::add_if_le(a[u], TR::ld_real(a[u] + s_b), cur[u], s_b);
+        }
+      }
+      uint32_t code[CH];
+#pragma unroll
+      for (int u = 0; u < CH; ++u) code[u] = (a[u] - thr_m1) >> eshift;
+      if (any_cat) {
+        // groups with categorical features only (the warp-wide barrier keeps this a real branch
+        // instead of conversions and selects that every group would execute): the code of a
+        // categorical value is the category itself (truncated value); negative and huge values
+        // match no listed category
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
           const bool in_range = (cur[u] >= T(0)) && (cur[u] < T(Q_NO_CATEGORY));
-          pos_b[u] = (in_range ? static_cast<uint32_t>(cur[u]) : Q_NO_CATEGORY) * TR::ES;
-        }
-      } else {
-#pragma unroll
-        for (int u = 0; u < NU; ++u) {
-          // same expression as q_bucket_host: fma, clamp (NaN becomes 0), truncate
-          T v = fma(cur[u], scale, offset);
-          v   = fmax(v, T(0));
-          v   = fmin(v, nbm1);
-          pos_b[u] = lds_u16(lut + static_cast<uint32_t>(v) * 2u) * TR::ES;
-        }
-        if (STEPS >= 0) {
-#pragma unroll
-          for (int k = STEPS - 1; k >= 0; --k) {
-            const uint32_t s_b = (1u << k) * TR::ES;
-            T thr[NU];
-#pragma unroll
-            for (int u = 0; u < NU; ++u) thr[u] = TR::ld_real(thr_m1 + pos_b[u] + s_b);
-#pragma unroll
-            for (int u = 0; u < NU; ++u) pos_b[u] += (thr[u] <= cur[u]) ? s_b : 0u;
-          }
-        } else {  // very full buckets: the number of halvings is only known at run time
-          for (int k = static_cast<int>(grp.steps) - 1; k >= 0; --k) {
-            const uint32_t s_b = (1u << k) * TR::ES;
-#pragma unroll
-            for (int u = 0; u < NU; ++u)
-              pos_b[u] += (TR::ld_real(thr_m1 + pos_b[u] + s_b) <= cur[u]) ? s_b : 0u;
-          }
+          if (mine.is_cat) code[u] = in_range ? static_cast<uint32_t>(cur[u]) : Q_NO_CATEGORY;
         }
       }
 #pragma unroll
-      for (int u = 0; u < NU; ++u) {
+      for (int u = 0; u < CH; ++u) {
         const bool is_nan = cur[u] != cur[u];
         saw_nan |= is_nan;
-        sts_u16(q_feat + q_slot(r_first + u * r_step, R) * 2u,
-                is_nan ? Q_NAN_CODE : pos_b[u] / TR::ES);
+        const uint32_t cd = is_nan ? Q_NAN_CODE : code[u];
+        const int j       = c * CH + u;
+        if (NU == 1) {
+          packed[0] = cd;
+        } else if (j & 1) {
+          packed[j >> 1] |= cd << 16;
+        } else {
+          packed[j >> 1] = cd;
+        }
+      }
+    }
+    // Q[tile][feature][slot]: the thread's NU consecutive slots of its feature in one store
+    if (active) {
+      uint16_t* dst = Q + t * tile_elems + q_mine;
+      if (NU == 8) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[NU > 2 ? 1 : 0],
+                                                    packed[NU > 4 ? 2 : 0], packed[NU > 6 ? 3 : 0]);
+      } else if (NU == 4) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[NU > 2 ? 1 : 0]);
+      } else if (NU == 2) {
+        *reinterpret_cast<uint32_t*>(dst) = packed[0];
+      } else {
+        *dst = static_cast<uint16_t>(packed[0]);
       }
     }
     if (__any_sync(0xffffffffu, saw_nan) && (tid & 31) == 0) atomicOr(tile_flags + t, 1);
-    __syncthreads();
-    // staging buffer -> Q[tile][feature][row], two rows per 32-bit store
-    uint32_t* out32 =
-      reinterpret_cast<uint32_t*>(Q) + (t * F + grp.f_begin) * static_cast<int64_t>(half);
-    for (int e = tid; e < (GF << hshift); e += nthreads) {
-      const int fi = e >> hshift;
-      const int c  = e & (half - 1);
-      out32[e]     = lds_u32(qbuf_a + (fi * (half + 1) + c) * 4u);
-    }
-    __syncthreads();
   }
 }
 
@@ -748,15 +855,20 @@ template <typename T, int STEPS>
 __device__ __forceinline__ void quantise_rows(const PredictParams& p, const QGroup& grp,
                                               uint16_t* __restrict__ Q,
                                               int32_t* __restrict__ tile_flags, int R,
-                                              uint32_t blob_a, const QFeatRec* rec,
-                                              uint32_t qbuf_a)
+                                              uint32_t blob_a, const QFeatRec* rec)
 {
-  const int per_thread = (R * static_cast<int>(grp.f_end - grp.f_begin)) / static_cast<int>(blockDim.x);
+  const int GF         = static_cast<int>(grp.f_end - grp.f_begin);
+  const int per_thread = (R * GF) / static_cast<int>(blockDim.x);
+  // full-width groups on large tiles, the shape of big batches, get the group size baked in
+  if (GF == 32 && STEPS >= 2 && per_thread == 8) {
+    quantise_tiles<T, STEPS, 8, 32>(p, grp, Q, tile_flags, R, blob_a, rec);
+    return;
+  }
   switch (per_thread) {
-    case 8: quantise_tiles<T, STEPS, 8>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 4: quantise_tiles<T, STEPS, 4>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 2: quantise_tiles<T, STEPS, 2>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    default: quantise_tiles<T, STEPS, 1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 8: quantise_tiles<T, STEPS, 8, 0>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 4: quantise_tiles<T, STEPS, 4, 0>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 2: quantise_tiles<T, STEPS, 2, 0>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    default: quantise_tiles<T, STEPS, 1, 0>(p, grp, Q, tile_flags, R, blob_a, rec); break;
   }
 }
 
@@ -771,7 +883,6 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
   const uint32_t bar    = smem_addr(smem);
   unsigned char* blob   = smem + 16;
   const uint32_t blob_a = smem_addr(blob);
-  const uint32_t qbuf_a = blob_a + grp.blob_bytes;
   const QFeatRec* rec   = reinterpret_cast<const QFeatRec*>(blob);
 
   if (threadIdx.x == 0) {
@@ -787,13 +898,13 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
   }
   // the number of halvings is fixed per group: pick the unrolled body once
   switch (grp.steps) {
-    case 0: quantise_rows<T, 0>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 1: quantise_rows<T, 1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 2: quantise_rows<T, 2>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 3: quantise_rows<T, 3>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 4: quantise_rows<T, 4>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    case 5: quantise_rows<T, 5>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
-    default: quantise_rows<T, -1>(p, grp, Q, tile_flags, R, blob_a, rec, qbuf_a); break;
+    case 0: quantise_rows<T, 0>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 1: quantise_rows<T, 1>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 2: quantise_rows<T, 2>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 3: quantise_rows<T, 3>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 4: quantise_rows<T, 4>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    case 5: quantise_rows<T, 5>(p, grp, Q, tile_flags, R, blob_a, rec); break;
+    default: quantise_rows<T, -1>(p, grp, Q, tile_flags, R, blob_a, rec); break;
   }
 }
 
@@ -803,15 +914,17 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
 // Shared memory: [mbarriers 128 B][row tile F x R uint16][accumulators][flags 16 B][S tree stages].
 // The row tile arrives with one bulk copy per tile (the pre-pass already stored it feature-major);
 // tree batches stream through the stage ring exactly as in dense_kernel.  A node is 4 bytes
-// (rank j << 16 | default-left << 15 | feature) and a test is one signed subtraction.
+// (rank j << 17 | default-left << 16 | feature << 2 | categorical) and a test is one signed
+// subtraction.
 constexpr int kBarTileFull  = 2 * kMaxStages;      // mbarrier slots after the stage ring
 constexpr int kBarTileEmpty = 2 * kMaxStages + 1;
 
-// q * (-65536) + node in one multiply-add: the sign of (j - rank) lands in bit 31.
+// node - (q << 17) in one multiply-add: the sign of (j - rank) lands in bit 31.
 __device__ __forceinline__ uint32_t rank_diff(uint32_t node, uint32_t q)
 {
+  static_assert(Q_RANK_SHIFT == 17, "the multiplier below is -(1 << Q_RANK_SHIFT)");
   uint32_t d;
-  asm("mad.lo.u32 %0, %1, 0xFFFF0000, %2;" : "=r"(d) : "r"(q), "r"(node));
+  asm("mad.lo.u32 %0, %1, 0xFFFE0000, %2;" : "=r"(d) : "r"(q), "r"(node));
   return d;
 }
 
@@ -827,95 +940,115 @@ struct DenseQWalker {
                                               int r, int64_t row, int lane, uint32_t bars,
                                               uint32_t stages, uint32_t stage_bytes,
                                               uint32_t row_addr, uint32_t stride_b, T* acc_group,
-                                              int R, uint32_t& it, Running<T>& run)
+                                              int R, RingPos& pos, Running<T>& run)
   {
     const ForestView& f    = p.f;
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
     const uint32_t width_b = (1u << D) * 4u;
     const uint32_t cat_off = (1u << D) * (4u + TR::ES);  // node address -> its category set
+    const uint32_t fstride = stride_b >> Q_FEATURE_SHIFT;  // R / 2 <= 128: fits a byte
     const int per_sub      = G * NT;
     const int per_batch    = per_sub * K;
     const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
+    const uint32_t mine    = static_cast<uint32_t>(g * NT) * tstride;  // this warp's trees in a sub-batch
+    const uint32_t sub_b   = static_cast<uint32_t>(per_sub) * tstride;
     bool ok                = true;
-    for (int b = 0; b < n_batches; ++b, ++it) {
-      const uint32_t s = it % S;
-      if (ok) ok = mbar_wait(bars + 8u * s, (it / S) & 1u);
-      if (ok) {
-        const uint32_t stage = stages + s * stage_bytes;
-        for (int kk = 0; kk < K; ++kk) {
-          const int slot0 = kk * per_sub + g * NT;  // first tree of this warp inside the stage
-          const int first = b * per_batch + slot0;
-          const int n_act = min(NT, f.n_trees - first);
-          if (n_act <= 0) break;
-          uint32_t base[NT], idx[NT], a[NT];
+
+    // One sub-batch: NT trees side by side.  FULL means all NT slots hold live trees, which lets
+    // the compiler drop every per-slot guard.
+    auto sub_batch = [&](auto full_tag, uint32_t base0, int first, int n_act) {
+      constexpr bool FULL = decltype(full_tag)::value;
+      uint32_t base[NT], idx[NT], a[NT];
 #pragma unroll
-          for (int k = 0; k < NT; ++k) {
-            // slots past the end of the forest repeat the last live tree; results are dropped
-            base[k] = stage + (slot0 + min(k, n_act - 1)) * tstride;
-            idx[k]  = 1u;  // heap index of the root
-            a[k]    = base[k] + 4u;
-          }
-          // the NT walks are independent: all node loads are issued first, then all rank loads,
-          // so that their shared-memory latencies overlap inside one warp
-          auto level = [&]() {
-            uint32_t node[NT], q[NT];
+      for (int k = 0; k < NT; ++k) {
+        // slots past the end of the forest repeat the last live tree; results are dropped
+        base[k] = base0 + static_cast<uint32_t>(FULL ? k : min(k, n_act - 1)) * tstride;
+        idx[k]  = 1u;  // heap index of the root
+        a[k]    = base[k] + 4u;
+      }
+      // the NT walks are independent: all node loads are issued first, then all rank loads,
+      // so that their shared-memory latencies overlap inside one warp
+      auto level = [&]() {
+        uint32_t node[NT], q[NT];
 #pragma unroll
-            for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
+        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
 #pragma unroll
-            for (int k = 0; k < NT; ++k)
-              q[k] = lds_u16((node[k] & Q_FEATURE_MASK) * stride_b + row_addr);
+        for (int k = 0; k < NT; ++k)
+          // the low half of a node is feature * 4 (plus the categorical flag): without
+          // categorical tests one dot-product instruction (low half x byte 0 of fstride, high
+          // half x byte 1 = 0) turns it into the address of the row's rank of that feature
+          q[k] = lds_u16(CAT ? (node[k] & Q_FEATURE_FIELD) * fstride + row_addr
+                             : __dp2a_lo(node[k], fstride, row_addr));
 #pragma unroll
-            for (int k = 0; k < NT; ++k) {
-              // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0:
-              // the sign bit of the difference is the step to the right child
-              uint32_t d = rank_diff(node[k], q[k]);
-              if (CAT) {
-                if (node[k] & Q_CATEGORICAL) {
-                  // the code of a categorical value is its category: a set bit sends it right
-                  const uint32_t bits = lds_u32(a[k] + cat_off);
-                  d = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
-                }
-              }
-              if (NANS) {
-                if (q[k] == Q_NAN_CODE) d = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
-              }
-              // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
-              idx[k] = __funnelshift_l(d, idx[k], 1);
-              a[k]   = idx[k] * 4u + base[k];
+        for (int k = 0; k < NT; ++k) {
+          // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0:
+          // the sign bit of the difference is the step to the right child
+          uint32_t d = rank_diff(node[k], q[k]);
+          if (CAT) {
+            if (node[k] & Q_CATEGORICAL) {
+              // the code of a categorical value is its category: a set bit sends it right
+              const uint32_t bits = lds_u32(a[k] + cat_off);
+              d = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
             }
-          };
-          if (DEPTH > 0) {
+          }
+          if (NANS) {
+            if (q[k] == Q_NAN_CODE) d = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
+          }
+          // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
+          idx[k] = __funnelshift_l(d, idx[k], 1);
+          a[k]   = idx[k] * 4u + base[k];
+        }
+      };
+      if (DEPTH > 0) {
 #pragma unroll
-            for (int lvl = 0; lvl < DEPTH; ++lvl) level();
-          } else {
+        for (int lvl = 0; lvl < DEPTH; ++lvl) level();
+      } else {
 #pragma unroll 4
-            for (int lvl = 0; lvl < D; ++lvl) level();
-          }
+        for (int lvl = 0; lvl < D; ++lvl) level();
+      }
 #pragma unroll
-          for (int k = 0; k < NT; ++k) {
-            if (k < n_act) {
-              // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
-              // address of leaf slot j is exactly the address the walk ended on
-              const uint32_t slot   = idx[k] - (1u << D);
-              const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
-              const typename TR::Val payload = TR::ld_val(leaf_a);
-              take_leaf<T, MODE>(p, first + k, payload,
-                                 (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
-                                 row, run);
-            }
+      for (int k = 0; k < NT; ++k) {
+        if (FULL || k < n_act) {
+          // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
+          // address of leaf slot j is exactly the address the walk ended on
+          const uint32_t slot   = idx[k] - (1u << D);
+          const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
+          const typename TR::Val payload = TR::ld_val(leaf_a);
+          take_leaf<T, MODE>(p, first + k, payload,
+                             (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r, row,
+                             run);
+        }
+      }
+    };
+
+    for (int b = 0; b < n_batches; ++b) {
+      const uint32_t s = pos.stage;
+      if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
+      if (ok) {
+        uint32_t base0 = stages + s * stage_bytes + mine;
+        int first      = b * per_batch + g * NT;  // first tree of this warp inside the stage
+        for (int kk = 0; kk < K; ++kk, base0 += sub_b, first += per_sub) {
+          const int n_act = f.n_trees - first;
+          if (n_act >= NT) {
+            sub_batch(std::true_type{}, base0, first, NT);
+          } else if (n_act > 0) {
+            sub_batch(std::false_type{}, base0, first, n_act);
+          } else {
+            break;
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
+      pos.advance(S);
     }
     return ok;
   }
 };
 
 template <typename T, int MODE, int NT, int DEPTH, bool CAT>
-__global__ void __launch_bounds__(1024, 1)
+__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
 dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
                const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
                const int K)
@@ -964,7 +1097,8 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
     if (lane == 0) {
       const unsigned char* src  = static_cast<const unsigned char*>(f.q_nodes);
       const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(Q);
-      uint32_t it               = 0;
+      RingPos pos;
+      bool primed               = false;  // every stage has been filled once
       uint32_t n_done           = 0;
       for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
         // the tile buffer is free once every consumer warp has left the previous tile's trees
@@ -974,10 +1108,9 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
         }
         mbar_expect_tx(bar_tfull, tile_bytes);
         bulk_copy_g2s(tile, qsrc + static_cast<size_t>(t) * tile_bytes, tile_bytes, bar_tfull);
-        for (int b = 0; b < n_batches; ++b, ++it) {
-          const uint32_t s   = it % S;
-          const uint32_t use = it / S;
-          if (use > 0 && !mbar_wait(bars + 8u * (kMaxStages + s), (use - 1) & 1u)) {
+        for (int b = 0; b < n_batches; ++b) {
+          const uint32_t s = pos.stage;
+          if (primed && !mbar_wait(bars + 8u * (kMaxStages + s), pos.phase ^ 1u)) {
             atomicExch(p.status, 1);
             return;
           }
@@ -987,6 +1120,8 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
           mbar_expect_tx(bars + 8u * s, bytes);
           bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
                         bytes, bars + 8u * s);
+          pos.advance(S);
+          if (pos.stage == 0) primed = true;
         }
       }
     }
@@ -998,7 +1133,7 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
   const int r             = (warp % rw) * 32 + lane;
   T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
   const uint32_t row_addr = tile + q_slot(r, R) * 2u;
-  uint32_t it             = 0;
+  RingPos pos;
   uint32_t n_done         = 0;
   bool ok                 = true;
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
@@ -1014,11 +1149,11 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
       if (nans) {
         ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<true>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, it, run);
+          acc_group, R, pos, run);
       } else {
         ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<false>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, it, run);
+          acc_group, R, pos, run);
       }
       if (!ok) atomicExch(p.status, 2);
     }
@@ -1310,8 +1445,18 @@ size_t dense_q_smem(size_t qstride, int precision, int F, int NC, bool reduce, i
   return b;
 }
 
+// Most trees a warp of the quantised kernel may walk side by side: the kernels that exist.
+int q_max_trees_in_flight(const ForestView& f, int mode)
+{
+  if (f.q_has_cat) return 2;
+  const bool specialised = f.format == FMT_DENSE_F && mode == MODE_SCALAR && f.dense_depth >= 4 &&
+                           f.dense_depth <= 10;
+  return specialised ? 6 : 4;
+}
+
 // Launch shape of the quantised dense kernel: the largest row tile that fits, then as many warps
-// as fit (32 consumer warps at most), two trees in flight per warp and a three-stage tree ring.
+// as fit (31 consumer warps at most), then as many trees in flight per warp as there is a kernel
+// for, then the deepest tree ring that still fits.
 bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bool reduce,
                     int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
 {
@@ -1324,7 +1469,8 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
   if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S,K"
     int R, G, NT, S, K;
     if (sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5 && R >= 32 && R % 32 == 0 &&
-        G >= 1 && (R / 32) * G <= 31 && (NT == 1 || NT == 2 || NT == 4) && S >= 2 &&
+        R <= 256 && (R & (R - 1)) == 0 && G >= 1 && (R / 32) * G <= 31 &&
+        (NT == 1 || NT == 2 || NT == 4 || (NT == 6 && (R / 32) * G <= 24)) && S >= 2 &&
         S <= kMaxStages && K >= 1 && NT <= max_nt) {
       const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
@@ -1337,9 +1483,12 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
     const int rw = R / 32;
     // a CTA holds at most 32 warps and one of them is the producer
     for (int G = std::min(8, 31 / rw); G >= 1; --G) {
-      for (int NT = max_nt; NT >= 1; NT /= 2) {
-        // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees;
-        // the ring must also cover the bytes in flight over the latency of a bulk copy
+      for (int NT = max_nt; NT >= 1; NT = NT == 6 ? 4 : NT / 2) {
+        // the six-tree kernels are built for at most 24 consumer warps (80 registers a thread)
+        if (NT > 4 && rw * G > 24) continue;
+        // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees.
+        // Trees in flight per warp come before ring depth: two stages already hide the bulk
+        // copies (measured: S = 2 and S = 3 run alike), while 6 trees against 4 is 5 % faster.
         for (int K = 2; K >= 1; K /= 2) {
           for (int S = 3; S >= 2; --S) {
             const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
@@ -1386,6 +1535,21 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
       }
     }
     return B2FIL_OK;
+  }
+  if constexpr (std::is_same<T, float>::value) {
+    // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies with six
+    // trees in flight (q_max_trees_in_flight offers six only for them)
+    if (c.trees_in_flight == 6) {
+      switch (p.f.dense_depth) {
+        case 4: B2FIL_Q_CASE(MODE_SCALAR, 6, 4) return B2FIL_OK;
+        case 5: B2FIL_Q_CASE(MODE_SCALAR, 6, 5) return B2FIL_OK;
+        case 6: B2FIL_Q_CASE(MODE_SCALAR, 6, 6) return B2FIL_OK;
+        case 7: B2FIL_Q_CASE(MODE_SCALAR, 6, 7) return B2FIL_OK;
+        case 8: B2FIL_Q_CASE(MODE_SCALAR, 6, 8) return B2FIL_OK;
+        case 9: B2FIL_Q_CASE(MODE_SCALAR, 6, 9) return B2FIL_OK;
+        default: B2FIL_Q_CASE(MODE_SCALAR, 6, 10) return B2FIL_OK;
+      }
+    }
   }
   if (c.trees_in_flight == 4) {
     // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies
@@ -1439,7 +1603,7 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
   const bool reduce   = mode <= MODE_VECTOR;
   DenseCfg c;
-  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), f.q_has_cat ? 2 : 4, precision,
+  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
                       f.n_features, f.n_outputs, reduce, p.n_rows, chunk_size, sm_count, c)) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
@@ -1471,9 +1635,8 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   }
   uint16_t* Q    = reinterpret_cast<uint16_t*>(scratch);
   int32_t* flags = reinterpret_cast<int32_t*>(scratch + q_bytes);
-  // shared memory of the pre-pass: mbarrier, the largest group blob, staging buffer
-  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes) +
-                        static_cast<size_t>(kQMaxGroupFeatures) * (R + 2) * 2;
+  // shared memory of the pre-pass: mbarrier and the largest group blob
+  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes);
   int rc = B2FIL_OK;
   const size_t out_row_b =
     (p.kind == B2FIL_INFER_LEAF_ID ? size_t(4) * f.n_trees
@@ -1757,7 +1920,7 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
   }
   const int precision = f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64;
   DenseCfg c;
-  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), f.q_has_cat ? 2 : 4, precision,
+  if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
                       f.n_features, f.n_outputs, mode <= MODE_VECTOR, p.n_rows, chunk_size,
                       sm_count, c)) {
     err = "no quantised launch shape fits shared memory";
@@ -1789,8 +1952,7 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
     err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e);
     return B2FIL_ERR_CUDA;
   }
-  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes) +
-                        static_cast<size_t>(kQMaxGroupFeatures) * (R + 2) * 2;
+  const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes);
   const int gx = static_cast<int>(
     std::min<int64_t>(n_tiles, std::max(1, sm_count / f.q_n_groups)));
   const dim3 qgrid(gx, f.q_n_groups);

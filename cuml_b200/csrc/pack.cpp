@@ -398,7 +398,7 @@ struct Packer {
   bool build_quantised(int D)
   {
     const int F = d.n_features;
-    if (F > static_cast<int>(Q_FEATURE_MASK) + 1) return false;
+    if (F > static_cast<int>(Q_MAX_FEATURES)) return false;
     if (D < 1) return false;  // forests of single leaves have nothing to rank
     if (has_cat && !cat_inline) return false;  // category sets must fit 32 bits
     const int nt = d.n_trees;
@@ -422,149 +422,147 @@ struct Packer {
     for (int f = 0; f < F; ++f) {
       if (used_num[f] && used_cat[f]) return false;
     }
-    // tables and groups for a given number of buckets per threshold; returns the number of
-    // groups, or -1 when a limit is exceeded
-    auto build_tables = [&](uint32_t bucket_factor) -> int {
-      out.q_groups.clear();
-      out.q_blob.clear();
-      out.view.q_max_blob_bytes = 0;
-      size_t total_thr = 0, total_lut = 0;
-      out.q_feats.assign(F, QFeature{});
-      for (int f = 0; f < F; ++f) {
-        auto& v = per[f];
-        std::sort(v.begin(), v.end());
-        v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
-        if (v.size() > Q_MAX_RANK) return -1;
-        QFeature& qf = out.q_feats[f];
-        qf.is_cat    = used_cat[f];
-        qf.m         = static_cast<uint32_t>(v.size());
-        uint32_t nb  = 16;
-        while (nb < bucket_factor * qf.m && nb < 4096) nb *= 2;
-        qf.n_buckets = qf.m == 0 ? 1 : nb;
-        // bucket grid over the finite thresholds
-        T scale = 0, offset = 0;
-        size_t lo = 0, hi = v.size();
-        while (lo < hi && !std::isfinite(v[lo])) ++lo;
-        while (hi > lo && !std::isfinite(v[hi - 1])) --hi;
-        if (hi - lo >= 2) {
-          const double range = static_cast<double>(v[hi - 1]) - static_cast<double>(v[lo]);
-          const T sc         = static_cast<T>(static_cast<double>(qf.n_buckets) / range);
-          const T of         = static_cast<T>(-static_cast<double>(v[lo]) * static_cast<double>(sc));
-          if (std::isfinite(sc) && std::isfinite(of) && sc > T(0)) {
-            scale  = sc;
-            offset = of;
+    for (int f = 0; f < F; ++f) {
+      auto& v = per[f];
+      std::sort(v.begin(), v.end());
+      v.erase(std::unique(v.begin(), v.end()), v.end());  // -0.0 == +0.0: one threshold
+      if (v.size() > Q_MAX_RANK) return false;
+    }
+    // 2. bucket tables.  The table of one feature for a given number of buckets per threshold:
+    //    grid over the finite thresholds, lut[b] = thresholds in buckets below b, fullest bucket.
+    struct FeatTable {
+      uint32_t n_buckets = 1, max_occupancy = 0;
+      T scale = 0, offset = 0;
+      std::vector<uint16_t> lut;
+    };
+    auto make_table = [&](int f, double factor) {
+      const auto& v = per[f];
+      FeatTable t;
+      if (v.empty()) {
+        t.lut.assign(1, 0);
+        return t;
+      }
+      const double want = std::ceil(factor * static_cast<double>(v.size()));
+      t.n_buckets       = static_cast<uint32_t>(std::min(4096.0, std::max(16.0, want)));
+      size_t lo = 0, hi = v.size();
+      while (lo < hi && !std::isfinite(v[lo])) ++lo;
+      while (hi > lo && !std::isfinite(v[hi - 1])) --hi;
+      if (hi - lo >= 2) {
+        const double range = static_cast<double>(v[hi - 1]) - static_cast<double>(v[lo]);
+        const T sc         = static_cast<T>(static_cast<double>(t.n_buckets) / range);
+        const T of         = static_cast<T>(-static_cast<double>(v[lo]) * static_cast<double>(sc));
+        if (std::isfinite(sc) && std::isfinite(of) && sc > T(0)) {
+          t.scale  = sc;
+          t.offset = of;
+        }
+      }
+      std::vector<uint32_t> count(t.n_buckets + 1, 0);
+      for (size_t i = 0; i < v.size(); ++i)
+        ++count[q_bucket_host<T>(v[i], t.scale, t.offset, t.n_buckets) + 1];
+      t.lut.resize(t.n_buckets);
+      uint32_t run = 0;
+      for (uint32_t b = 0; b < t.n_buckets; ++b) {
+        run += count[b];  // thresholds in buckets below b
+        t.lut[b]        = static_cast<uint16_t>(run);
+        t.max_occupancy = std::max(t.max_occupancy, count[b + 1]);
+      }
+      return t;
+    };
+    // 3. feature groups, one blob each.  Inside a blob the tables of the group's GF features are
+    //    interleaved element by element (entry k of feature i sits at index k * GF + i), so that
+    //    the lanes of a warp, which hold one feature each, read different shared-memory banks
+    //    whatever k they probe.  Wide groups matter more than fine buckets: with 32 features a
+    //    warp's lookups never collide, and one more halving of a longer search window costs one
+    //    conflict-free load.  So for every run of features the widest power-of-two group is taken
+    //    for which some bucket density fits shared memory, densest first.
+    auto steps_for = [](uint32_t occ) {
+      uint32_t k = 0;
+      while ((1u << k) <= occ) ++k;  // 2^k > occ
+      return k;
+    };
+    std::vector<double> factors = {2.0, 1.0, 0.5, 0.25, 0.125};
+    int max_group = static_cast<int>(kQMaxGroupFeatures);
+    if (const char* e = std::getenv("B2FIL_Q_BUCKETS")) {  // tuning aid: buckets per threshold
+      const double forced = std::atof(e);
+      if (forced >= 0.01 && forced <= 16.0) factors = {forced};
+    }
+    if (const char* e = std::getenv("B2FIL_Q_GROUP")) {  // tuning aid: widest feature group
+      const int forced = std::atoi(e);
+      if (forced >= 1 && forced <= max_group && (forced & (forced - 1)) == 0) max_group = forced;
+    }
+    out.q_feats.assign(F, QFeature{});
+    out.q_groups.clear();
+    out.q_blob.clear();
+    out.view.q_max_blob_bytes = 0;
+    const uint32_t rec_bytes  = kQMaxGroupFeatures * sizeof(QFeatRec);
+    for (int f = 0; f < F;) {
+      int n = 0;
+      std::vector<FeatTable> tables;
+      uint32_t steps = 0, n_thr = 0, lut_bytes = 0, thr_bytes = 0;
+      for (int want = max_group; want >= 1 && n == 0; want /= 2) {
+        if (f + want > F) continue;  // a short tail is split into smaller powers of two
+        for (double factor : factors) {
+          std::vector<FeatTable> cand;
+          uint32_t st = 0, n_lut = 0, m_max = 0;
+          for (int g = f; g < f + want; ++g) {
+            cand.push_back(make_table(g, factor));
+            st    = std::max(st, steps_for(cand.back().max_occupancy));
+            n_lut = std::max(n_lut, cand.back().n_buckets);
+            m_max = std::max<uint32_t>(m_max, static_cast<uint32_t>(per[g].size()));
           }
-        }
-        qf.scale   = static_cast<double>(scale);
-        qf.offset  = static_cast<double>(offset);
-        qf.t_off   = static_cast<uint32_t>(total_thr);
-        qf.lut_off = static_cast<uint32_t>(total_lut);
-        total_thr += v.size();
-        total_lut += qf.n_buckets + 1;
-      }
-      out.q_thresholds.assign(total_thr * sizeof(T), 0);
-      out.q_lut.assign(total_lut, 0);
-      for (int f = 0; f < F; ++f) {
-        const QFeature& qf = out.q_feats[f];
-        const auto& v      = per[f];
-        std::vector<uint32_t> count(qf.n_buckets + 1, 0);
-        for (size_t i = 0; i < v.size(); ++i) {
-          put(out.q_thresholds, (qf.t_off + i) * sizeof(T), v[i]);
-          const uint32_t b = q_bucket_host<T>(v[i], static_cast<T>(qf.scale),
-                                              static_cast<T>(qf.offset), qf.n_buckets);
-          ++count[b + 1];  // lut[b'] counts thresholds in buckets below b'
-        }
-        uint32_t run = 0, occ = 0;
-        for (uint32_t b = 0; b <= qf.n_buckets; ++b) {
-          run += count[b];
-          occ = std::max(occ, count[b]);
-          out.q_lut[qf.lut_off + b] = static_cast<uint16_t>(run);
-        }
-        out.q_feats[f].max_occupancy = occ;
-      }
-      // 2. feature groups whose tables fit the quantisation kernel's shared memory, one blob each
-      auto steps_for = [](uint32_t occ) {
-        uint32_t k = 0;
-        while ((1u << k) <= occ) ++k;  // 2^k > occ
-        return k;
-      };
-      auto feat_bytes = [&](int f, uint32_t steps) {
-        const QFeature& qf = out.q_feats[f];
-        const uint32_t lut = ((qf.n_buckets + 1) * 2 + 7) / 8 * 8;
-        return lut + static_cast<uint32_t>(((qf.m + (1u << steps)) * sizeof(T) + 7) / 8 * 8);
-      };
-      out.q_groups.clear();
-      out.q_blob.clear();
-      const uint32_t rec_bytes = kQMaxGroupFeatures * sizeof(QFeatRec);
-      for (int f = 0; f < F;) {
-        // the largest power-of-two run of features whose blob (with the window padding of its
-        // fullest bucket) fits; a power of two lets every thread of the pre-pass keep one feature
-        int end        = f;
-        uint32_t steps = 0;
-        for (int want = static_cast<int>(kQMaxGroupFeatures); want >= 1; want /= 2) {
-          const int stop = std::min(F, f + want);
-          uint32_t st    = 0;
-          for (int g = f; g < stop; ++g) st = std::max(st, steps_for(out.q_feats[g].max_occupancy));
-          uint32_t bytes = rec_bytes;
-          for (int g = f; g < stop; ++g) bytes += feat_bytes(g, st);
-          if (bytes <= kQGroupSmemBudget && (stop - f == want || want == 1 || stop == F)) {
-            // a short tail group is rounded down to a power of two as well
-            int n = stop - f;
-            while (n & (n - 1)) n &= n - 1;
-            end   = f + n;
-            steps = st;
+          const uint32_t nt_ = m_max + (1u << st);  // window padding behind the longest table
+          const uint32_t lb  = (n_lut * want * 2 + 15) / 16 * 16;
+          const uint32_t tb  = static_cast<uint32_t>((static_cast<size_t>(nt_) * want * sizeof(T) + 15) / 16 * 16);
+          if (rec_bytes + lb + tb <= kQGroupSmemBudget) {
+            n         = want;
+            tables    = std::move(cand);
+            steps     = st;
+            n_thr     = nt_;
+            lut_bytes = lb;
+            thr_bytes = tb;
             break;
           }
         }
-        if (end == f) return -1;  // one feature alone exceeds the budget
-        QGroup g{};
-        g.f_begin  = static_cast<uint32_t>(f);
-        g.f_end    = static_cast<uint32_t>(end);
-        g.steps    = steps;
-        g.blob_off = static_cast<uint32_t>(out.q_blob.size());
-        std::vector<uint8_t> blob(rec_bytes, 0);
-        for (int h = f; h < end; ++h) {
-          const QFeature& qf = out.q_feats[h];
-          QFeatRec rec{};
-          rec.is_cat = qf.is_cat;
-          rec.nbm1   = qf.n_buckets - 1;
-          rec.scale  = qf.scale;
-          rec.offset = qf.offset;
-          rec.lut_off = static_cast<uint32_t>(blob.size());
-          blob.resize(blob.size() + ((qf.n_buckets + 1) * 2 + 7) / 8 * 8, 0);
-          std::memcpy(blob.data() + rec.lut_off, out.q_lut.data() + qf.lut_off,
-                      (qf.n_buckets + 1) * 2);
-          rec.thr_off = static_cast<uint32_t>(blob.size());
-          const size_t n_pad = qf.m + (size_t(1) << steps);
-          blob.resize(blob.size() + (n_pad * sizeof(T) + 7) / 8 * 8, 0);
-          std::memcpy(blob.data() + rec.thr_off, out.q_thresholds.data() + qf.t_off * sizeof(T),
-                      qf.m * sizeof(T));
-          const T nan = std::numeric_limits<T>::quiet_NaN();
-          for (size_t k = qf.m; k < n_pad; ++k) put(blob, rec.thr_off + k * sizeof(T), nan);
-          std::memcpy(blob.data() + (h - f) * sizeof(QFeatRec), &rec, sizeof(rec));
-        }
-        blob.resize((blob.size() + 15) / 16 * 16, 0);
-        g.blob_bytes = static_cast<uint32_t>(blob.size());
-        out.q_blob.insert(out.q_blob.end(), blob.begin(), blob.end());
-        out.view.q_max_blob_bytes = std::max<int64_t>(out.view.q_max_blob_bytes, g.blob_bytes);
-        out.q_groups.push_back(g);
-        f = end;
       }
-      return static_cast<int>(out.q_groups.size());
-    };
-    // two buckets per threshold keep the search windows short (measured on the 1000-tree
-    // depth-8 forest: the pre-pass takes 120 us per 114 k rows with two buckets per threshold and
-    // 16-feature groups, 196 us with one bucket per threshold and 32-feature groups); the coarser
-    // table is only the fallback when the finer one does not fit shared memory at all
-    {
-      uint32_t factor = 2;
-      if (const char* e = std::getenv("B2FIL_Q_BUCKETS")) {  // tuning aid: force 1 or 2
-        const int forced = std::atoi(e);
-        if (forced == 1 || forced == 2) factor = static_cast<uint32_t>(forced);
+      if (n == 0) return false;  // one feature alone exceeds the budget
+      QGroup g{};
+      g.f_begin  = static_cast<uint32_t>(f);
+      g.f_end    = static_cast<uint32_t>(f + n);
+      g.steps    = steps;
+      g.blob_off = static_cast<uint32_t>(out.q_blob.size());
+      std::vector<uint8_t> blob(rec_bytes + lut_bytes + thr_bytes, 0);
+      const T nan = std::numeric_limits<T>::quiet_NaN();
+      for (int h = f; h < f + n; ++h) {
+        const FeatTable& t = tables[h - f];
+        const auto& v      = per[h];
+        const uint32_t i   = static_cast<uint32_t>(h - f);
+        QFeature& qf       = out.q_feats[h];
+        qf.is_cat          = used_cat[h];
+        qf.m               = static_cast<uint32_t>(v.size());
+        qf.n_buckets       = t.n_buckets;
+        qf.max_occupancy   = t.max_occupancy;
+        qf.scale           = static_cast<double>(t.scale);
+        qf.offset          = static_cast<double>(t.offset);
+        QFeatRec rec{};
+        rec.is_cat  = qf.is_cat;
+        rec.nbm1    = t.n_buckets - 1;
+        rec.scale   = qf.scale;
+        rec.offset  = qf.offset;
+        rec.lut_off = rec_bytes + i * 2;  // entry k: + k * n * 2
+        rec.thr_off = rec_bytes + lut_bytes + i * static_cast<uint32_t>(sizeof(T));
+        for (uint32_t k = 0; k < t.n_buckets; ++k)
+          put(blob, rec.lut_off + static_cast<size_t>(k) * n * 2, t.lut[k]);
+        for (uint32_t k = 0; k < n_thr; ++k)
+          put(blob, rec.thr_off + static_cast<size_t>(k) * n * sizeof(T), k < v.size() ? v[k] : nan);
+        std::memcpy(blob.data() + i * sizeof(QFeatRec), &rec, sizeof(rec));
       }
-      if (build_tables(factor) < 0 && (factor == 1 || build_tables(1) < 0)) return false;
+      g.blob_bytes = static_cast<uint32_t>(blob.size());
+      out.q_blob.insert(out.q_blob.end(), blob.begin(), blob.end());
+      out.view.q_max_blob_bytes = std::max<int64_t>(out.view.q_max_blob_bytes, g.blob_bytes);
+      out.q_groups.push_back(g);
+      f += n;
     }
-    // 3. nodes: same heap layout as the dense blocks, 4 bytes per test node; forests with
+    // 4. nodes: same heap layout as the dense blocks, 4 bytes per test node; forests with
     //    categorical tests carry a third array with the 32-bit category set of every node
     const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
     const size_t es      = sizeof(T);
@@ -582,7 +580,7 @@ struct Packer {
         std::memcpy(&thr, src + i * nb, sizeof(T));
         std::memcpy(&meta, src + i * nb + sizeof(T), 4);
         const uint32_t feat = meta & 0x3FFFFFFFu;
-        uint32_t node       = ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | feat;
+        uint32_t node       = ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | (feat << Q_FEATURE_SHIFT);
         if (meta & META_CATEGORICAL) {
           uint32_t bits;  // the inline category set sits in the low word of the value slot
           std::memcpy(&bits, src + i * nb, 4);
@@ -591,14 +589,14 @@ struct Packer {
         } else {
           uint32_t j;
           if (std::isnan(thr)) {
-            j = 0xFFFFu;  // x < NaN never holds: always right
+            j = Q_NEVER_LEFT;  // x < NaN never holds: always right
           } else {
             const auto& v = per[feat];
             const auto it = std::lower_bound(v.begin(), v.end(), thr);
             // filler tests (both subtrees equal) need no real threshold
             j = (it != v.end() && *it == thr) ? static_cast<uint32_t>(it - v.begin()) : 0u;
           }
-          node |= j << 16;
+          node |= j << Q_RANK_SHIFT;
         }
         std::memcpy(dst + i * 4, &node, 4);
       }

@@ -167,7 +167,7 @@ def run_pack_check(pack_check, desc: ForestDesc, X, precision="single", layout="
     n = X.shape[0]
     ids = np.zeros((n, desc.n_trees), np.uint32)
     pay = np.zeros((n, desc.n_trees), np.float64)
-    info = np.zeros(8, np.int64)
+    info = np.zeros(12, np.int64)
     cd = desc.to_c()
     opts = CCreateOpts(0 if precision == "single" else 1, LAYOUTS[layout], STORAGES[storage],
                        align_bytes, 0, 0, row_quantization, 0)

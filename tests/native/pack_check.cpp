@@ -3,6 +3,7 @@
 // description and follows the packed nodes with the same index arithmetic as the kernels
 // (heap addressing for dense storage, child offsets and bit fields for sparse storage).
 // It is not part of libb2fil.so.
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -147,12 +148,15 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
         }
         const uint32_t b = q_bucket_host<T>(x, static_cast<T>(rec.scale),
                                             static_cast<T>(rec.offset), rec.nbm1 + 1);
+        // both tables are interleaved across the group's GF features
+        const size_t GF = g.f_end - g.f_begin;
         uint16_t lo16;
-        std::memcpy(&lo16, blob + rec.lut_off + b * 2, 2);
-        const T* thr = reinterpret_cast<const T*>(blob + rec.thr_off);
+        std::memcpy(&lo16, blob + rec.lut_off + b * GF * 2, 2);
         uint32_t pos = lo16;
         for (uint32_t s2 = (1u << g.steps) >> 1; s2 >= 1; s2 >>= 1) {
-          if (thr[pos + s2 - 1] <= x) pos += s2;
+          T thr;
+          std::memcpy(&thr, blob + rec.thr_off + (pos + s2 - 1) * GF * sizeof(T), sizeof(T));
+          if (thr <= x) pos += s2;
         }
         q[f] = static_cast<uint16_t>(pos);
       }
@@ -163,8 +167,8 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
       for (int l = 0; l < D; ++l) {
         uint32_t node;
         std::memcpy(&node, t + i * 4, 4);
-        const uint32_t qq = q[node & Q_FEATURE_MASK];
-        bool right = (static_cast<int32_t>(node) - static_cast<int32_t>(qq << 16)) < 0;
+        const uint32_t qq = q[(node & Q_FEATURE_FIELD) >> Q_FEATURE_SHIFT];
+        bool right = static_cast<int32_t>(node - (qq << Q_RANK_SHIFT)) < 0;
         if (node & Q_CATEGORICAL) {
           const size_t es = sizeof(T);
           uint32_t bits;
@@ -189,7 +193,9 @@ const char* pack_check_error() { return g_err.c_str(); }
 // Packs `desc` and walks n_rows rows.  ids: leaf id per (row, tree); payload: scalar leaf value
 // (or vector index) per (row, tree).  info[0..5] = format, storage, dense_depth, node_bytes,
 // n_nodes_packed, feat_bits; info[6] = 1 when a rank-quantised copy was built, info[7] = number of
-// (row, tree) pairs where the walk over that copy reaches another leaf.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
+// (row, tree) pairs where the walk over that copy reaches another leaf; info[8..11] = feature
+// groups of the quantised copy, most halvings of a group's search window, largest group blob in
+// bytes, features in the first group.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
 int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, const void* X,
                int64_t n_rows, int64_t stride, uint32_t* ids, double* payload, int64_t* info)
 {
@@ -204,6 +210,13 @@ int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, con
   info[5] = pf.view.feat_bits;
   info[6] = pf.view.q_enabled;
   info[7] = 0;
+  info[8] = static_cast<int64_t>(pf.q_groups.size());
+  info[9] = info[10] = info[11] = 0;
+  for (const QGroup& g : pf.q_groups) {
+    info[9]  = std::max<int64_t>(info[9], g.steps);
+    info[10] = std::max<int64_t>(info[10], g.blob_bytes);
+  }
+  if (!pf.q_groups.empty()) info[11] = pf.q_groups[0].f_end - pf.q_groups[0].f_begin;
   if (n_rows > 0) {
     if (opts->precision == B2FIL_F32) {
       walk<float>(pf, static_cast<const float*>(X), n_rows, stride, ids, payload);
