@@ -70,6 +70,7 @@ struct b2fil_forest {
   int64_t n_nodes_in = 0, n_nodes_packed = 0, device_bytes = 0;
   int32_t* status = nullptr;
   cudaMemPool_t pool = nullptr;  // stream-ordered scratch of the rank-quantised path
+  std::vector<uint32_t> q_top;   // host copy of the three top nodes per tree (may be empty)
   struct Block {
     void* ptr;
     size_t bytes;
@@ -181,6 +182,7 @@ int enqueue(const b2fil_forest* f, int kind, const void* X, int64_t n_rows, int6
   p.kind       = kind;
   p.threshold  = threshold;
   p.status     = f->status;
+  p.q_top      = f->q_top.empty() ? nullptr : f->q_top.data();
   std::string err;
   int64_t n = 0;
   const int rc =
@@ -276,6 +278,7 @@ int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* 
       if ((rc = upload(f.get(), pf.q_blob, offsetof(ForestView, q_blob))) != B2FIL_OK) return rc;
       if ((rc = upload(f.get(), pf.q_groups, offsetof(ForestView, q_groups))) != B2FIL_OK)
         return rc;
+      f->q_top = std::move(pf.q_top);
     }
     *out = f.release();
     return B2FIL_OK;
@@ -305,6 +308,7 @@ int b2fil_forest_clone_to_device(const b2fil_forest* src, int device_id, b2fil_f
     f->n_nodes_in     = src->n_nodes_in;
     f->n_nodes_packed = src->n_nodes_packed;
     f->default_chunk  = src->default_chunk;
+    f->q_top          = src->q_top;
     f->device         = device_id;
     DeviceGuard guard(device_id);
     if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
@@ -412,6 +416,7 @@ int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const voi
   p.kind       = infer_kind;
   p.threshold  = threshold;
   p.status     = f->status;
+  p.q_top      = f->q_top.empty() ? nullptr : f->q_top.data();
   std::string err;
   int64_t n = 0;
   rc = launch_predict_fixed_scratch(p, chunk_size > 0 ? chunk_size : f->default_chunk,

@@ -128,6 +128,10 @@ constexpr uint32_t Q_CATEGORICAL   = 0x1u;
 constexpr uint32_t Q_DEFAULT_LEFT  = 0x10000u;
 constexpr uint32_t Q_RANK_SHIFT    = 17;
 constexpr uint32_t Q_NEVER_LEFT    = 0x7FFFu;  // j of a test that no value passes
+// Forests of at most this many trees, at least two levels deep and without categorical tests also
+// keep the three top nodes of every tree on the host: the traversal kernel takes them as a launch
+// parameter and reads them through the constant cache instead of shared memory.
+constexpr int kQTopTrees = 2048;
 
 enum NodeFormat : int32_t {
   FMT_DENSE_F   = 0,
@@ -195,6 +199,7 @@ struct PackedForest {
   std::vector<uint8_t> out_scale;
   std::vector<uint8_t> out_bias;
   std::vector<uint8_t> q_nodes;
+  std::vector<uint32_t> q_top;  // root and its two children of every tree (3 words per tree), or empty
   std::vector<uint8_t> q_thresholds;
   std::vector<uint16_t> q_lut;
   std::vector<QFeature> q_feats;

@@ -27,6 +27,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <map>
+#include <cstring>
 #include <mutex>
 #include <utility>
 #include <type_traits>
@@ -928,9 +929,17 @@ __device__ __forceinline__ uint32_t rank_diff(uint32_t node, uint32_t q)
   return d;
 }
 
+// The three top nodes (heap words 1..3) of every tree, passed to the kernel by value: kernel
+// parameters live in the constant bank, so the first two levels of every walk read their nodes
+// through the constant cache and spend no shared-memory bandwidth, the resource that bounds the
+// traversal (a warp reads the same tree in all lanes, so each lookup is one constant access).
+struct QTop {
+  uint32_t w[3 * kQTopTrees];
+};
+
 // DEPTH > 0 fixes the tree depth at compile time (the level loop is fully unrolled); DEPTH == 0
-// reads it from the forest.
-template <typename T, int MODE, int NT, int DEPTH, bool CAT>
+// reads it from the forest.  TOPC: the first two levels take their nodes from `top`.
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
 struct DenseQWalker {
   using TR = Traits<T>;
   // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
@@ -940,8 +949,10 @@ struct DenseQWalker {
                                               int r, int64_t row, int lane, uint32_t bars,
                                               uint32_t stages, uint32_t stage_bytes,
                                               uint32_t row_addr, uint32_t stride_b, T* acc_group,
-                                              int R, RingPos& pos, Running<T>& run)
+                                              int R, RingPos& pos, Running<T>& run,
+                                              const QTop* top)
   {
+    static_assert(!TOPC || (DEPTH >= 2 && !CAT), "top nodes need two plain levels");
     const ForestView& f    = p.f;
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
@@ -968,11 +979,10 @@ struct DenseQWalker {
         a[k]    = base[k] + 4u;
       }
       // the NT walks are independent: all node loads are issued first, then all rank loads,
-      // so that their shared-memory latencies overlap inside one warp
-      auto level = [&]() {
-        uint32_t node[NT], q[NT];
-#pragma unroll
-        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
+      // so that their shared-memory latencies overlap inside one warp.
+      // test(): the rows' ranks against NT nodes; the sign bit of d[k] is the step to the right.
+      auto test = [&](const uint32_t(&node)[NT], uint32_t(&d)[NT]) {
+        uint32_t q[NT];
 #pragma unroll
         for (int k = 0; k < NT; ++k)
           // the low half of a node is feature * 4 (plus the categorical flag): without
@@ -982,27 +992,58 @@ struct DenseQWalker {
                              : __dp2a_lo(node[k], fstride, row_addr));
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
-          // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0:
-          // the sign bit of the difference is the step to the right child
-          uint32_t d = rank_diff(node[k], q[k]);
+          // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
+          d[k] = rank_diff(node[k], q[k]);
           if (CAT) {
             if (node[k] & Q_CATEGORICAL) {
               // the code of a categorical value is its category: a set bit sends it right
               const uint32_t bits = lds_u32(a[k] + cat_off);
-              d = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
+              d[k] = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
             }
           }
           if (NANS) {
-            if (q[k] == Q_NAN_CODE) d = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
+            if (q[k] == Q_NAN_CODE) d[k] = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
           }
+        }
+      };
+      auto level = [&]() {
+        uint32_t node[NT], d[NT];
+#pragma unroll
+        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
+        test(node, d);
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
           // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
-          idx[k] = __funnelshift_l(d, idx[k], 1);
+          idx[k] = __funnelshift_l(d[k], idx[k], 1);
           a[k]   = idx[k] * 4u + base[k];
         }
       };
+      if (TOPC) {
+        // root and children from the constant bank: the same words in every lane
+        uint32_t n1[NT], n2[NT], n3[NT], node[NT], d[NT];
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          const int t = 3 * (first + (FULL ? k : min(k, n_act - 1)));
+          n1[k]       = top->w[t];
+          n2[k]       = top->w[t + 1];
+          n3[k]       = top->w[t + 2];
+        }
+        test(n1, d);
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          node[k] = static_cast<int32_t>(d[k]) < 0 ? n3[k] : n2[k];
+          idx[k]  = __funnelshift_l(d[k], 1u, 1);
+        }
+        test(node, d);
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          idx[k] = __funnelshift_l(d[k], idx[k], 1);
+          a[k]   = idx[k] * 4u + base[k];
+        }
+      }
       if (DEPTH > 0) {
 #pragma unroll
-        for (int lvl = 0; lvl < DEPTH; ++lvl) level();
+        for (int lvl = TOPC ? 2 : 0; lvl < DEPTH; ++lvl) level();
       } else {
 #pragma unroll 4
         for (int lvl = 0; lvl < D; ++lvl) level();
@@ -1047,11 +1088,11 @@ struct DenseQWalker {
   }
 };
 
-template <typename T, int MODE, int NT, int DEPTH, bool CAT>
-__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
-dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
-               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
-               const int K)
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
+__device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint16_t* __restrict__ Q,
+                                             const int32_t* __restrict__ tile_flags, const int R,
+                                             const int G, const int S, const int K,
+                                             const QTop* top)
 {
   using TR = Traits<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -1147,13 +1188,13 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
     Running<T> run{T(0), 0};
     if (ok) {
       if (nans) {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<true>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<true>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, pos, run);
+          acc_group, R, pos, run, top);
       } else {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT>::template walk<false>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<false>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, pos, run);
+          acc_group, R, pos, run, top);
       }
       if (!ok) atomicExch(p.status, 2);
     }
@@ -1166,6 +1207,26 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
     }
     consumer_sync(n_ct);
   }
+}
+
+
+template <typename T, int MODE, int NT, int DEPTH, bool CAT>
+__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
+dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
+               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
+               const int K)
+{
+  dense_q_body<T, MODE, NT, DEPTH, CAT, false>(p, Q, tile_flags, R, G, S, K, nullptr);
+}
+
+// Same kernel with the top nodes of every tree in the parameter block.
+template <typename T, int MODE, int NT, int DEPTH>
+__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
+dense_q_top_kernel(const __grid_constant__ PredictParams p, const uint16_t* __restrict__ Q,
+                   const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
+                   const int K, const __grid_constant__ QTop top)
+{
+  dense_q_body<T, MODE, NT, DEPTH, false, true>(p, Q, tile_flags, R, G, S, K, &top);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1539,6 +1600,28 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
   if constexpr (std::is_same<T, float>::value) {
     // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies with six
     // trees in flight (q_max_trees_in_flight offers six only for them)
+    if (c.trees_in_flight == 6 && p.q_top != nullptr && p.f.n_trees <= kQTopTrees) {
+      // the three top nodes of every tree travel in the parameter block
+      static thread_local QTop top;
+      std::memcpy(top.w, p.q_top, static_cast<size_t>(p.f.n_trees) * 3 * sizeof(uint32_t));
+#define B2FIL_Q_TOP_CASE(DD)                                                                   \
+  {                                                                                            \
+    auto k = dense_q_top_kernel<T, MODE_SCALAR, 6, DD>;                                        \
+    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                          \
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups,  \
+                                                 c.stages, c.sub_batches, top);                \
+  }
+      switch (p.f.dense_depth) {
+        case 4: B2FIL_Q_TOP_CASE(4) return B2FIL_OK;
+        case 5: B2FIL_Q_TOP_CASE(5) return B2FIL_OK;
+        case 6: B2FIL_Q_TOP_CASE(6) return B2FIL_OK;
+        case 7: B2FIL_Q_TOP_CASE(7) return B2FIL_OK;
+        case 8: B2FIL_Q_TOP_CASE(8) return B2FIL_OK;
+        case 9: B2FIL_Q_TOP_CASE(9) return B2FIL_OK;
+        default: B2FIL_Q_TOP_CASE(10) return B2FIL_OK;
+      }
+#undef B2FIL_Q_TOP_CASE
+    }
     if (c.trees_in_flight == 6) {
       switch (p.f.dense_depth) {
         case 4: B2FIL_Q_CASE(MODE_SCALAR, 6, 4) return B2FIL_OK;

@@ -19,6 +19,9 @@ struct PredictParams {
   int32_t kind;        // B2FIL_INFER_*
   double threshold;    // binary decision threshold of B2FIL_INFER_CLASS
   int32_t* status;     // device word: set non-zero when a bounded wait inside a kernel ran out
+  // HOST memory, never read on the device: three top nodes per tree of the rank-quantised copy
+  // (PackedForest::q_top), or null; the launch code copies them into a kernel parameter
+  const uint32_t* q_top;
 };
 
 // Shape of one dense launch.

@@ -602,6 +602,13 @@ struct Packer {
       }
       std::memcpy(dst + width * 4, src + width * nb, static_cast<size_t>(width) * es);
     }
+    out.q_top.clear();
+    if (!has_cat && D >= 2 && nt <= kQTopTrees) {
+      out.q_top.resize(static_cast<size_t>(nt) * 3);
+      for (int p = 0; p < nt; ++p)  // heap words 1..3 of the tree
+        std::memcpy(out.q_top.data() + static_cast<size_t>(p) * 3,
+                    out.q_nodes.data() + static_cast<size_t>(qstride) * p + 4, 12);
+    }
     out.view.q_has_cat     = has_cat ? 1 : 0;
     out.view.q_enabled     = 1;
     out.view.q_n_groups    = static_cast<int32_t>(out.q_groups.size());
@@ -831,6 +838,7 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
     if (!ok) {
       out.q_nodes.clear();
       out.q_thresholds.clear();
+      out.q_top.clear();
       out.q_lut.clear();
       out.q_feats.clear();
       out.q_groups.clear();
