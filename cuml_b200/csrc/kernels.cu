@@ -1509,7 +1509,7 @@ size_t dense_q_smem(size_t qstride, int precision, int F, int NC, bool reduce, i
 // Most trees a warp of the quantised kernel may walk side by side: the kernels that exist.
 int q_max_trees_in_flight(const ForestView& f, int mode)
 {
-  if (f.q_has_cat) return 2;
+  if (f.q_has_cat) return 4;
   const bool specialised = f.format == FMT_DENSE_F && mode == MODE_SCALAR && f.dense_depth >= 4 &&
                            f.dense_depth <= 10;
   return specialised ? 6 : 4;
@@ -1579,22 +1579,22 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
                                                  c.stages, c.sub_batches);                  \
   }
   if (p.f.q_has_cat) {
-    // forests with categorical tests: two trees in flight at most (dense_q_config honours it)
-    if (c.trees_in_flight == 2) {
-      switch (mode) {
-        case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, 2, 0, true) break;
-        case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, 2, 0, true) break;
-        case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, 2, 0, true) break;
-        default: B2FIL_Q_CASE_CAT(MODE_LEAFID, 2, 0, true) break;
-      }
+    // forests with categorical tests: four trees in flight at most (dense_q_config honours it)
+#define B2FIL_Q_CAT_MODES(N)                                            \
+  switch (mode) {                                                       \
+    case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, N, 0, true) break;  \
+    case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, N, 0, true) break;  \
+    case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, N, 0, true) break; \
+    default: B2FIL_Q_CASE_CAT(MODE_LEAFID, N, 0, true) break;           \
+  }
+    if (c.trees_in_flight == 4) {
+      B2FIL_Q_CAT_MODES(4)
+    } else if (c.trees_in_flight == 2) {
+      B2FIL_Q_CAT_MODES(2)
     } else {
-      switch (mode) {
-        case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, 1, 0, true) break;
-        case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, 1, 0, true) break;
-        case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, 1, 0, true) break;
-        default: B2FIL_Q_CASE_CAT(MODE_LEAFID, 1, 0, true) break;
-      }
+      B2FIL_Q_CAT_MODES(1)
     }
+#undef B2FIL_Q_CAT_MODES
     return B2FIL_OK;
   }
   if constexpr (std::is_same<T, float>::value) {

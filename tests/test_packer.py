@@ -200,3 +200,39 @@ def test_rank_quantisation_off_and_limits(pack_check):
     for prec in ("single", "double"):
         info = _check(pack_check, desc, X, prec, "depth_first", "dense")
         assert info[6] == 1
+
+
+def test_rank_tables_feature_groups(pack_check):
+    """The rank tables are interleaved across power-of-two groups of features: 70 features make
+    groups of 32, 32, 4 and 2, and the walk over the quantised copy still reaches every leaf,
+    also with NaN rows and with thresholds crowded into a few buckets."""
+    desc = random_forest_desc(31, n_trees=40, n_features=70, max_depth=7, mixed_ops=True)
+    # crowd the thresholds of feature 0 next to each other so that its search window grows
+    num = (desc.node_kind == 1) & (desc.feature == 0)
+    desc.threshold[num] = 1.0 + 1e-6 * np.arange(int(num.sum()))
+    X = random_rows(32, 600, 70, np.float32, nan_frac=0.05)
+    X[:200, 0] = (1.0 + 1e-6 * np.arange(200)).astype(np.float32)
+    for prec in ("single", "double"):
+        info = _check(pack_check, desc, X, prec, "depth_first", "dense")
+        assert info[6] == 1
+        assert info[8] == 4 and info[11] == 32  # groups, width of the first one
+        assert info[10] <= 208 * 1024
+
+
+def test_rank_quantisation_threshold_limit(pack_check):
+    """A feature with more distinct thresholds than a rank can number keeps the forest on the
+    plain dense path."""
+    from cuml_b200.fil._desc import ForestDesc
+
+    n = 16400  # one more stump than the 16,382 thresholds a feature may have, and then some
+    kind = np.tile([1, 0, 0], n)
+    desc = ForestDesc(n_features=2, n_outputs=1, tree_offsets=np.arange(0, 3 * n + 1, 3),
+                      node_kind=kind, feature=np.zeros(3 * n, np.int32),
+                      threshold=np.repeat(np.arange(n, dtype=np.float64), 3),
+                      left=np.tile([1, -1, -1], n), right=np.tile([2, -1, -1], n),
+                      default_left=np.zeros(3 * n, np.int32),
+                      leaf_value=np.tile([0.0, 1.0, 2.0], n))
+    X = random_rows(33, 20, 2, np.float32) * 5000
+    rc, ids, _, info = run_pack_check(pack_check, desc, X, storage="dense")
+    assert rc == 0 and info[1] == 1 and info[6] == 0
+    assert np.array_equal(ids, oracle.predict(desc, X, INFER_LEAF_ID, "single"))
