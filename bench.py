@@ -35,10 +35,10 @@ ROWS_PER_GPU = 10_000_000
 BYTES_PER_ROW = N_FEATURES * 4 + 2 * 4
 WORKLOAD = "gbdt_1000x_depth8_256f_fp32_sigmoid_10M_rows"
 # dram__bytes_read.sum + dram__bytes_write.sum per row of the two kernels of a prediction, from
-# the ncu captures of a 1 M-row case summarised under profiles/ (quantise 1697 B + dense_q 525 B;
+# the ncu captures of a 1 M-row case summarised under profiles/ (quantise 1560 B + dense_q 525 B;
 # the rank image of a chunk is larger than L2 and goes through HBM); traffic grows in proportion to
 # the rows, so it is scaled to the batch
-NCU_TRAFFIC_BYTES_PER_ROW = 2222
+NCU_TRAFFIC_BYTES_PER_ROW = 2085
 
 
 def measured_peak():
@@ -318,7 +318,7 @@ def run_ours(args):
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * n
                                      if NCU_TRAFFIC_BYTES_PER_ROW else None),
-                         "kernel": "quantise_kernel<float> + dense_q_kernel<float,MODE_SCALAR,4,8,false>",
+                         "kernel": "quantise_kernel<float> + dense_q_top_kernel<float,MODE_SCALAR,6,8>",
                          "kernel_ms": k_ms, "algorithmic_bytes_per_row": BYTES_PER_ROW},
             "e2e": e2e,
             "gpu_launches": int(launches),

@@ -158,6 +158,13 @@ struct Traits<float> {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
   }
+  // read-only global load that stays where it is written (the compiler may not sink it)
+  static __device__ __forceinline__ float ldg_here(const float* ptr)
+  {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
+    return v;
+  }
   template <uint32_t OFF>
   static __device__ __forceinline__ float ld_real_at(uint32_t a)  // [a + OFF], OFF an immediate
   {
@@ -204,6 +211,12 @@ struct Traits<double> {
   {
     double v;
     asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(a));
+    return v;
+  }
+  static __device__ __forceinline__ double ldg_here(const double* ptr)
+  {
+    double v;
+    asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(ptr));
     return v;
   }
   template <uint32_t OFF>
@@ -669,7 +682,7 @@ __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
 // divides the thread count, so a thread keeps one feature for good (its record sits in registers)
 // and with 32-feature groups a warp reads 128 contiguous bytes of one row per load and its 32
 // table lookups never share a bank.  A thread owns NU consecutive slots of the rank tile (slot =
-// q_slot(row)); it ranks them four at a time while the loads of the next four are in flight,
+// q_slot(row)); it ranks them four at a time while the loads of its next tile are in flight,
 // packs the ranks two per word and writes its piece of Q[tile][feature][slot] (uint16) with one
 // vector store, the layout the traversal kernel pulls into shared memory with a single bulk
 // copy.  Nothing is exchanged between threads, so the tile loop has no barrier.  NaN becomes
@@ -728,7 +741,7 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
   const uint32_t e_mine  = b * e1 + grp.f_begin + i;
   const T* X             = static_cast<const T*>(p.X);
 
-  T xs[CH];
+  T xs[NU];
   // loads chunk c (slots s0 + c * CH ...) of tile t
   auto fetch = [&](int64_t t, int c) {
     const int64_t row0 = t * R;
@@ -737,16 +750,20 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
     if (row0 + R <= p.n_rows) {
 #pragma unroll
       for (int u = 0; u < CH; ++u)
-        xs[u] = active ? __ldg(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
+        xs[c * CH + u] = active ? TR::ldg_here(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
     } else {
 #pragma unroll
       for (int u = 0; u < CH; ++u) {
         const int64_t row = row0 + b + c * (CH / 2) + (u >> 1) + 32 * (u & 1);
-        xs[u] = (active && row < p.n_rows) ? __ldg(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
+        xs[c * CH + u] =
+          (active && row < p.n_rows) ? TR::ldg_here(tb + (cb + (u >> 1) * e1 + (u & 1) * e32)) : T(0);
       }
     }
   };
-  if (blockIdx.x < n_tiles) fetch(blockIdx.x, 0);
+  if (blockIdx.x < n_tiles) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) fetch(blockIdx.x, c);
+  }
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     uint32_t packed[NU > 1 ? NU / 2 : 1];
     bool saw_nan = false;
@@ -754,13 +771,10 @@ __device__ __forceinline__ void quantise_tiles(const PredictParams& p, const QGr
     for (int c = 0; c < NCH; ++c) {
       T cur[CH];
 #pragma unroll
-      for (int u = 0; u < CH; ++u) cur[u] = xs[u];
-      // the loads of the next chunk fly while this one is ranked
-      if (c + 1 < NCH) {
-        fetch(t, c + 1);
-      } else if (t + gridDim.x < n_tiles) {
-        fetch(t + gridDim.x, 0);
-      }
+      for (int u = 0; u < CH; ++u) cur[u] = xs[c * CH + u];
+      // the same chunk of the CTA's next tile is requested right away, so a whole tile of loads
+      // per thread stays in flight (an additional L2 prefetch further ahead measured slower)
+      if (t + gridDim.x < n_tiles) fetch(t + gridDim.x, c);
       // rank of the CH values, step by step across all of them so that the dependent
       // shared-memory lookups of different values overlap.  A NaN walks the same code (bucket 0,
       // every comparison false) and is replaced by Q_NAN_CODE at the end; so does a categorical
