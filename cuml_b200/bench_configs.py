@@ -17,6 +17,7 @@ module is the quick way to see the other shapes.
       categories), 5 % NaN, softmax, 20 M rows
   c5  2000 complete depth-10 trees, 512 fp32 features; 20 M rows per pass (100 M x 512 fp32 does
       not fit one GPU's memory)
+  sweep  the c2 forest at batch sizes 1 ... 10 M: back-to-back GPU time per call
 """
 from __future__ import annotations
 
@@ -155,6 +156,24 @@ def run(config: str, steps: int, scale: float):
         out = torch.empty((n, 2), device="cuda:0", dtype=torch.float32)
         ms = _time(lambda: fi.predict_proba(Xd, preds=out), steps)
         report("c5", "predict_proba", n, ms, 512 * 4 + 2 * 4, fi)
+    elif config == "sweep":
+        fi = ForestInference.load_from_treelite_model(synthetic_complete_forest(1000, 8, 256, 2))
+        big = int(10_000_000 * scale)
+        Xd = _randn_rows(big, 256, torch.float32, 3)
+        out = torch.empty((big, 2), device="cuda:0", dtype=torch.float32)
+        for n in (1, 8, 64, 512, 1024, 4096, 32768, 65536, 262144, 1_000_000, big):
+            n = min(n, big)
+            # rotate through the resident rows so that small batches do not re-read L2-hot rows
+            starts = [(i * n) % max(1, big - n + 1) for i in range(64)]
+            state = {"i": 0}
+
+            def call():
+                b = starts[state["i"] % len(starts)]
+                state["i"] += 1
+                fi.predict_proba(Xd[b:b + n], preds=out[:n])
+
+            ms = _time(call, max(steps, 200 if n <= 65536 else steps))
+            report("sweep", f"predict_proba batch {n}", n, ms, 256 * 4 + 2 * 4, fi)
     else:
         raise ValueError(f"unknown config {config}")
     return lines
