@@ -580,3 +580,28 @@ def test_graph_replay_of_a_small_batch():
         np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), rtol=1e-6, atol=1e-7)
     with pytest.raises(ValueError):
         graphed(torch.zeros((100, 32), device="cuda:0"))
+
+
+@pytest.mark.parametrize("n_trees,depth,n_classes", [(300, 5, 3), (2100, 4, 1), (40, 3, 1),
+                                                     (30, 12, 1), (1, 2, 1), (37, 10, 1)])
+def test_quantised_traversal_kernel_variants(n_trees, depth, n_classes):
+    """Every variant of the traversal over rank-quantised rows: top nodes in the parameter block
+    (up to 2048 trees of depth 4..10), the same depth-specialised kernel without them (more
+    trees), the generic-depth kernel (depth 3 and 12), partial tree batches, NaN and NaN-free
+    tiles, one and several classes."""
+    kw = dict(n_classes=n_classes) if n_classes > 1 else {}
+    desc = synthetic_complete_forest(n_trees, depth, 24, seed=40 + depth, **kw)
+    rng = np.random.default_rng(41)
+    n = 6000
+    X = rng.standard_normal((n, 24)).astype(np.float32)
+    X[:3000][rng.random((3000, 24)) < 0.05] = np.nan  # the second half stays NaN-free
+    fi = ForestInference.load_from_treelite_model(desc)
+    assert fi.describe()["row_quantization"] == 1
+    Xd = _dev(X, "single")
+    for chunk_size in (8, 2):  # 256-row and 64-row tiles of the quantised path
+        raw = fi._run(Xd, INFER_DEFAULT, chunk_size).cpu().numpy()
+        np.testing.assert_allclose(raw, oracle.predict(desc, X, INFER_DEFAULT, "single"),
+                                   **_tol(desc, "single"))
+        ids = fi.apply(Xd, chunk_size=chunk_size).cpu().numpy()
+        assert np.array_equal(ids.astype(np.uint32),
+                              oracle.predict(desc, X, INFER_LEAF_ID, "single"))
