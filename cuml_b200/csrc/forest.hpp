@@ -69,7 +69,7 @@ struct SparseNode16D {  // fp64
 //     x < T[j]  <=>  r(x) <= j.
 // A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x3FFF); the traversal kernel
 // then reads 2-byte values and 4-byte nodes
-//     bits 31..17: j (0x7FFF = never left)   bit 16: missing goes left
+//     bits 31..17: j (0x7FFF = never left)   bit 16: missing goes right
 //     bits 15..2: feature                    bit 0: categorical
 // so a test is one signed subtraction: right <=> int(node) - (rank << 17) < 0 (the flag in bit 16
 // is below the weight of one rank and cannot change the sign), and the low half is the feature
@@ -125,7 +125,7 @@ constexpr uint32_t Q_MAX_FEATURES  = 0x4000u;
 constexpr uint32_t Q_FEATURE_FIELD = 0xFFFCu;  // feature << 2
 constexpr uint32_t Q_FEATURE_SHIFT = 2;
 constexpr uint32_t Q_CATEGORICAL   = 0x1u;
-constexpr uint32_t Q_DEFAULT_LEFT  = 0x10000u;
+constexpr uint32_t Q_DEFAULT_RIGHT = 0x10000u;  // missing values go right (stored in this sense: << 15 makes it the sign)
 constexpr uint32_t Q_RANK_SHIFT    = 17;
 constexpr uint32_t Q_NEVER_LEFT    = 0x7FFFu;  // j of a test that no value passes
 // Forests of at most this many trees, at least two levels deep and without categorical tests also

@@ -929,7 +929,7 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
 // Shared memory: [mbarriers 128 B][row tile F x R uint16][accumulators][flags 16 B][S tree stages].
 // The row tile arrives with one bulk copy per tile (the pre-pass already stored it feature-major);
 // tree batches stream through the stage ring exactly as in dense_kernel.  A node is 4 bytes
-// (rank j << 17 | default-left << 16 | feature << 2 | categorical) and a test is one signed
+// (rank j << 17 | default-right << 16 | feature << 2 | categorical) and a test is one signed
 // subtraction.
 constexpr int kBarTileFull  = 2 * kMaxStages;      // mbarrier slots after the stage ring
 constexpr int kBarTileEmpty = 2 * kMaxStages + 1;
@@ -1004,19 +1004,33 @@ struct DenseQWalker {
           // half x byte 1 = 0) turns it into the address of the row's rank of that feature
           q[k] = lds_u16(CAT ? (node[k] & Q_FEATURE_FIELD) * fstride + row_addr
                              : __dp2a_lo(node[k], fstride, row_addr));
+        // forests with categorical tests: the 32-bit category set of every node, fetched for
+        // all nodes (numerical ones hold an empty set) to keep the walk free of branches
+        uint32_t bits[CAT ? NT : 1];
+        if (CAT) {
+#pragma unroll
+          for (int k = 0; k < NT; ++k) bits[k] = lds_u32(a[k] + cat_off);
+        }
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
           d[k] = rank_diff(node[k], q[k]);
           if (CAT) {
-            if (node[k] & Q_CATEGORICAL) {
-              // the code of a categorical value is its category: a set bit sends it right
-              const uint32_t bits = lds_u32(a[k] + cat_off);
-              d[k] = (q[k] < 32u && ((bits >> (q[k] & 31u)) & 1u)) ? 0x80000000u : 0u;
-            }
+            // the code of a categorical value is its category and a set bit of the node's set
+            // sends it right: the clamped funnel shift moves bit q to the sign position and
+            // yields 0 for every code of 32 and above (no category, NaN)
+            const uint32_t dc = __funnelshift_lc(0u, bits[k], 31u - q[k]);
+            d[k]              = (node[k] & Q_CATEGORICAL) ? dc : d[k];
           }
           if (NANS) {
-            if (q[k] == Q_NAN_CODE) d[k] = (node[k] & Q_DEFAULT_LEFT) ? 0u : 0x80000000u;
+            // the missing-goes-right flag sits 15 bits below the sign.  (Both forms compute the
+            // same; each kernel family keeps the one it was measured fastest with: the two walks
+            // of a kernel share its register allocation.)
+            if (CAT) {
+              if (q[k] == Q_NAN_CODE) d[k] = node[k] << 15;
+            } else {
+              if (q[k] == Q_NAN_CODE) d[k] = (node[k] & Q_DEFAULT_RIGHT) ? 0x80000000u : 0u;
+            }
           }
         }
       };
@@ -1062,6 +1076,14 @@ struct DenseQWalker {
 #pragma unroll 4
         for (int lvl = 0; lvl < D; ++lvl) level();
       }
+      // scalar leaves of a multi-class forest: trees are stored class by class, so when the
+      // first and the last tree of the sub-batch feed the class of the running sum, all do
+      bool same_class = false;
+      if (MODE == MODE_SCALAR && CAT) {
+        same_class = f.n_outputs == 1 ||
+                     (__ldg(f.tree_class + first) == run.cls &&
+                      __ldg(f.tree_class + first + n_act - 1) == run.cls);
+      }
 #pragma unroll
       for (int k = 0; k < NT; ++k) {
         if (FULL || k < n_act) {
@@ -1070,9 +1092,13 @@ struct DenseQWalker {
           const uint32_t slot   = idx[k] - (1u << D);
           const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
           const typename TR::Val payload = TR::ld_val(leaf_a);
-          take_leaf<T, MODE>(p, first + k, payload,
-                             (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r, row,
-                             run);
+          if (MODE == MODE_SCALAR && CAT && same_class) {
+            run.sum += TR::as_real(payload);
+          } else {
+            take_leaf<T, MODE>(p, first + k, payload,
+                               (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
+                               row, run);
+          }
         }
       }
     };
@@ -1602,6 +1628,18 @@ int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const 
     default: B2FIL_Q_CASE_CAT(MODE_LEAFID, N, 0, true) break;           \
   }
     if (c.trees_in_flight == 4) {
+      if constexpr (std::is_same<T, float>::value) {
+        if (mode == MODE_SCALAR) {  // fp32 scalar leaves: depth-specialised bodies
+          switch (p.f.dense_depth) {
+            case 4: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 4, true) return B2FIL_OK;
+            case 5: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 5, true) return B2FIL_OK;
+            case 6: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 6, true) return B2FIL_OK;
+            case 7: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 7, true) return B2FIL_OK;
+            case 8: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 8, true) return B2FIL_OK;
+            default: break;
+          }
+        }
+      }
       B2FIL_Q_CAT_MODES(4)
     } else if (c.trees_in_flight == 2) {
       B2FIL_Q_CAT_MODES(2)

@@ -580,7 +580,7 @@ struct Packer {
         std::memcpy(&thr, src + i * nb, sizeof(T));
         std::memcpy(&meta, src + i * nb + sizeof(T), 4);
         const uint32_t feat = meta & 0x3FFFFFFFu;
-        uint32_t node       = ((meta & META_DEFAULT_LEFT) ? Q_DEFAULT_LEFT : 0u) | (feat << Q_FEATURE_SHIFT);
+        uint32_t node       = ((meta & META_DEFAULT_LEFT) ? 0u : Q_DEFAULT_RIGHT) | (feat << Q_FEATURE_SHIFT);
         if (meta & META_CATEGORICAL) {
           uint32_t bits;  // the inline category set sits in the low word of the value slot
           std::memcpy(&bits, src + i * nb, 4);

@@ -175,7 +175,7 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
           std::memcpy(&bits, t + (size_t(1) << D) * (4 + es) + i * 4, 4);
           right = qq < 32u && ((bits >> qq) & 1u);
         }
-        if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_LEFT) == 0u;
+        if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_RIGHT) != 0u;
         i = 2 * i + (right ? 1 : 0);
       }
       const uint32_t slot = i - (1u << D);
