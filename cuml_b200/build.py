@@ -14,8 +14,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libb2fil.so")
-SOURCES = ["api.cu", "kernels.cu", "pack.cpp"]
-HEADERS = ["forest.hpp", "kernels.hpp", os.path.join("..", "..", "include", "b2fil.h")]
+SOURCES = ["api.cu", "kernels.cu", "kernels_q_top6.cu", "kernels_q_plain6.cu", "kernels_q_plain4.cu",
+           "kernels_q_cat.cu", "kernels_q_generic.cu", "pack.cpp"]
+HEADERS = ["forest.hpp", "kernels.hpp", "kernels_q.hpp", "device_common.cuh", "dense_q.cuh",
+           os.path.join("..", "..", "include", "b2fil.h")]
 
 
 def _nvcc() -> str:
@@ -39,17 +41,39 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not all(os.path.exists(os.path.join(SRC, s)) for s in SOURCES):
         raise RuntimeError("kernel sources missing; cannot build libb2fil.so")
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
-           "-std=c++17", "-Xcompiler", "-fPIC,-Wall", "-Xptxas", "-v", "-shared", "-o", LIB]
-    cmd += [os.path.join(SRC, s) for s in SOURCES]
-    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    # one nvcc per translation unit, all at once (the kernel families are split over several
+    # files for exactly this), then one link step
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    base = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+            "-Xcompiler", "-fPIC,-Wall", "-Xptxas", "-v"]
+    jobs = []
+    for src in SOURCES:
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
+        cmd = base + ["-c", os.path.join(SRC, src), "-o", obj]
+        out = open(obj + ".log", "w+")  # a file, not a pipe: nothing blocks while others run
+        jobs.append((cmd, obj, subprocess.Popen(cmd, stdout=out, stderr=subprocess.STDOUT), out))
+    log, failed = [], False
+    for cmd, obj, proc, out in jobs:
+        proc.wait()
+        out.seek(0)
+        log.append(" ".join(cmd) + "\n" + out.read())
+        out.close()
+        failed |= proc.returncode != 0
+    if not failed:
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB]
+        cmd += [obj for _, obj, _, _ in jobs]
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        log.append(" ".join(cmd) + "\n" + proc.stdout)
+        failed = proc.returncode != 0
+    text = "\n".join(log)
     with open(os.path.join(LIB_DIR, "ptxas.log"), "w") as fh:
-        fh.write(" ".join(cmd) + "\n" + proc.stdout)
-    if proc.returncode != 0:
-        sys.stderr.write(proc.stdout)
+        fh.write(text)
+    if failed:
+        sys.stderr.write(text)
         raise RuntimeError("nvcc failed building libb2fil.so")
     if verbose:
-        print(proc.stdout)
+        print(text)
     return LIB
 
 

@@ -20,431 +20,14 @@
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel sets the status word,
 // stops working and returns.
-#include <cuda_runtime.h>
-
-#include <algorithm>
-#include <cstdint>
-#include <cstdio>
-#include <cstdlib>
 #include <map>
-#include <cstring>
 #include <mutex>
-#include <utility>
-#include <type_traits>
 
-#include "kernels.hpp"
+#include "device_common.cuh"
+#include "kernels_q.hpp"
 
 namespace b2fil {
 namespace {
-
-#ifndef B2FIL_SPIN_NS
-#define B2FIL_SPIN_NS 256  // sleep between two tries of a bounded mbarrier wait
-#endif
-constexpr uint32_t kSpinLimit = 1u << 22;  // tries of a bounded mbarrier wait
-constexpr int kBarBytes       = 256;       // room for the mbarriers at the start of shared memory
-constexpr int kMaxStages      = 8;
-
-// ---------------------------------------------------------------------------------------------
-// shared-memory and mbarrier primitives (inline PTX)
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void* p)
-{
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_fence_init()
-{
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-  uint32_t ok;
-  asm volatile(
-    "{\n"
-    ".reg .pred p;\n"
-    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-    "selp.u32 %0, 1, 0, p;\n"
-    "}\n"
-    : "=r"(ok)
-    : "r"(bar), "r"(parity)
-    : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the barrier did not complete within kSpinLimit tries (each try blocks
-// for a hardware-defined short time, then the warp sleeps briefly).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
-{
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    // a waiting warp must not compete for issue slots with the warps that are walking trees
-#if B2FIL_SPIN_NS > 0
-    __nanosleep(B2FIL_SPIN_NS);
-#endif
-  }
-  return false;
-}
-// Position in a ring of S stages: the stage index and the parity of its current use, advanced
-// without a division.
-struct RingPos {
-  uint32_t stage = 0, phase = 0;
-  __device__ __forceinline__ void advance(int S)
-  {
-    if (++stage == static_cast<uint32_t>(S)) {
-      stage = 0;
-      phase ^= 1u;
-    }
-  }
-};
-
-// Bulk asynchronous copy global -> shared memory of this CTA, completing `bytes` on `bar`.
-// Both addresses are 16-byte aligned and `bytes` is a multiple of 16.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                              uint32_t bar)
-{
-  asm volatile(
-    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-      dst),
-    "l"(src), "r"(bytes), "r"(bar)
-    : "memory");
-}
-__device__ __forceinline__ uint32_t lds_u32(uint32_t a)
-{
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds_u16(uint32_t a)
-{
-  uint32_t v;  // a 16-bit load into a 32-bit register zero-extends
-  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-// Barrier among the consumer threads only (the producer warp never joins it).
-__device__ __forceinline__ void consumer_sync(int n_threads)
-{
-  asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory");
-}
-
-// ---------------------------------------------------------------------------------------------
-// per-precision traits
-// ---------------------------------------------------------------------------------------------
-template <typename T>
-struct Traits;
-
-template <>
-struct Traits<float> {
-  using Val                    = uint32_t;
-  static constexpr uint32_t NB = 8;  // dense node bytes
-  static constexpr uint32_t ES = 4;  // element bytes (rows, leaves, outputs)
-  static __device__ __forceinline__ void ld_node(uint32_t a, Val& v, uint32_t& m)
-  {
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(m) : "r"(a));
-  }
-  static __device__ __forceinline__ float ld_real(uint32_t a)
-  {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-    return v;
-  }
-  // read-only global load that stays where it is written (the compiler may not sink it)
-  static __device__ __forceinline__ float ldg_here(const float* ptr)
-  {
-    float v;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(ptr));
-    return v;
-  }
-  template <uint32_t OFF>
-  static __device__ __forceinline__ float ld_real_at(uint32_t a)  // [a + OFF], OFF an immediate
-  {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
-    return v;
-  }
-  // a += inc when t <= x (false for NaN), as one predicated add
-  static __device__ __forceinline__ void add_if_le(uint32_t& a, float t, float x, uint32_t inc)
-  {
-    asm("{\n.reg .pred p;\nsetp.le.f32 p, %1, %2;\n@p add.u32 %0, %0, %3;\n}"
-        : "+r"(a)
-        : "f"(t), "f"(x), "r"(inc));
-  }
-  static __device__ __forceinline__ void st_real(uint32_t a, float v)
-  {
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
-  }
-  static __device__ __forceinline__ Val ld_val(uint32_t a)
-  {
-    Val v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-  }
-  static __device__ __forceinline__ float as_real(Val v) { return __uint_as_float(v); }
-  static __device__ __forceinline__ uint32_t low32(Val v) { return v; }
-  static __device__ __forceinline__ float exp_(float x) { return expf(x); }
-  static __device__ __forceinline__ float exp2_(float x) { return exp2f(x); }
-  static __device__ __forceinline__ float log1p_(float x) { return log1pf(x); }
-};
-
-template <>
-struct Traits<double> {
-  using Val                    = uint64_t;
-  static constexpr uint32_t NB = 16;
-  static constexpr uint32_t ES = 8;
-  static __device__ __forceinline__ void ld_node(uint32_t a, Val& v, uint32_t& m)
-  {
-    uint64_t second;
-    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v), "=l"(second) : "r"(a));
-    m = static_cast<uint32_t>(second);
-  }
-  static __device__ __forceinline__ double ld_real(uint32_t a)
-  {
-    double v;
-    asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(a));
-    return v;
-  }
-  static __device__ __forceinline__ double ldg_here(const double* ptr)
-  {
-    double v;
-    asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(ptr));
-    return v;
-  }
-  template <uint32_t OFF>
-  static __device__ __forceinline__ double ld_real_at(uint32_t a)
-  {
-    double v;
-    asm volatile("ld.shared.f64 %0, [%1+%2];" : "=d"(v) : "r"(a), "n"(OFF));
-    return v;
-  }
-  static __device__ __forceinline__ void add_if_le(uint32_t& a, double t, double x, uint32_t inc)
-  {
-    asm("{\n.reg .pred p;\nsetp.le.f64 p, %1, %2;\n@p add.u32 %0, %0, %3;\n}"
-        : "+r"(a)
-        : "d"(t), "d"(x), "r"(inc));
-  }
-  static __device__ __forceinline__ void st_real(uint32_t a, double v)
-  {
-    asm volatile("st.shared.f64 [%0], %1;" ::"r"(a), "d"(v) : "memory");
-  }
-  static __device__ __forceinline__ Val ld_val(uint32_t a)
-  {
-    Val v;
-    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(a));
-    return v;
-  }
-  static __device__ __forceinline__ double as_real(Val v) { return __longlong_as_double(v); }
-  static __device__ __forceinline__ uint32_t low32(Val v) { return static_cast<uint32_t>(v); }
-  static __device__ __forceinline__ double exp_(double x) { return exp(x); }
-  static __device__ __forceinline__ double exp2_(double x) { return exp2(x); }
-  static __device__ __forceinline__ double log1p_(double x) { return log1p(x); }
-};
-
-// ---------------------------------------------------------------------------------------------
-// one test: does the row go to the right child?
-//   numerical: x < threshold goes left; categorical: a listed category goes right;
-//   a missing value (NaN) follows the node's default direction.
-// ---------------------------------------------------------------------------------------------
-template <typename T, bool CAT, bool NANS>
-__device__ __forceinline__ bool goes_right(typename Traits<T>::Val v, uint32_t meta, T x,
-                                           const ForestView& f)
-{
-  bool left = x < Traits<T>::as_real(v);
-  if (CAT) {
-    if (meta & META_CATEGORICAL) {
-      // category = truncated value; negative and huge values match nothing
-      const bool in_range = (x >= T(0)) && (x < T(16777216));
-      const uint32_t c    = in_range ? static_cast<uint32_t>(x) : 0u;
-      bool matched;
-      if (f.cat_inline) {
-        const uint32_t bits = Traits<T>::low32(v);
-        matched             = in_range && (c < 32u) && (((bits >> (c & 31u)) & 1u) != 0u);
-      } else {
-        const uint32_t off     = Traits<T>::low32(v);
-        const uint32_t n_words = __ldg(f.cat_pool + off);
-        const uint32_t w       = c >> 5;
-        matched                = false;
-        if (in_range && w < n_words) {
-          matched = ((__ldg(f.cat_pool + off + 1 + w) >> (c & 31u)) & 1u) != 0u;
-        }
-      }
-      left = !matched;
-    }
-  }
-  if (CAT || NANS) {
-    if (x != x) left = (meta & META_DEFAULT_LEFT) != 0u;
-  }
-  return !left;
-}
-
-// ---------------------------------------------------------------------------------------------
-// shared pieces of both kernels: row-tile staging, accumulation of a leaf, epilogue
-// ---------------------------------------------------------------------------------------------
-
-// Stage rows [row0, row0+R) feature-major.  A warp reads 32 consecutive features of one row
-// (one 128-byte line for fp32) and scatters them to 32 different banks.  Rows past the end of the
-// batch are filled with zeros.  Returns true when this thread saw a NaN.
-template <typename T>
-__device__ __forceinline__ bool stage_rows(const PredictParams& p, uint32_t tile, int R,
-                                           int64_t row0, int warp, int lane, int n_warps)
-{
-  const int F             = p.f.n_features;
-  const uint32_t stride_b = (R + 1) * Traits<T>::ES;
-  const T* X              = static_cast<const T*>(p.X);
-  bool saw_nan            = false;
-  for (int rr = warp; rr < R; rr += n_warps) {
-    const int64_t row = row0 + rr;
-    const bool live   = row < p.n_rows;
-    const T* src      = X + row * p.row_stride;
-    for (int c = lane; c < F; c += 32) {
-      const T v = live ? __ldg(src + c) : T(0);
-      saw_nan |= (v != v);
-      Traits<T>::st_real(tile + c * stride_b + rr * Traits<T>::ES, v);
-    }
-  }
-  return saw_nan;
-}
-
-template <typename T>
-__device__ __forceinline__ T postprocess_one(T s, int postproc, T alpha, T ratio_c)
-{
-  switch (postproc) {
-    case B2FIL_POST_SIGMOID:
-    case B2FIL_POST_MULTICLASS_OVA: return T(1) / (T(1) + Traits<T>::exp_(-alpha * s));
-    case B2FIL_POST_EXPONENTIAL: return Traits<T>::exp_(s);
-    case B2FIL_POST_LOG1PEXP: return Traits<T>::log1p_(Traits<T>::exp_(s));
-    case B2FIL_POST_SIGNED_SQUARE: return (s < T(0) ? T(-1) : T(1)) * s * s;
-    case B2FIL_POST_HINGE: return s > T(0) ? T(1) : T(0);
-    case B2FIL_POST_EXP_STD_RATIO: return Traits<T>::exp2_(-s / ratio_c);
-    default: return s;
-  }
-}
-
-// Epilogue of a row tile, one thread per row: fixed-order sum over the G tree groups, average and
-// base score, postprocessor, then the output the caller asked for.  `acc` is laid out
-// [group][output][row]; results overwrite group 0.
-template <typename T>
-__device__ __forceinline__ void finish_row(const PredictParams& p, T* acc, int R, int G, int j,
-                                           int64_t row)
-{
-  const ForestView& f = p.f;
-  const int NC        = f.n_outputs;
-  const T* scale      = static_cast<const T*>(f.out_scale);
-  const T* bias       = static_cast<const T*>(f.out_bias);
-  const T alpha       = static_cast<T>(f.sigmoid_alpha);
-  const T ratio_c     = static_cast<T>(f.ratio_c);
-  T mx                = T(0);
-  for (int c = 0; c < NC; ++c) {
-    T s = acc[c * R + j];
-    for (int g = 1; g < G; ++g) s += acc[(g * NC + c) * R + j];
-    s = s * __ldg(scale + c) + __ldg(bias + c);
-    if (f.postproc != B2FIL_POST_SOFTMAX) s = postprocess_one(s, f.postproc, alpha, ratio_c);
-    acc[c * R + j] = s;
-    mx             = (c == 0 || s > mx) ? s : mx;
-  }
-  if (f.postproc == B2FIL_POST_SOFTMAX) {
-    T z = T(0);
-    for (int c = 0; c < NC; ++c) {
-      const T e      = Traits<T>::exp_(acc[c * R + j] - mx);
-      acc[c * R + j] = e;
-      z += e;
-    }
-    for (int c = 0; c < NC; ++c) acc[c * R + j] = acc[c * R + j] / z;
-  }
-  if (row >= p.n_rows) return;
-  if (p.kind == B2FIL_INFER_DEFAULT) {
-    T* out = static_cast<T*>(p.out) + row * NC;
-    for (int c = 0; c < NC; ++c) out[c] = acc[c * R + j];
-  } else if (p.kind == B2FIL_INFER_PROBA2) {
-    T* out       = static_cast<T*>(p.out) + row * 2;
-    const T prob = acc[j];
-    out[0]       = T(1) - prob;
-    out[1]       = prob;
-  } else {  // B2FIL_INFER_CLASS
-    int best = 0;
-    if (NC == 1) {
-      best = acc[j] > static_cast<T>(p.threshold) ? 1 : 0;
-    } else {
-      T bv = acc[j];
-      for (int c = 1; c < NC; ++c) {
-        const T s = acc[c * R + j];
-        if (s > bv) {  // first maximum wins
-          bv   = s;
-          best = c;
-        }
-      }
-    }
-    static_cast<int32_t*>(p.out)[row] = best;
-  }
-}
-
-// Kernel modes.
-constexpr int MODE_SCALAR  = 0;  // scalar leaves, reduced outputs
-constexpr int MODE_VECTOR  = 1;  // vector leaves, reduced outputs
-constexpr int MODE_PERTREE = 2;  // raw per-tree outputs
-constexpr int MODE_LEAFID  = 3;  // id of the leaf reached
-
-// Per-thread running state of the reduced modes.
-template <typename T>
-struct Running {
-  T sum;
-  int cls;
-};
-
-// Consume one leaf.  `payload` is the leaf's scalar (as bits) or the index of its vector;
-// `leaf_id_index` is the index of the leaf in `leaf_ids`.
-template <typename T, int MODE>
-__device__ __forceinline__ void take_leaf(const PredictParams& p, int tree,
-                                          typename Traits<T>::Val payload, uint32_t leaf_id_index,
-                                          T* acc_group, int R, int r, int64_t row, Running<T>& run)
-{
-  const ForestView& f = p.f;
-  const int NC        = f.n_outputs;
-  if (MODE == MODE_SCALAR) {
-    if (NC > 1) {
-      const int cls = __ldg(f.tree_class + tree);  // same for the whole warp
-      if (cls != run.cls) {
-        acc_group[run.cls * R + r] += run.sum;
-        run.sum = T(0);
-        run.cls = cls;
-      }
-    }
-    run.sum += Traits<T>::as_real(payload);
-  } else if (MODE == MODE_VECTOR) {
-    const T* lv = static_cast<const T*>(f.leaf_vectors) +
-                  static_cast<size_t>(Traits<T>::low32(payload)) * NC;
-    for (int c = 0; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
-  } else if (MODE == MODE_PERTREE) {
-    if (row < p.n_rows) {
-      const int orig = __ldg(f.tree_orig + tree);
-      if (f.leaf_vector_len > 1) {
-        const T* lv = static_cast<const T*>(f.leaf_vectors) +
-                      static_cast<size_t>(Traits<T>::low32(payload)) * NC;
-        T* out = static_cast<T*>(p.out) + (row * f.n_trees + orig) * NC;
-        for (int c = 0; c < NC; ++c) out[c] = __ldg(lv + c);
-      } else {
-        static_cast<T*>(p.out)[row * f.n_trees + orig] = Traits<T>::as_real(payload);
-      }
-    }
-  } else {
-    if (row < p.n_rows) {
-      const int orig = __ldg(f.tree_orig + tree);
-      static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = __ldg(f.leaf_ids + leaf_id_index);
-    }
-  }
-}
-
-__host__ __device__ inline size_t align16(size_t x) { return (x + 15) / 16 * 16; }
-
 // ---------------------------------------------------------------------------------------------
 // DENSE kernel
 // ---------------------------------------------------------------------------------------------
@@ -664,18 +247,6 @@ __device__ __forceinline__ void for_each_constant(F&& f, std::integer_sequence<i
   (f(std::integral_constant<int, Ks>{}), ...);
 }
 
-__device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
-{
-  asm volatile(
-    "{\n"
-    ".reg .u16 h;\n"
-    "cvt.u16.u32 h, %1;\n"
-    "st.shared.u16 [%0], h;\n"
-    "}\n" ::"r"(a),
-    "r"(v)
-    : "memory");
-}
-
 // One CTA owns one feature group: the group's blob (feature records, bucket tables, sorted
 // thresholds, both tables interleaved across the group's features) arrives in shared memory with
 // one bulk copy, then the CTA loops over row tiles.  The group size GF is a power of two that
@@ -688,20 +259,6 @@ __device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v)
 // copy.  Nothing is exchanged between threads, so the tile loop has no barrier.  NaN becomes
 // Q_NAN_CODE and raises the tile's flag.
 // Shared memory: [mbarrier 16 B][blob].
-
-// Position of row r among the R uint16 entries of one feature in a rank tile.  Rows r and r + 32
-// share a 32-bit word, so the 32 consecutive rows of a warp sit in 32 different banks whatever
-// feature each lane reads (with the plain order two neighbouring rows share a bank and collide
-// as soon as they read different features).  Tiles of 32 rows keep the plain order.
-__device__ __forceinline__ uint32_t q_slot(uint32_t r, int R)
-{
-  return R >= 64 ? (((r & 31u) << 1) | ((r >> 5) & 1u) | ((r >> 6) << 6)) : r;
-}
-// The row that sits in slot s (inverse of q_slot).
-__device__ __forceinline__ uint32_t q_row_of_slot(uint32_t s, int R)
-{
-  return R >= 64 ? (((s >> 6) << 6) | ((s & 63u) >> 1) | ((s & 1u) << 5)) : s;
-}
 
 // NU = slots of a tile each thread owns (R * GF / threads, at least 1).  GFC > 0 fixes the group
 // size at compile time (table strides become immediates), GFC == 0 reads it from the group.
@@ -924,352 +481,6 @@ quantise_kernel(const PredictParams p, uint16_t* __restrict__ Q, int32_t* __rest
 }
 
 // ---------------------------------------------------------------------------------------------
-// DENSE kernel on rank-quantised rows
-// ---------------------------------------------------------------------------------------------
-// Shared memory: [mbarriers 128 B][row tile F x R uint16][accumulators][flags 16 B][S tree stages].
-// The row tile arrives with one bulk copy per tile (the pre-pass already stored it feature-major);
-// tree batches stream through the stage ring exactly as in dense_kernel.  A node is 4 bytes
-// (rank j << 17 | default-right << 16 | feature << 2 | categorical) and a test is one signed
-// subtraction.
-constexpr int kBarTileFull  = 2 * kMaxStages;      // mbarrier slots after the stage ring
-constexpr int kBarTileEmpty = 2 * kMaxStages + 1;
-
-// node - (q << 17) in one multiply-add: the sign of (j - rank) lands in bit 31.
-__device__ __forceinline__ uint32_t rank_diff(uint32_t node, uint32_t q)
-{
-  static_assert(Q_RANK_SHIFT == 17, "the multiplier below is -(1 << Q_RANK_SHIFT)");
-  uint32_t d;
-  asm("mad.lo.u32 %0, %1, 0xFFFE0000, %2;" : "=r"(d) : "r"(q), "r"(node));
-  return d;
-}
-
-// The three top nodes (heap words 1..3) of every tree, passed to the kernel by value: kernel
-// parameters live in the constant bank, so the first two levels of every walk read their nodes
-// through the constant cache and spend no shared-memory bandwidth, the resource that bounds the
-// traversal (a warp reads the same tree in all lanes, so each lookup is one constant access).
-struct QTop {
-  uint32_t w[3 * kQTopTrees];
-};
-
-// DEPTH > 0 fixes the tree depth at compile time (the level loop is fully unrolled); DEPTH == 0
-// reads it from the forest.  TOPC: the first two levels take their nodes from `top`.
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
-struct DenseQWalker {
-  using TR = Traits<T>;
-  // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
-  // trees; the warp waits once per stage and walks its NT trees of every sub-batch.
-  template <bool NANS>
-  static __device__ __forceinline__ bool walk(const PredictParams& p, int G, int S, int K, int g,
-                                              int r, int64_t row, int lane, uint32_t bars,
-                                              uint32_t stages, uint32_t stage_bytes,
-                                              uint32_t row_addr, uint32_t stride_b, T* acc_group,
-                                              int R, RingPos& pos, Running<T>& run,
-                                              const QTop* top)
-  {
-    static_assert(!TOPC || (DEPTH >= 2 && !CAT), "top nodes need two plain levels");
-    const ForestView& f    = p.f;
-    const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
-    const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
-    const uint32_t width_b = (1u << D) * 4u;
-    const uint32_t cat_off = (1u << D) * (4u + TR::ES);  // node address -> its category set
-    const uint32_t fstride = stride_b >> Q_FEATURE_SHIFT;  // R / 2 <= 128: fits a byte
-    const int per_sub      = G * NT;
-    const int per_batch    = per_sub * K;
-    const int n_batches    = (f.n_trees + per_batch - 1) / per_batch;
-    const uint32_t mine    = static_cast<uint32_t>(g * NT) * tstride;  // this warp's trees in a sub-batch
-    const uint32_t sub_b   = static_cast<uint32_t>(per_sub) * tstride;
-    bool ok                = true;
-
-    // One sub-batch: NT trees side by side.  FULL means all NT slots hold live trees, which lets
-    // the compiler drop every per-slot guard.
-    auto sub_batch = [&](auto full_tag, uint32_t base0, int first, int n_act) {
-      constexpr bool FULL = decltype(full_tag)::value;
-      uint32_t base[NT], idx[NT], a[NT];
-#pragma unroll
-      for (int k = 0; k < NT; ++k) {
-        // slots past the end of the forest repeat the last live tree; results are dropped
-        base[k] = base0 + static_cast<uint32_t>(FULL ? k : min(k, n_act - 1)) * tstride;
-        idx[k]  = 1u;  // heap index of the root
-        a[k]    = base[k] + 4u;
-      }
-      // the NT walks are independent: all node loads are issued first, then all rank loads,
-      // so that their shared-memory latencies overlap inside one warp.
-      // test(): the rows' ranks against NT nodes; the sign bit of d[k] is the step to the right.
-      auto test = [&](const uint32_t(&node)[NT], uint32_t(&d)[NT]) {
-        uint32_t q[NT];
-#pragma unroll
-        for (int k = 0; k < NT; ++k)
-          // the low half of a node is feature * 4 (plus the categorical flag): without
-          // categorical tests one dot-product instruction (low half x byte 0 of fstride, high
-          // half x byte 1 = 0) turns it into the address of the row's rank of that feature
-          q[k] = lds_u16(CAT ? (node[k] & Q_FEATURE_FIELD) * fstride + row_addr
-                             : __dp2a_lo(node[k], fstride, row_addr));
-        // forests with categorical tests: the 32-bit category set of every node, fetched for
-        // all nodes (numerical ones hold an empty set) to keep the walk free of branches
-        uint32_t bits[CAT ? NT : 1];
-        if (CAT) {
-#pragma unroll
-          for (int k = 0; k < NT; ++k) bits[k] = lds_u32(a[k] + cat_off);
-        }
-#pragma unroll
-        for (int k = 0; k < NT; ++k) {
-          // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
-          d[k] = rank_diff(node[k], q[k]);
-          if (CAT) {
-            // the code of a categorical value is its category and a set bit of the node's set
-            // sends it right: the clamped funnel shift moves bit q to the sign position and
-            // yields 0 for every code of 32 and above (no category, NaN)
-            const uint32_t dc = __funnelshift_lc(0u, bits[k], 31u - q[k]);
-            d[k]              = (node[k] & Q_CATEGORICAL) ? dc : d[k];
-          }
-          if (NANS) {
-            // the missing-goes-right flag sits 15 bits below the sign.  (Both forms compute the
-            // same; each kernel family keeps the one it was measured fastest with: the two walks
-            // of a kernel share its register allocation.)
-            if (CAT) {
-              if (q[k] == Q_NAN_CODE) d[k] = node[k] << 15;
-            } else {
-              if (q[k] == Q_NAN_CODE) d[k] = (node[k] & Q_DEFAULT_RIGHT) ? 0x80000000u : 0u;
-            }
-          }
-        }
-      };
-      auto level = [&]() {
-        uint32_t node[NT], d[NT];
-#pragma unroll
-        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
-        test(node, d);
-#pragma unroll
-        for (int k = 0; k < NT; ++k) {
-          // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
-          idx[k] = __funnelshift_l(d[k], idx[k], 1);
-          a[k]   = idx[k] * 4u + base[k];
-        }
-      };
-      if (TOPC) {
-        // root and children from the constant bank: the same words in every lane
-        uint32_t n1[NT], n2[NT], n3[NT], node[NT], d[NT];
-#pragma unroll
-        for (int k = 0; k < NT; ++k) {
-          const int t = 3 * (first + (FULL ? k : min(k, n_act - 1)));
-          n1[k]       = top->w[t];
-          n2[k]       = top->w[t + 1];
-          n3[k]       = top->w[t + 2];
-        }
-        test(n1, d);
-#pragma unroll
-        for (int k = 0; k < NT; ++k) {
-          node[k] = static_cast<int32_t>(d[k]) < 0 ? n3[k] : n2[k];
-          idx[k]  = __funnelshift_l(d[k], 1u, 1);
-        }
-        test(node, d);
-#pragma unroll
-        for (int k = 0; k < NT; ++k) {
-          idx[k] = __funnelshift_l(d[k], idx[k], 1);
-          a[k]   = idx[k] * 4u + base[k];
-        }
-      }
-      if (DEPTH > 0) {
-#pragma unroll
-        for (int lvl = TOPC ? 2 : 0; lvl < DEPTH; ++lvl) level();
-      } else {
-#pragma unroll 4
-        for (int lvl = 0; lvl < D; ++lvl) level();
-      }
-      // scalar leaves of a multi-class forest: trees are stored class by class, so when the
-      // first and the last tree of the sub-batch feed the class of the running sum, all do
-      bool same_class = false;
-      if (MODE == MODE_SCALAR && CAT) {
-        same_class = f.n_outputs == 1 ||
-                     (__ldg(f.tree_class + first) == run.cls &&
-                      __ldg(f.tree_class + first + n_act - 1) == run.cls);
-      }
-#pragma unroll
-      for (int k = 0; k < NT; ++k) {
-        if (FULL || k < n_act) {
-          // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
-          // address of leaf slot j is exactly the address the walk ended on
-          const uint32_t slot   = idx[k] - (1u << D);
-          const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
-          const typename TR::Val payload = TR::ld_val(leaf_a);
-          if (MODE == MODE_SCALAR && CAT && same_class) {
-            run.sum += TR::as_real(payload);
-          } else {
-            take_leaf<T, MODE>(p, first + k, payload,
-                               (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
-                               row, run);
-          }
-        }
-      }
-    };
-
-    for (int b = 0; b < n_batches; ++b) {
-      const uint32_t s = pos.stage;
-      if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
-      if (ok) {
-        uint32_t base0 = stages + s * stage_bytes + mine;
-        int first      = b * per_batch + g * NT;  // first tree of this warp inside the stage
-        for (int kk = 0; kk < K; ++kk, base0 += sub_b, first += per_sub) {
-          const int n_act = f.n_trees - first;
-          if (n_act >= NT) {
-            sub_batch(std::true_type{}, base0, first, NT);
-          } else if (n_act > 0) {
-            sub_batch(std::false_type{}, base0, first, n_act);
-          } else {
-            break;
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
-      pos.advance(S);
-    }
-    return ok;
-  }
-};
-
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
-__device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint16_t* __restrict__ Q,
-                                             const int32_t* __restrict__ tile_flags, const int R,
-                                             const int G, const int S, const int K,
-                                             const QTop* top)
-{
-  using TR = Traits<T>;
-  extern __shared__ __align__(128) unsigned char smem[];
-  const ForestView& f = p.f;
-  const int F         = f.n_features;
-  const int NC        = f.n_outputs;
-  const int rw        = R >> 5;
-  const int n_cw      = rw * G;
-  const int n_ct      = n_cw * 32;
-  const int warp      = threadIdx.x >> 5;
-  const int lane      = threadIdx.x & 31;
-
-  const uint32_t stride_b    = R * 2u;  // bytes between features in the tile
-  const uint32_t tile_bytes  = static_cast<uint32_t>(F) * stride_b;  // multiple of 64
-  const size_t acc_bytes     = (MODE <= MODE_VECTOR) ? align16(static_cast<size_t>(G) * NC * R * TR::ES) : 0;
-  unsigned char* tile_ptr    = smem + kBarBytes;
-  T* acc                     = reinterpret_cast<T*>(tile_ptr + tile_bytes);
-  unsigned char* stage_ptr   = tile_ptr + tile_bytes + acc_bytes + 16;
-  const uint32_t bars        = smem_addr(smem);
-  const uint32_t tile        = smem_addr(tile_ptr);
-  const uint32_t stages      = smem_addr(stage_ptr);
-  const uint32_t tstride     = static_cast<uint32_t>(f.q_tree_stride);
-  const int per_batch        = G * NT * K;
-  const uint32_t stage_bytes = per_batch * tstride;
-  const int n_batches        = (f.n_trees + per_batch - 1) / per_batch;
-  const int64_t n_tiles      = (p.n_rows + R - 1) / R;
-  const uint32_t bar_tfull   = bars + 8u * kBarTileFull;
-  const uint32_t bar_tempty  = bars + 8u * kBarTileEmpty;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(bars + 8u * s, 1);
-      mbar_init(bars + 8u * (kMaxStages + s), n_cw);
-    }
-    mbar_init(bar_tfull, 1);
-    mbar_init(bar_tempty, n_cw);
-    mbar_fence_init();
-  }
-  __syncthreads();
-
-  if (warp == n_cw) {
-    // ---- producer: row tile, then the tree batches of that tile ------------------------------
-    if (lane == 0) {
-      const unsigned char* src  = static_cast<const unsigned char*>(f.q_nodes);
-      const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(Q);
-      RingPos pos;
-      bool primed               = false;  // every stage has been filled once
-      uint32_t n_done           = 0;
-      for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
-        // the tile buffer is free once every consumer warp has left the previous tile's trees
-        if (n_done > 0 && !mbar_wait(bar_tempty, (n_done - 1) & 1u)) {
-          atomicExch(p.status, 3);
-          return;
-        }
-        mbar_expect_tx(bar_tfull, tile_bytes);
-        bulk_copy_g2s(tile, qsrc + static_cast<size_t>(t) * tile_bytes, tile_bytes, bar_tfull);
-        for (int b = 0; b < n_batches; ++b) {
-          const uint32_t s = pos.stage;
-          if (primed && !mbar_wait(bars + 8u * (kMaxStages + s), pos.phase ^ 1u)) {
-            atomicExch(p.status, 1);
-            return;
-          }
-          const int first      = b * per_batch;
-          const int count      = min(per_batch, f.n_trees - first);
-          const uint32_t bytes = count * tstride;
-          mbar_expect_tx(bars + 8u * s, bytes);
-          bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
-                        bytes, bars + 8u * s);
-          pos.advance(S);
-          if (pos.stage == 0) primed = true;
-        }
-      }
-    }
-    return;
-  }
-
-  // ---- consumers ------------------------------------------------------------------------------
-  const int g             = warp / rw;
-  const int r             = (warp % rw) * 32 + lane;
-  T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
-  const uint32_t row_addr = tile + q_slot(r, R) * 2u;
-  RingPos pos;
-  uint32_t n_done         = 0;
-  bool ok                 = true;
-  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++n_done) {
-    const int64_t row0 = t * R;
-    if (MODE <= MODE_VECTOR) {
-      for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
-    }
-    const bool nans = __ldg(tile_flags + t) != 0;
-    consumer_sync(n_ct);
-    if (ok) ok = mbar_wait(bar_tfull, n_done & 1u);
-    Running<T> run{T(0), 0};
-    if (ok) {
-      if (nans) {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<true>(
-          p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, pos, run, top);
-      } else {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<false>(
-          p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
-          acc_group, R, pos, run, top);
-      }
-      if (!ok) atomicExch(p.status, 2);
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_tempty);
-    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
-    consumer_sync(n_ct);
-    if (MODE <= MODE_VECTOR) {
-      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
-    }
-    consumer_sync(n_ct);
-  }
-}
-
-
-template <typename T, int MODE, int NT, int DEPTH, bool CAT>
-__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
-dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
-               const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
-               const int K)
-{
-  dense_q_body<T, MODE, NT, DEPTH, CAT, false>(p, Q, tile_flags, R, G, S, K, nullptr);
-}
-
-// Same kernel with the top nodes of every tree in the parameter block.
-template <typename T, int MODE, int NT, int DEPTH>
-__global__ void __launch_bounds__(NT > 4 ? 800 : 1024, 1)
-dense_q_top_kernel(const __grid_constant__ PredictParams p, const uint16_t* __restrict__ Q,
-                   const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
-                   const int K, const __grid_constant__ QTop top)
-{
-  dense_q_body<T, MODE, NT, DEPTH, false, true>(p, Q, tile_flags, R, G, S, K, &top);
-}
-
-// ---------------------------------------------------------------------------------------------
 // SPARSE kernel
 // ---------------------------------------------------------------------------------------------
 template <int FMT>
@@ -1445,30 +656,10 @@ size_t dense_smem(int depth, int precision, int F, int NC, bool reduce, int R, i
 // Raise a kernel's dynamic shared-memory limit to `bytes`.  The limit is a per-device attribute
 // of the kernel: it is set once per (device, kernel) and only raised afterwards, so the steady
 // state of a serving loop pays a table lookup instead of a driver call.
-std::mutex g_smem_mu;
-std::map<std::pair<int, const void*>, size_t> g_smem_set;
-
 template <typename K>
 int set_smem(K kernel, size_t bytes, std::string& err)
 {
-  int device = 0;
-  cudaGetDevice(&device);
-  const auto key = std::make_pair(device, reinterpret_cast<const void*>(kernel));
-  {
-    std::lock_guard<std::mutex> lock(g_smem_mu);
-    const auto it = g_smem_set.find(key);
-    if (it != g_smem_set.end() && it->second >= bytes) return B2FIL_OK;
-  }
-  const cudaError_t e = cudaFuncSetAttribute(
-    kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
-  if (e != cudaSuccess) {
-    err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
-    return B2FIL_ERR_CUDA;
-  }
-  std::lock_guard<std::mutex> lock(g_smem_mu);
-  size_t& have = g_smem_set[key];
-  have         = std::max(have, bytes);
-  return B2FIL_OK;
+  return set_smem_bytes(reinterpret_cast<const void*>(kernel), bytes, err);
 }
 
 template <typename T, bool CAT, int MODE>
@@ -1605,127 +796,21 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
   return false;
 }
 
-template <typename T>
-int launch_dense_q_t(const PredictParams& p, int mode, const DenseCfg& c, const uint16_t* Q,
-                     const int32_t* flags, int grid, cudaStream_t stream, std::string& err)
+// Pick the kernel family for a launch of the quantised traversal; the families are instantiated
+// in the kernels_q_*.cu translation units.
+int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err)
 {
-  int rc;
-#define B2FIL_Q_CASE(M, N, DD) B2FIL_Q_CASE_CAT(M, N, DD, false)
-#define B2FIL_Q_CASE_CAT(M, N, DD, CC)                                                      \
-  {                                                                                         \
-    auto k = dense_q_kernel<T, M, N, DD, CC>;                                               \
-    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                       \
-    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups, \
-                                                 c.stages, c.sub_batches);                  \
+  const ForestView& f = L.p.f;
+  if (f.q_has_cat) return launch_q_cat(L, mode, f64, err);
+  const bool specialised = !f64 && mode == MODE_SCALAR && f.dense_depth >= 4 && f.dense_depth <= 10;
+  if (specialised && L.c.trees_in_flight == 6) {
+    // the common boosted-tree shapes: depth-specialised bodies with six trees in flight
+    // (q_max_trees_in_flight offers six only for them)
+    if (L.p.q_top != nullptr && f.n_trees <= kQTopTrees) return launch_q_top6(L, err);
+    return launch_q_plain6(L, err);
   }
-  if (p.f.q_has_cat) {
-    // forests with categorical tests: four trees in flight at most (dense_q_config honours it)
-#define B2FIL_Q_CAT_MODES(N)                                            \
-  switch (mode) {                                                       \
-    case MODE_SCALAR: B2FIL_Q_CASE_CAT(MODE_SCALAR, N, 0, true) break;  \
-    case MODE_VECTOR: B2FIL_Q_CASE_CAT(MODE_VECTOR, N, 0, true) break;  \
-    case MODE_PERTREE: B2FIL_Q_CASE_CAT(MODE_PERTREE, N, 0, true) break; \
-    default: B2FIL_Q_CASE_CAT(MODE_LEAFID, N, 0, true) break;           \
-  }
-    if (c.trees_in_flight == 4) {
-      if constexpr (std::is_same<T, float>::value) {
-        if (mode == MODE_SCALAR) {  // fp32 scalar leaves: depth-specialised bodies
-          switch (p.f.dense_depth) {
-            case 4: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 4, true) return B2FIL_OK;
-            case 5: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 5, true) return B2FIL_OK;
-            case 6: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 6, true) return B2FIL_OK;
-            case 7: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 7, true) return B2FIL_OK;
-            case 8: B2FIL_Q_CASE_CAT(MODE_SCALAR, 4, 8, true) return B2FIL_OK;
-            default: break;
-          }
-        }
-      }
-      B2FIL_Q_CAT_MODES(4)
-    } else if (c.trees_in_flight == 2) {
-      B2FIL_Q_CAT_MODES(2)
-    } else {
-      B2FIL_Q_CAT_MODES(1)
-    }
-#undef B2FIL_Q_CAT_MODES
-    return B2FIL_OK;
-  }
-  if constexpr (std::is_same<T, float>::value) {
-    // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies with six
-    // trees in flight (q_max_trees_in_flight offers six only for them)
-    if (c.trees_in_flight == 6 && p.q_top != nullptr && p.f.n_trees <= kQTopTrees) {
-      // the three top nodes of every tree travel in the parameter block
-      static thread_local QTop top;
-      std::memcpy(top.w, p.q_top, static_cast<size_t>(p.f.n_trees) * 3 * sizeof(uint32_t));
-#define B2FIL_Q_TOP_CASE(DD)                                                                   \
-  {                                                                                            \
-    auto k = dense_q_top_kernel<T, MODE_SCALAR, 6, DD>;                                        \
-    if ((rc = set_smem(k, c.smem_bytes, err)) != B2FIL_OK) return rc;                          \
-    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, Q, flags, c.rows_per_tile, c.tree_groups,  \
-                                                 c.stages, c.sub_batches, top);                \
-  }
-      switch (p.f.dense_depth) {
-        case 4: B2FIL_Q_TOP_CASE(4) return B2FIL_OK;
-        case 5: B2FIL_Q_TOP_CASE(5) return B2FIL_OK;
-        case 6: B2FIL_Q_TOP_CASE(6) return B2FIL_OK;
-        case 7: B2FIL_Q_TOP_CASE(7) return B2FIL_OK;
-        case 8: B2FIL_Q_TOP_CASE(8) return B2FIL_OK;
-        case 9: B2FIL_Q_TOP_CASE(9) return B2FIL_OK;
-        default: B2FIL_Q_TOP_CASE(10) return B2FIL_OK;
-      }
-#undef B2FIL_Q_TOP_CASE
-    }
-    if (c.trees_in_flight == 6) {
-      switch (p.f.dense_depth) {
-        case 4: B2FIL_Q_CASE(MODE_SCALAR, 6, 4) return B2FIL_OK;
-        case 5: B2FIL_Q_CASE(MODE_SCALAR, 6, 5) return B2FIL_OK;
-        case 6: B2FIL_Q_CASE(MODE_SCALAR, 6, 6) return B2FIL_OK;
-        case 7: B2FIL_Q_CASE(MODE_SCALAR, 6, 7) return B2FIL_OK;
-        case 8: B2FIL_Q_CASE(MODE_SCALAR, 6, 8) return B2FIL_OK;
-        case 9: B2FIL_Q_CASE(MODE_SCALAR, 6, 9) return B2FIL_OK;
-        default: B2FIL_Q_CASE(MODE_SCALAR, 6, 10) return B2FIL_OK;
-      }
-    }
-  }
-  if (c.trees_in_flight == 4) {
-    // the common boosted-tree shapes (fp32, scalar leaves) get depth-specialised bodies
-    if constexpr (std::is_same<T, float>::value) {
-      if (mode == MODE_SCALAR) {
-        switch (p.f.dense_depth) {
-          case 4: B2FIL_Q_CASE(MODE_SCALAR, 4, 4) return B2FIL_OK;
-          case 5: B2FIL_Q_CASE(MODE_SCALAR, 4, 5) return B2FIL_OK;
-          case 6: B2FIL_Q_CASE(MODE_SCALAR, 4, 6) return B2FIL_OK;
-          case 7: B2FIL_Q_CASE(MODE_SCALAR, 4, 7) return B2FIL_OK;
-          case 8: B2FIL_Q_CASE(MODE_SCALAR, 4, 8) return B2FIL_OK;
-          case 9: B2FIL_Q_CASE(MODE_SCALAR, 4, 9) return B2FIL_OK;
-          case 10: B2FIL_Q_CASE(MODE_SCALAR, 4, 10) return B2FIL_OK;
-          default: break;
-        }
-      }
-    }
-    switch (mode) {
-      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 4, 0) break;
-      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 4, 0) break;
-      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 4, 0) break;
-      default: B2FIL_Q_CASE(MODE_LEAFID, 4, 0) break;
-    }
-  } else if (c.trees_in_flight == 2) {
-    switch (mode) {
-      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 2, 0) break;
-      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 2, 0) break;
-      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 2, 0) break;
-      default: B2FIL_Q_CASE(MODE_LEAFID, 2, 0) break;
-    }
-  } else {
-    switch (mode) {
-      case MODE_SCALAR: B2FIL_Q_CASE(MODE_SCALAR, 1, 0) break;
-      case MODE_VECTOR: B2FIL_Q_CASE(MODE_VECTOR, 1, 0) break;
-      case MODE_PERTREE: B2FIL_Q_CASE(MODE_PERTREE, 1, 0) break;
-      default: B2FIL_Q_CASE(MODE_LEAFID, 1, 0) break;
-    }
-  }
-#undef B2FIL_Q_CASE
-#undef B2FIL_Q_CASE_CAT
-  return B2FIL_OK;
+  if (specialised && L.c.trees_in_flight == 4) return launch_q_plain4(L, err);
+  return launch_q_generic(L, mode, f64, err);
 }
 
 // Rank-quantised prediction: rows are processed in chunks of whole waves of tiles; for each
@@ -1807,8 +892,8 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
       k<<<qgrid, qblock, q_smem, stream>>>(pc, Q, flags, R);
     }
     const int grid = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
-    rc = precision == B2FIL_F32 ? launch_dense_q_t<float>(pc, mode, c, Q, flags, grid, stream, err)
-                                : launch_dense_q_t<double>(pc, mode, c, Q, flags, grid, stream, err);
+    rc = launch_dense_q_kernel(QLaunch{pc, Q, flags, c, grid, stream}, mode,
+                               precision != B2FIL_F32, err);
     if (launches) *launches += 2;
   }
   cudaFreeAsync(scratch, stream);
@@ -1860,7 +945,31 @@ int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
   return 32;
 }
 
+std::mutex g_smem_mu;
+std::map<std::pair<int, const void*>, size_t> g_smem_set;
 }  // namespace
+
+int set_smem_bytes(const void* kernel, size_t bytes, std::string& err)
+{
+  int device = 0;
+  cudaGetDevice(&device);
+  const auto key = std::make_pair(device, kernel);
+  {
+    std::lock_guard<std::mutex> lock(g_smem_mu);
+    const auto it = g_smem_set.find(key);
+    if (it != g_smem_set.end() && it->second >= bytes) return B2FIL_OK;
+  }
+  const cudaError_t e = cudaFuncSetAttribute(
+    kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) {
+    err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_smem_mu);
+  size_t& have = g_smem_set[key];
+  have         = std::max(have, bytes);
+  return B2FIL_OK;
+}
 
 bool dense_config(int depth, int precision, int n_features, int n_outputs, bool reduce_kind,
                   int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
@@ -2102,8 +1211,8 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
     k<<<qgrid, qblock, q_smem, stream>>>(p, Q, flags, R);
   }
   const int grid = static_cast<int>(std::min<int64_t>(n_tiles, sm_count));
-  rc = precision == B2FIL_F32 ? launch_dense_q_t<float>(p, mode, c, Q, flags, grid, stream, err)
-                              : launch_dense_q_t<double>(p, mode, c, Q, flags, grid, stream, err);
+  rc = launch_dense_q_kernel(QLaunch{p, Q, flags, c, grid, stream}, mode, precision != B2FIL_F32,
+                             err);
   if (rc != B2FIL_OK) return rc;
   e = cudaGetLastError();
   if (e != cudaSuccess) {
