@@ -102,11 +102,12 @@ struct DenseQWalker {
           // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
           d[k] = rank_diff(node[k], q[k]);
           if (CAT) {
-            // the code of a categorical value is its category and a set bit of the node's set
-            // sends it right: the clamped funnel shift moves bit q to the sign position and
-            // yields 0 for every code of 32 and above (no category, NaN)
-            const uint32_t dc = __funnelshift_lc(0u, bits[k], 31u - q[k]);
-            d[k]              = (node[k] & Q_CATEGORICAL) ? dc : d[k];
+            // the code of a categorical value is its category and the node's set is stored
+            // bit-reversed: the clamped funnel shift by the code moves the category's bit to the
+            // sign position and yields 0 for every code of 32 and above (no category, NaN).  A
+            // categorical node carries the largest rank (its comparison never says "right") and
+            // a numerical node an empty set, so the two answers are simply ORed.
+            d[k] |= __funnelshift_lc(0u, bits[k], q[k]);
           }
           if (NANS) {
             // the missing-goes-right flag sits 15 bits below the sign.  (Both forms compute the

@@ -79,7 +79,9 @@ struct SparseNode16D {  // fp64
 // their place in the same scheme: the "rank" of a value is its category (Q_NO_CATEGORY when it is
 // negative, fractional-truncated out of range or too large), and a categorical node looks its
 // 32-bit category set up in a third per-tree array indexed like the nodes; a set bit sends the
-// row right.
+// row right.  The sets are stored bit-reversed (category c in bit 31 - c) and a categorical node
+// carries the largest rank, so its rank comparison always says "left" and the walk can simply OR
+// the two answers: sign(node - (code << 17)) | sign(set << code).
 // The rank is found through a per-feature bucket table: bucket(x) = clamp(int(fma(x, scale,
 // offset)), 0, n_buckets-1) is monotone in x, lut[b] is the number of thresholds in buckets below
 // b (all of them are <= x), thresholds of higher buckets are all > x, so the rank is lut[b] plus
@@ -128,6 +130,7 @@ constexpr uint32_t Q_CATEGORICAL   = 0x1u;
 constexpr uint32_t Q_DEFAULT_RIGHT = 0x10000u;  // missing values go right (stored in this sense: << 15 makes it the sign)
 constexpr uint32_t Q_RANK_SHIFT    = 17;
 constexpr uint32_t Q_NEVER_LEFT    = 0x7FFFu;  // j of a test that no value passes
+constexpr uint32_t Q_MAX_RANK_FIELD = 0x3FFFu;  // j of a test that every code passes (categorical nodes)
 // Forests of at most this many trees, at least two levels deep and without categorical tests also
 // keep the three top nodes of every tree on the host: the traversal kernel takes them as a launch
 // parameter and reads them through the constant cache instead of shared memory.

@@ -584,8 +584,13 @@ struct Packer {
         if (meta & META_CATEGORICAL) {
           uint32_t bits;  // the inline category set sits in the low word of the value slot
           std::memcpy(&bits, src + i * nb, 4);
-          std::memcpy(sets + i * 4, &bits, 4);
-          node |= Q_CATEGORICAL;
+          // stored bit-reversed (category c in bit 31 - c): shifting the word left by the
+          // category then puts the answer in the sign bit
+          uint32_t rev = 0;
+          for (int c = 0; c < 32; ++c) rev |= ((bits >> c) & 1u) << (31 - c);
+          std::memcpy(sets + i * 4, &rev, 4);
+          // the rank comparison of such a node must never say "right": the largest rank field
+          node |= Q_CATEGORICAL | (Q_MAX_RANK_FIELD << Q_RANK_SHIFT);
         } else {
           uint32_t j;
           if (std::isnan(thr)) {

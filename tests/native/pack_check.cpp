@@ -169,11 +169,15 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
         std::memcpy(&node, t + i * 4, 4);
         const uint32_t qq = q[(node & Q_FEATURE_FIELD) >> Q_FEATURE_SHIFT];
         bool right = static_cast<int32_t>(node - (qq << Q_RANK_SHIFT)) < 0;
-        if (node & Q_CATEGORICAL) {
+        if (pf.view.q_has_cat) {
+          // the kernel's arithmetic: OR of the rank comparison (never "right" on a categorical
+          // node) and the bit-reversed category set shifted left by the code (0 from 32 up)
           const size_t es = sizeof(T);
           uint32_t bits;
           std::memcpy(&bits, t + (size_t(1) << D) * (4 + es) + i * 4, 4);
-          right = qq < 32u && ((bits >> qq) & 1u);
+          const uint32_t shifted = qq < 32u ? bits << qq : 0u;
+          right = right || (shifted >> 31) != 0u;
+          if (!(node & Q_CATEGORICAL) && bits != 0u) ++bad;  // numerical nodes hold empty sets
         }
         if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_RIGHT) != 0u;
         i = 2 * i + (right ? 1 : 0);
