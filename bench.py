@@ -220,6 +220,10 @@ def measure_e2e(fi, X, out, n, world, dev, barrier, args):
     while need * 4 > avail and e2e_rows > 100_000:
         e2e_rows //= 2
         need = e2e_rows * N_FEATURES * 4
+    if world > 1:  # every rank times the same number of rows
+        agreed = torch.tensor([e2e_rows], device=dev, dtype=torch.int64)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        e2e_rows = int(agreed.item())
     Xh = torch.empty((e2e_rows, N_FEATURES), dtype=torch.float32, pin_memory=True)
     Xh.copy_(X[:e2e_rows])
     oh = torch.empty((e2e_rows, 2), dtype=torch.float32, pin_memory=True)
