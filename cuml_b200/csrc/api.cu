@@ -275,6 +275,8 @@ int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* 
     if ((rc = upload(f.get(), pf.out_bias, offsetof(ForestView, out_bias))) != B2FIL_OK) return rc;
     if (pf.view.q_enabled) {
       if ((rc = upload(f.get(), pf.q_nodes, offsetof(ForestView, q_nodes))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.q_nodes_ids, offsetof(ForestView, q_nodes_ids))) != B2FIL_OK)
+        return rc;
       if ((rc = upload(f.get(), pf.q_blob, offsetof(ForestView, q_blob))) != B2FIL_OK) return rc;
       if ((rc = upload(f.get(), pf.q_groups, offsetof(ForestView, q_groups))) != B2FIL_OK)
         return rc;

@@ -171,20 +171,67 @@ struct DenseQWalker {
                      (__ldg(f.tree_class + first) == run.cls &&
                       __ldg(f.tree_class + first + n_act - 1) == run.cls);
       }
+      if (MODE >= MODE_PERTREE) {
+        // One output per (row, tree).  The payload slot holds what is reported: the leaf value,
+        // or the leaf id when the CTA streams the image made for that (MODE_LEAFID).  With four
+        // live trees that are also the caller's trees first..first+3, a row's four outputs are
+        // contiguous and leave as 16-byte stores: scalar 4-byte stores at a stride of a whole
+        // output row cost one sector request each and bound these predictions otherwise.
+        typename TR::Val val[NT];
 #pragma unroll
-      for (int k = 0; k < NT; ++k) {
-        if (FULL || k < n_act) {
-          // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
-          // address of leaf slot j is exactly the address the walk ended on
+        for (int k = 0; k < NT; ++k) {
           const uint32_t slot   = idx[k] - (1u << D);
           const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
-          const typename TR::Val payload = TR::ld_val(leaf_a);
-          if (MODE == MODE_SCALAR && CAT && same_class) {
-            run.sum += TR::as_real(payload);
-          } else {
-            take_leaf<T, MODE>(p, first + k, payload,
-                               (static_cast<uint32_t>(first + k) << D) + slot, acc_group, R, r,
-                               row, run);
+          val[k]                = TR::ld_val(leaf_a);
+        }
+        const bool scalar_out = MODE == MODE_LEAFID || f.leaf_vector_len <= 1;
+        const bool wide = FULL && NT == 4 && scalar_out && f.q_trees_in_order != 0 &&
+                          (f.n_trees & 3) == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+        if (wide) {
+          if (row < p.n_rows) {
+            if (MODE == MODE_LEAFID || TR::ES == 4) {
+              uint32_t* dst = static_cast<uint32_t*>(p.out) + row * f.n_trees + first;
+              *reinterpret_cast<uint4*>(dst) =
+                make_uint4(TR::low32(val[0]), TR::low32(val[NT > 1 ? 1 : 0]),
+                           TR::low32(val[NT > 2 ? 2 : 0]), TR::low32(val[NT > 3 ? 3 : 0]));
+            } else {
+              uint64_t* dst = static_cast<uint64_t*>(p.out) + row * f.n_trees + first;
+              *reinterpret_cast<ulonglong2*>(dst) =
+                make_ulonglong2(val[0], val[NT > 1 ? 1 : 0]);
+              *reinterpret_cast<ulonglong2*>(dst + 2) =
+                make_ulonglong2(val[NT > 2 ? 2 : 0], val[NT > 3 ? 3 : 0]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            if (FULL || k < n_act) {
+              if (MODE == MODE_LEAFID) {
+                if (row < p.n_rows) {
+                  const int orig = __ldg(f.tree_orig + first + k);
+                  static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = TR::low32(val[k]);
+                }
+              } else {
+                take_leaf<T, MODE>(p, first + k, val[k], 0u, acc_group, R, r, row, run);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          if (FULL || k < n_act) {
+            // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
+            // address of leaf slot j is exactly the address the walk ended on
+            const uint32_t slot   = idx[k] - (1u << D);
+            const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
+            const typename TR::Val payload = TR::ld_val(leaf_a);
+            if (MODE == MODE_SCALAR && CAT && same_class) {
+              run.sum += TR::as_real(payload);
+            } else {
+              take_leaf<T, MODE>(p, first + k, payload, 0u, acc_group, R, r, row, run);
+            }
           }
         }
       }
@@ -263,7 +310,9 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
   if (warp == n_cw) {
     // ---- producer: row tile, then the tree batches of that tile ------------------------------
     if (lane == 0) {
-      const unsigned char* src  = static_cast<const unsigned char*>(f.q_nodes);
+      // predictions that report leaves stream the image whose payload slots hold the leaf ids
+      const unsigned char* src  = static_cast<const unsigned char*>(
+        MODE == MODE_LEAFID ? f.q_nodes_ids : f.q_nodes);
       const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(Q);
       RingPos pos;
       bool primed               = false;  // every stage has been filled once

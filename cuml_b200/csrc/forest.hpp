@@ -174,10 +174,12 @@ struct ForestView {
   int32_t q_enabled;
   int32_t q_n_groups;
   int32_t q_has_cat;            // 1: tree blocks carry a third array of 32-bit category sets
-  int32_t q_pad;
+  int32_t q_trees_in_order;     // 1: packed tree t is the caller's tree t (tree_orig is the identity)
   int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size [+ 4]), 16-byte multiple
   const void* q_nodes;          // [n_trees] blocks of [2^D nodes uint32][2^D leaf payloads]
                                 //           [2^D category sets uint32, when q_has_cat]
+  const void* q_nodes_ids;      // same blocks with the leaf id (uint32) in every leaf payload slot:
+                                // what the traversal streams when it reports leaf ids
   int64_t q_max_blob_bytes;     // largest group blob
   const unsigned char* q_blob;  // group blobs
   const QGroup* q_groups;       // [q_n_groups]
@@ -202,6 +204,7 @@ struct PackedForest {
   std::vector<uint8_t> out_scale;
   std::vector<uint8_t> out_bias;
   std::vector<uint8_t> q_nodes;
+  std::vector<uint8_t> q_nodes_ids;  // q_nodes with leaf ids in the payload slots
   std::vector<uint32_t> q_top;  // root and its two children of every tree (3 words per tree), or empty
   std::vector<uint8_t> q_thresholds;
   std::vector<uint16_t> q_lut;

@@ -607,6 +607,19 @@ struct Packer {
       }
       std::memcpy(dst + width * 4, src + width * nb, static_cast<size_t>(width) * es);
     }
+    // the same image with the leaf id in every payload slot, for predictions that report leaves
+    out.q_nodes_ids = out.q_nodes;
+    for (int p = 0; p < nt; ++p) {
+      uint8_t* leaves = out.q_nodes_ids.data() + static_cast<size_t>(qstride) * p + width * 4;
+      std::memset(leaves, 0, static_cast<size_t>(width) * es);
+      for (int64_t s = 0; s < width; ++s) {
+        const uint32_t id = out.leaf_ids[static_cast<size_t>(width) * p + s];
+        std::memcpy(leaves + s * es, &id, 4);
+      }
+    }
+    bool in_order = true;
+    for (int p = 0; p < nt; ++p) in_order = in_order && out.tree_orig[p] == p;
+    out.view.q_trees_in_order = in_order ? 1 : 0;
     out.q_top.clear();
     if (!has_cat && D >= 2 && nt <= kQTopTrees) {
       out.q_top.resize(static_cast<size_t>(nt) * 3);
@@ -844,6 +857,7 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
       out.q_nodes.clear();
       out.q_thresholds.clear();
       out.q_top.clear();
+      out.q_nodes_ids.clear();
       out.q_lut.clear();
       out.q_feats.clear();
       out.q_groups.clear();

@@ -605,3 +605,33 @@ def test_quantised_traversal_kernel_variants(n_trees, depth, n_classes):
         ids = fi.apply(Xd, chunk_size=chunk_size).cpu().numpy()
         assert np.array_equal(ids.astype(np.uint32),
                               oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+
+
+@pytest.mark.parametrize("precision", ["single", "double"])
+def test_per_tree_outputs_wide_and_narrow_stores(precision):
+    """Leaf ids and per-tree values leave the quantised traversal as 16-byte stores when a row's
+    four outputs are contiguous and aligned, and as scalar stores otherwise: a tree count that is
+    a multiple of four (wide), one that is not, an output buffer that starts 4 bytes off a
+    16-byte boundary, and a multi-class forest whose trees are stored class by class."""
+    torch = _torch()
+    rng = np.random.default_rng(50)
+    n = 5000
+    X = rng.standard_normal((n, 16)).astype(np.float32)
+    X[rng.random((n, 16)) < 0.02] = np.nan
+    for n_trees, n_classes in ((24, 1), (23, 1), (24, 3)):
+        kw = dict(n_classes=n_classes) if n_classes > 1 else {}
+        desc = synthetic_complete_forest(n_trees, 5, 16, seed=51 + n_trees, **kw)
+        fi = ForestInference.load_from_treelite_model(desc, precision=precision)
+        Xd = _dev(X, precision)
+        want_ids = oracle.predict(desc, X, INFER_LEAF_ID, precision)
+        want_pt = oracle.predict(desc, X, INFER_PER_TREE, precision)
+        ids = fi.apply(Xd, chunk_size=8).cpu().numpy()
+        assert np.array_equal(ids.astype(np.uint32), want_ids)
+        pt = fi.predict_per_tree(Xd, chunk_size=8).cpu().numpy()
+        assert np.array_equal(pt, want_pt)
+        # output buffer one element past an aligned address
+        buf = torch.zeros(n * n_trees + 1, device="cuda:0", dtype=torch.int32)
+        view = buf[1:].view(n, n_trees)
+        fi.apply(Xd, preds=view, chunk_size=8)
+        assert np.array_equal(view.cpu().numpy().astype(np.uint32), want_ids)
+        assert int(buf[0]) == 0
