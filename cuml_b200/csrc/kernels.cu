@@ -585,40 +585,37 @@ sparse_kernel(const PredictParams p, const int R, const int G, const int rows_in
       const int n_act = min(NT, f.n_trees - first);
       uint32_t idx[NT];
       typename SF::Node node[NT];
-      bool done[NT];
 #pragma unroll
-      for (int k = 0; k < NT; ++k) {
-        idx[k]  = __ldg(f.roots + first + min(k, n_act - 1));
-        done[k] = false;
-      }
-      // max_depth + 1 nodes lie on the longest path: the loop cannot run away on a bad forest
+      for (int k = 0; k < NT; ++k) idx[k] = __ldg(f.roots + first + min(k, n_act - 1));
+      // max_depth + 1 nodes lie on the longest path: the loop cannot run away on a bad forest.
+      // Every step first issues the node fetches of all NT walks (a walk that has reached its
+      // leaf fetches the leaf again, a cache hit), then advances them without branches, so a
+      // thread really has NT independent fetches in flight; the warp leaves the loop together.
       for (int step = 0; step <= f.max_depth; ++step) {
-        bool all_done = true;
+#pragma unroll
+        for (int k = 0; k < NT; ++k) node[k] = SF::load(f.nodes, idx[k], fb);
+        bool walking = false;
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
-          if (!done[k]) {
-            node[k] = SF::load(f.nodes, idx[k], fb);
-            if (node[k].meta & META_LEAF) {
-              done[k] = true;
-            } else {
-              const uint32_t feat = SF::feature(node[k], fb);
-              const T x = rows_in_smem ? TR::ld_real(feat * stride_b + row_addr) : __ldg(xrow + feat);
-              typename TR::Val v  = node[k].value;
-              const bool right    = f.has_categorical
-                                      ? goes_right<T, true, true>(v, node[k].meta, x, f)
-                                      : goes_right<T, false, true>(v, node[k].meta, x, f);
-              // depth-first: left child follows its parent, `offset` reaches the right child;
-              // otherwise the children are adjacent and `offset` reaches the left one
-              idx[k] += dfs ? (right ? node[k].offset : 1u) : (node[k].offset + (right ? 1u : 0u));
-              all_done = false;
-            }
-          }
+          const bool leaf     = (node[k].meta & META_LEAF) != 0;
+          const uint32_t feat = leaf ? 0u : SF::feature(node[k], fb);
+          const T x = rows_in_smem ? TR::ld_real(feat * stride_b + row_addr) : __ldg(xrow + feat);
+          typename TR::Val v  = node[k].value;
+          const bool right    = f.has_categorical
+                                  ? goes_right<T, true, true>(v, node[k].meta, x, f)
+                                  : goes_right<T, false, true>(v, node[k].meta, x, f);
+          // depth-first: left child follows its parent, `offset` reaches the right child;
+          // otherwise the children are adjacent and `offset` reaches the left one
+          const uint32_t hop =
+            dfs ? (right ? node[k].offset : 1u) : (node[k].offset + (right ? 1u : 0u));
+          idx[k] += leaf ? 0u : hop;
+          walking |= !leaf;
         }
-        if (all_done) break;
+        if (!__any_sync(0xffffffffu, walking)) break;
       }
 #pragma unroll
       for (int k = 0; k < NT; ++k) {
-        if (k < n_act && done[k]) {
+        if (k < n_act && (node[k].meta & META_LEAF) != 0) {
           take_leaf<T, MODE>(p, first + k, node[k].value, idx[k], acc_group, R, r, row, run);
         }
       }
