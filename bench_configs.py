@@ -1,12 +1,17 @@
-"""Throughput of the five benchmark configurations on one GPU.
+"""Throughput of the five benchmark configurations on one GPU, each checked against the CPU
+oracle in the run that times it.
 
-    python -m cuml_b200.bench_configs [--config c1 c2 c3 c4 c5] [--steps K] [--rows-scale S]
+    python bench_configs.py [--config c1 c2 c3 c4 c5 sweep] [--steps K] [--rows-scale S] [--no-cpu]
 
-Prints one JSON line per configuration: rows/s with device-resident rows (CUDA events on the
-launching stream), the algorithmic bytes per row (features read once + outputs written once) and
-the fraction of the measured HBM copy bandwidth that the row stream reaches.  `bench.py` at the
-repository root measures the headline configuration (c2) under the full reporting contract; this
-module is the quick way to see the other shapes.
+Prints one JSON line per configuration and call: rows/s with device-resident rows (CUDA events on
+the launching stream), the algorithmic bytes per row (features read once + outputs written once),
+the fraction of the measured HBM copy bandwidth that the row stream reaches, the kernels that ran
+(as the library reports them), and a `cpu` record: the CPU oracle (all host threads) timed on a
+bounded row sample of the same workload, whose outputs are also what the GPU results of that
+sample are compared with (`parity`: scores within rtol 1e-5 / atol 1e-6 in fp32, rtol 1e-12 in
+fp64; leaf ids bit-exact), plus scikit-learn with `n_jobs=-1` where scikit-learn trained the model.
+`bench.py` measures the headline configuration (c2) under the full reporting contract and embeds
+the other lines; this file is the quick way to run one shape (e.g. under a profiler).
 
   c1  scikit-learn RandomForestClassifier, 100 trees, depth <= 8, 32 fp32 features, 2 classes,
       predict_proba on 1 M rows
@@ -24,18 +29,21 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 import time
 
 import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 HBM_GBS_FALLBACK = 6650.0
 
 
 def _peak():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-                        "MEASURED_PEAKS.json")
     try:
-        with open(path) as fh:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
             return float(json.load(fh)["hbm_gbs"]), "measured"
     except Exception:
         return HBM_GBS_FALLBACK, "fallback"
@@ -53,6 +61,9 @@ def _time(fn, steps):
         fn()
     b.record()
     torch.cuda.synchronize()
+    from cuml_b200.fil import _lib
+
+    _time.variant = _lib.last_variant()  # the kernels of the call that was just timed
     return a.elapsed_time(b) / steps
 
 
@@ -68,26 +79,76 @@ def _randn_rows(n, f, dtype, seed, chunk=2_000_000):
     return X
 
 
-def run(config: str, steps: int, scale: float):
+def _cpu_and_parity(desc, Xd, gpu_out, kind, precision, sample_rows, seconds=4.0, ids_out=None):
+    """CPU baseline leg: run the oracle with all host threads on a bounded sample of the timed
+    rows (sized for about `seconds` of CPU work, at most `sample_rows`), report its rows/s, and
+    compare the GPU results of the same rows with it."""
+    from cuml_b200.fil._desc import INFER_LEAF_ID
+    from oracle import oracle
+
+    cores = os.cpu_count() or 1
+    n = int(Xd.shape[0])
+    probe = Xd[:min(n, 2048)].cpu().numpy()
+    oracle.predict(desc, probe[:64], kind, precision, n_threads=cores)
+    t0 = time.perf_counter()
+    oracle.predict(desc, probe, kind, precision, n_threads=cores)
+    rate = probe.shape[0] / max(1e-9, time.perf_counter() - t0)
+    m = int(max(256, min(n, sample_rows, rate * seconds)))
+    # evenly spread rows, first and last included
+    idx = np.unique(np.linspace(0, n - 1, m).astype(np.int64))
     import torch
 
-    from .fil import ForestInference, synthetic_complete_forest
+    sel = torch.as_tensor(idx, device=Xd.device)
+    Xs = Xd[sel].cpu().numpy()
+    t0 = time.perf_counter()
+    want = oracle.predict(desc, Xs, kind, precision, n_threads=cores)
+    dt = time.perf_counter() - t0
+    got = gpu_out[sel].cpu().numpy()
+    tol = dict(rtol=1e-5, atol=1e-6) if precision == "single" else dict(rtol=1e-12, atol=1e-12)
+    if precision == "double":
+        tol["atol"] *= max(1.0, float(np.abs(want).max()))
+    ok = bool(np.allclose(got, want, **tol))
+    rec = {"cpu": {"value": idx.size / dt, "unit": "rows/s", "cores": cores, "kind": "port",
+                   "sample": f"{idx.size} of {n} rows, same forest, {cores} OpenMP threads"},
+           "parity": {"rows_checked": int(idx.size), "scores_within_tolerance": ok,
+                      "max_abs_diff": float(np.abs(got.astype(np.float64) - want).max())}}
+    if ids_out is not None:
+        k = min(idx.size, 2000)
+        want_ids = oracle.predict(desc, Xs[:k], INFER_LEAF_ID, precision, n_threads=cores)
+        rec["parity"]["leaf_ids_exact"] = bool(
+            np.array_equal(ids_out[sel[:k]].cpu().numpy().astype(np.uint32), want_ids))
+        rec["parity"]["leaf_id_rows_checked"] = int(k)
+    return rec
+
+
+def _print_line(line):
+    print(json.dumps(line), flush=True)
+
+
+def run(config: str, steps: int, scale: float, cpu: bool = True, emit=_print_line):
+    import torch
+
+    from cuml_b200.fil import ForestInference, _lib, synthetic_complete_forest
+    from cuml_b200.fil._desc import INFER_DEFAULT, INFER_PROBA2
 
     peak, peak_kind = _peak()
     lines = []
 
     def report(name, what, n, ms, bytes_per_row, fi, extra=None):
         rows_s = n / (ms * 1e-3)
+        d = fi.describe()
         line = {"config": name, "call": what, "rows": n, "ms": ms, "rows_per_s": rows_s,
                 "algorithmic_bytes_per_row": bytes_per_row,
                 "row_stream_GBps": rows_s * bytes_per_row / 1e9,
                 "hbm_frac": rows_s * bytes_per_row / 1e9 / peak, "hbm_peak": peak_kind,
-                "forest": {k: fi.describe()[k] for k in
+                "kernel": getattr(_time, "variant", ""),
+                "forest": {k: d[k] for k in
                            ("storage", "node_bytes", "max_depth", "n_trees", "row_quantization",
                             "device_bytes")}}
         if extra:
             line.update(extra)
-        print(json.dumps(line), flush=True)
+        if emit:
+            emit(line)
         lines.append(line)
 
     if config == "c1":
@@ -105,18 +166,28 @@ def run(config: str, steps: int, scale: float):
         Xd = torch.as_tensor(Xt, device="cuda:0")
         out = torch.empty((n, 2), device="cuda:0", dtype=torch.float32)
         ms = _time(lambda: fi.predict_proba(Xd, preds=out), steps)
-        t0 = time.perf_counter()
-        m.predict_proba(Xt[:200_000])
-        sk = 200_000 / (time.perf_counter() - t0)
-        report("c1", "predict_proba", n, ms, 32 * 4 + 2 * 4, fi,
-               {"sklearn_rows_per_s": sk, "cores": os.cpu_count()})
+        extra = {}
+        if cpu:
+            extra = _cpu_and_parity(fi._desc, Xd, out, INFER_DEFAULT, "single", 500_000,
+                                    ids_out=fi.apply(Xd))
+            k = min(n, 200_000)
+            t0 = time.perf_counter()
+            sk = m.predict_proba(Xt[:k])
+            extra["cpu_sklearn"] = {"value": k / (time.perf_counter() - t0), "unit": "rows/s",
+                                    "cores": os.cpu_count(), "kind": "scikit-learn n_jobs=-1",
+                                    "sample": f"{k} of {n} rows"}
+            extra["parity"]["matches_sklearn"] = bool(
+                np.allclose(out[:k].cpu().numpy(), sk, rtol=1e-5, atol=1e-6))
+        report("c1", "predict_proba", n, ms, 32 * 4 + 2 * 4, fi, extra)
     elif config == "c2":
         n = int(10_000_000 * scale)
-        fi = ForestInference.load_from_treelite_model(synthetic_complete_forest(1000, 8, 256, 2))
+        desc = synthetic_complete_forest(1000, 8, 256, 2)
+        fi = ForestInference.load_from_treelite_model(desc)
         Xd = _randn_rows(n, 256, torch.float32, 3)
         out = torch.empty((n, 2), device="cuda:0", dtype=torch.float32)
         ms = _time(lambda: fi.predict_proba(Xd, preds=out), steps)
-        report("c2", "predict_proba", n, ms, 256 * 4 + 2 * 4, fi)
+        extra = _cpu_and_parity(desc, Xd, out, INFER_PROBA2, "single", 200_000) if cpu else None
+        report("c2", "predict_proba", n, ms, 256 * 4 + 2 * 4, fi, extra)
     elif config == "c3":
         from sklearn.datasets import make_regression
         from sklearn.ensemble import RandomForestRegressor
@@ -129,11 +200,23 @@ def run(config: str, steps: int, scale: float):
         Xd = _randn_rows(n, 64, torch.float64, 1)
         out = torch.empty((n, 1), device="cuda:0", dtype=torch.float64)
         ms = _time(lambda: fi.predict(Xd, preds=out), steps)
-        report("c3", "predict", n, ms, 64 * 8 + 8, fi)
-        del out
+        variant_predict = _time.variant
         ids = torch.empty((n, 200), device="cuda:0", dtype=torch.int32)
-        ms = _time(lambda: fi.apply(Xd, preds=ids), steps)
-        report("c3", "apply", n, ms, 64 * 8 + 200 * 4, fi)
+        ms_apply = _time(lambda: fi.apply(Xd, preds=ids), steps)
+        variant_apply = _time.variant
+        extra = {"kernel": variant_predict}
+        if cpu:
+            extra.update(_cpu_and_parity(fi._desc, Xd, out, INFER_DEFAULT, "double", 200_000,
+                                         ids_out=ids))
+            k = min(n, 100_000)
+            X32 = Xd[:k].float().cpu().numpy()  # scikit-learn predicts on fp32 inputs
+            t0 = time.perf_counter()
+            m.predict(X32)
+            extra["cpu_sklearn"] = {"value": k / (time.perf_counter() - t0), "unit": "rows/s",
+                                    "cores": os.cpu_count(), "kind": "scikit-learn n_jobs=-1",
+                                    "sample": f"{k} of {n} rows"}
+        report("c3", "predict", n, ms, 64 * 8 + 8, fi, extra)
+        report("c3", "apply", n, ms_apply, 64 * 8 + 200 * 4, fi, {"kernel": variant_apply})
     elif config == "c4":
         n = int(20_000_000 * scale)
         desc = synthetic_complete_forest(5000, 6, 128, seed=4, n_classes=10, n_categorical=8,
@@ -148,14 +231,17 @@ def run(config: str, steps: int, scale: float):
             Xd[b:e][torch.rand((e - b, 128), generator=g, device="cuda:0") < 0.05] = float("nan")
         out = torch.empty((n, 10), device="cuda:0", dtype=torch.float32)
         ms = _time(lambda: fi.predict_proba(Xd, preds=out), steps)
-        report("c4", "predict_proba", n, ms, 128 * 4 + 10 * 4, fi)
+        extra = _cpu_and_parity(desc, Xd, out, INFER_DEFAULT, "single", 100_000) if cpu else None
+        report("c4", "predict_proba", n, ms, 128 * 4 + 10 * 4, fi, extra)
     elif config == "c5":
         n = int(20_000_000 * scale)
-        fi = ForestInference.load_from_treelite_model(synthetic_complete_forest(2000, 10, 512, 6))
+        desc = synthetic_complete_forest(2000, 10, 512, 6)
+        fi = ForestInference.load_from_treelite_model(desc)
         Xd = _randn_rows(n, 512, torch.float32, 7)
         out = torch.empty((n, 2), device="cuda:0", dtype=torch.float32)
         ms = _time(lambda: fi.predict_proba(Xd, preds=out), steps)
-        report("c5", "predict_proba", n, ms, 512 * 4 + 2 * 4, fi)
+        extra = _cpu_and_parity(desc, Xd, out, INFER_PROBA2, "single", 100_000) if cpu else None
+        report("c5", "predict_proba", n, ms, 512 * 4 + 2 * 4, fi, extra)
     elif config == "sweep":
         fi = ForestInference.load_from_treelite_model(synthetic_complete_forest(1000, 8, 256, 2))
         big = int(10_000_000 * scale)
@@ -185,9 +271,11 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--rows-scale", type=float, default=1.0,
                     help="multiply every configuration's row count (smaller runs)")
+    ap.add_argument("--no-cpu", action="store_true",
+                    help="skip the CPU baseline / parity leg (profiling runs)")
     args = ap.parse_args()
     for c in args.config:
-        run(c, args.steps, args.rows_scale)
+        run(c, args.steps, args.rows_scale, cpu=not args.no_cpu)
         import torch
 
         torch.cuda.empty_cache()

@@ -4,7 +4,10 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstring>
+#include <functional>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <new>
@@ -52,6 +55,77 @@ struct DeviceGuard {
   }
 };
 
+// Peer access is a per-process setting of a device pair.  It is switched on the first time a pair
+// is used (forest replication, output gather) and remembered: 1 = `dev` maps `peer`'s memory
+// directly (copies between them do not pass through host memory), 0 = it cannot.
+std::mutex g_peer_mu;
+std::map<std::pair<int, int>, int> g_peer;
+
+int enable_peer_one_way(int dev, int peer)
+{
+  if (dev == peer) return 1;
+  std::lock_guard<std::mutex> lock(g_peer_mu);
+  const auto key = std::make_pair(dev, peer);
+  const auto it  = g_peer.find(key);
+  if (it != g_peer.end()) return it->second;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer) != cudaSuccess) {
+    cudaGetLastError();
+    can = 0;
+  }
+  if (can) {
+    DeviceGuard guard(dev);
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      cudaGetLastError();  // somebody else in the process (e.g. the array library) did it already
+    } else if (e != cudaSuccess) {
+      cudaGetLastError();
+      can = 0;
+    }
+  }
+  g_peer[key] = can;
+  return can;
+}
+
+// Both directions: a peer copy is direct when either side can issue it, the library enables both.
+int enable_peer_pair(int a, int b)
+{
+  const int ab = enable_peer_one_way(a, b);
+  const int ba = enable_peer_one_way(b, a);
+  return (ab && ba) ? 1 : 0;
+}
+
+// Device times of the calling thread's last b2fil_predict_sharded call.
+struct ShardTiming {
+  double compute_ms = 0, gather_ms = 0, wall_ms = 0;
+  int direct = 0, valid = 0;
+};
+thread_local ShardTiming g_shard_timing;
+
+// Pipeline shape of b2fil_predict_host (tuning aids B2FIL_HOST_BLOCK_MB / B2FIL_HOST_SLOTS, read
+// from the environment once).
+constexpr int kMaxHostSlots = 4;
+struct HostPipeCfg {
+  size_t block_bytes = size_t(256) << 20;
+  int slots          = 2;
+  HostPipeCfg()
+  {
+    if (const char* e = getenv("B2FIL_HOST_BLOCK_MB")) {
+      const long mb = atol(e);
+      if (mb >= 1 && mb <= 4096) block_bytes = static_cast<size_t>(mb) << 20;
+    }
+    if (const char* e = getenv("B2FIL_HOST_SLOTS")) {
+      const long n = atol(e);
+      if (n >= 1 && n <= kMaxHostSlots) slots = static_cast<int>(n);
+    }
+  }
+};
+const HostPipeCfg& host_pipe_cfg()
+{
+  static const HostPipeCfg cfg;
+  return cfg;
+}
+
 }  // namespace
 
 // One slot of the host-buffer pipeline: device staging buffers and the stream that orders them.
@@ -61,6 +135,7 @@ struct HostSlot {
   void* out           = nullptr;
   size_t x_bytes      = 0;
   size_t out_bytes    = 0;
+  cudaEvent_t ev[3]   = {nullptr, nullptr, nullptr};  // sharded prediction: begin, kernels done, gathered
 };
 
 struct b2fil_forest {
@@ -77,8 +152,10 @@ struct b2fil_forest {
     size_t view_offset;  // offset of the pointer member inside ForestView
   };
   std::vector<Block> blocks;
+  int32_t clone_src_device = -1;  // device this forest was replicated from, or -1
+  int32_t clone_direct     = -1;  // 1: that replication went over a direct peer path
   std::mutex host_mu;  // serialises the calls that use the slots below
-  HostSlot slots[2];
+  HostSlot slots[kMaxHostSlots];
   ~b2fil_forest()
   {
     DeviceGuard g(device);
@@ -89,6 +166,8 @@ struct b2fil_forest {
       if (s.x) cudaFree(s.x);
       if (s.out) cudaFree(s.out);
       if (s.stream) cudaStreamDestroy(s.stream);
+      for (auto& e : s.ev)
+        if (e) cudaEventDestroy(e);
     }
   }
 };
@@ -316,6 +395,8 @@ int b2fil_forest_clone_to_device(const b2fil_forest* src, int device_id, b2fil_f
     if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
     int rc;
     if ((rc = init_device_state(f.get())) != B2FIL_OK) return rc;
+    f->clone_src_device = src->device;
+    f->clone_direct     = enable_peer_pair(device_id, src->device);
     for (const auto& b : src->blocks) {
       void* d       = nullptr;
       cudaError_t e = cudaMalloc(&d, b.bytes);
@@ -326,8 +407,8 @@ int b2fil_forest_clone_to_device(const b2fil_forest* src, int device_id, b2fil_f
       if (e != cudaSuccess) return cuda_error("cudaMalloc", e);
       f->blocks.push_back({d, b.bytes, b.view_offset});
       f->device_bytes += static_cast<int64_t>(b.bytes);
-      // cudaMemcpyPeer uses a direct peer path when the devices can reach each other and stages
-      // through the host otherwise
+      // direct over the peer path when it could be enabled above, staged through the host
+      // otherwise
       B2FIL_CUDA(cudaMemcpyPeer(d, device_id, b.ptr, src->device, b.bytes));
       std::memcpy(reinterpret_cast<char*>(&f->view) + b.view_offset, &d, sizeof(void*));
     }
@@ -365,6 +446,15 @@ int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info)
   info->device_bytes       = f->device_bytes;
   info->default_chunk_size = f->default_chunk;
   info->row_quantization   = f->view.q_enabled;
+  info->peer_direct        = f->clone_direct;
+  info->clone_src_device   = f->clone_src_device;
+  if (f->pool) {
+    uint64_t reserved = 0;
+    if (cudaMemPoolGetAttribute(f->pool, cudaMemPoolAttrReservedMemCurrent, &reserved) == cudaSuccess)
+      info->scratch_pool_bytes = static_cast<int64_t>(reserved);
+    else
+      cudaGetLastError();
+  }
   return B2FIL_OK;
 }
 
@@ -379,13 +469,77 @@ int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind)
   return n;
 }
 
+namespace {
+// Read and clear the status word.  The caller has already waited for the work it cares about.
+int read_status_word(const b2fil_forest* f, int32_t* status)
+{
+  B2FIL_CUDA(cudaMemcpy(status, f->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (*status != 0) {
+    // reported once: the next prediction starts from a clean word
+    B2FIL_CUDA(cudaMemset(f->status, 0, sizeof(int32_t)));
+    static const char* const where[] = {"", "tree ring (producer)", "tree ring (consumer)",
+                                        "row-tile buffer", "rank tables", "self test"};
+    const char* w = (*status >= 1 && *status <= 5) ? where[*status] : "unknown";
+    return set_error(B2FIL_ERR_TIMEOUT, std::string("a bounded wait inside a kernel ran out: ") +
+                                          w + " (status " + std::to_string(*status) + ")");
+  }
+  return B2FIL_OK;
+}
+}  // namespace
+
 int b2fil_forest_status(const b2fil_forest* f, int32_t* status)
 {
   if (!f || !status) return set_error(B2FIL_ERR_INVALID_ARG, "NULL argument");
   DeviceGuard guard(f->device);
-  B2FIL_CUDA(cudaMemcpy(status, f->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
-  if (*status != 0)
-    return set_error(B2FIL_ERR_TIMEOUT, "a bounded wait inside a prediction kernel ran out");
+  if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+  // every stream of the device, the non-blocking ones included: a plain copy on the default
+  // stream would not wait for them
+  B2FIL_CUDA(cudaDeviceSynchronize());
+  return read_status_word(f, status);
+}
+
+int b2fil_forest_selftest_timeout(b2fil_forest* f, int tries, void* cuda_stream)
+{
+  if (!f) return set_error(B2FIL_ERR_INVALID_ARG, "forest is NULL");
+  if (tries < 1 || tries > 4096)
+    return set_error(B2FIL_ERR_INVALID_ARG, "tries must be between 1 and 4096");
+  DeviceGuard guard(f->device);
+  if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+  std::string err;
+  const int rc = launch_bounded_wait_selftest(f->status, static_cast<uint32_t>(tries),
+                                              static_cast<cudaStream_t>(cuda_stream), err);
+  if (rc != B2FIL_OK) return set_error(rc, err);
+  return B2FIL_OK;
+}
+
+int b2fil_enable_peer_access(int device_a, int device_b)
+{
+  int n_dev = 0;
+  B2FIL_CUDA(cudaGetDeviceCount(&n_dev));
+  if (device_a < 0 || device_b < 0 || device_a >= n_dev || device_b >= n_dev)
+    return set_error(B2FIL_ERR_INVALID_ARG, "device ordinal out of range");
+  return enable_peer_pair(device_a, device_b);
+}
+
+int b2fil_last_variant(char* buf, size_t buf_bytes)
+{
+  if (!buf || buf_bytes == 0) return set_error(B2FIL_ERR_INVALID_ARG, "NULL or empty buffer");
+  const std::string v = last_launch_variant();
+  const size_t n      = std::min(v.size(), buf_bytes - 1);
+  std::memcpy(buf, v.data(), n);
+  buf[n] = 0;
+  return static_cast<int>(v.size());
+}
+
+int b2fil_last_sharded_timing(double* compute_ms, double* gather_ms, double* wall_ms,
+                              int* gather_direct)
+{
+  const ShardTiming& t = g_shard_timing;
+  if (!t.valid) return set_error(B2FIL_ERR_INVALID_ARG, "no sharded prediction on this thread yet");
+  if (compute_ms) *compute_ms = t.compute_ms;
+  if (gather_ms) *gather_ms = t.gather_ms;
+  if (wall_ms) *wall_ms = t.wall_ms;
+  if (gather_direct) *gather_direct = t.direct;
   return B2FIL_OK;
 }
 
@@ -444,40 +598,52 @@ int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int6
   const size_t out_row_b = static_cast<size_t>(out_elems(f, infer_kind)) * out_elem_bytes(f, infer_kind);
   // row blocks of about 256 MiB of input (and at most 256 MiB of output) keep both copy engines
   // and the SMs busy while two blocks are in flight
-  const size_t budget = size_t(256) << 20;
+  const HostPipeCfg& pipe = host_pipe_cfg();
+  const size_t budget     = pipe.block_bytes;
   int64_t block_rows  = static_cast<int64_t>(std::max<size_t>(1, budget / std::max(in_row_b, out_row_b)));
   block_rows          = std::max<int64_t>(block_rows / 128 * 128, 128);
   block_rows          = std::min(block_rows, n_rows);
-  for (auto& s : f->slots) {
-    rc = ensure_slot(f, s, static_cast<size_t>(block_rows) * in_row_b,
+  for (int i = 0; i < pipe.slots; ++i) {
+    rc = ensure_slot(f, f->slots[i], static_cast<size_t>(block_rows) * in_row_b,
                      static_cast<size_t>(block_rows) * out_row_b);
-    if (rc != B2FIL_OK) return rc;
+    if (rc != B2FIL_OK) return rc;  // nothing has been enqueued yet
   }
   const char* xin = static_cast<const char*>(X_host);
   char* yout      = static_cast<char*>(out_host);
   int which       = 0;
-  for (int64_t r0 = 0; r0 < n_rows; r0 += block_rows, which ^= 1) {
+  for (int64_t r0 = 0; r0 < n_rows && rc == B2FIL_OK; r0 += block_rows, which = (which + 1) % pipe.slots) {
     HostSlot& s     = f->slots[which];
     const int64_t n = std::min(block_rows, n_rows - r0);
     // stream order makes the slot's previous block finish before its buffers are reused
+    cudaError_t e;
     if (row_stride == F) {
-      B2FIL_CUDA(cudaMemcpyAsync(s.x, xin + static_cast<size_t>(r0) * in_row_b,
-                                 static_cast<size_t>(n) * in_row_b, cudaMemcpyHostToDevice,
-                                 s.stream));
+      e = cudaMemcpyAsync(s.x, xin + static_cast<size_t>(r0) * in_row_b,
+                          static_cast<size_t>(n) * in_row_b, cudaMemcpyHostToDevice, s.stream);
     } else {
-      B2FIL_CUDA(cudaMemcpy2DAsync(s.x, in_row_b, xin + static_cast<size_t>(r0) * row_stride * es,
-                                   static_cast<size_t>(row_stride) * es, in_row_b,
-                                   static_cast<size_t>(n), cudaMemcpyHostToDevice, s.stream));
+      e = cudaMemcpy2DAsync(s.x, in_row_b, xin + static_cast<size_t>(r0) * row_stride * es,
+                            static_cast<size_t>(row_stride) * es, in_row_b, static_cast<size_t>(n),
+                            cudaMemcpyHostToDevice, s.stream);
+    }
+    if (e != cudaSuccess) {
+      rc = cuda_error("host-to-device copy of a row block", e);
+      break;
     }
     rc = enqueue(f, infer_kind, s.x, n, F, s.out, chunk_size, threshold, s.stream);
-    if (rc != B2FIL_OK) return rc;
-    B2FIL_CUDA(cudaMemcpyAsync(yout + static_cast<size_t>(r0) * out_row_b, s.out,
-                               static_cast<size_t>(n) * out_row_b, cudaMemcpyDeviceToHost,
-                               s.stream));
+    if (rc != B2FIL_OK) break;
+    e = cudaMemcpyAsync(yout + static_cast<size_t>(r0) * out_row_b, s.out,
+                        static_cast<size_t>(n) * out_row_b, cudaMemcpyDeviceToHost, s.stream);
+    if (e != cudaSuccess) rc = cuda_error("device-to-host copy of a result block", e);
   }
-  for (auto& s : f->slots) B2FIL_CUDA(cudaStreamSynchronize(s.stream));
+  // Also after an error: copies already enqueued still read and write the caller's buffers, so
+  // the call may not return before they are done.
+  for (int i = 0; i < pipe.slots; ++i) {
+    if (!f->slots[i].stream) continue;
+    const cudaError_t e = cudaStreamSynchronize(f->slots[i].stream);
+    if (e != cudaSuccess && rc == B2FIL_OK) rc = cuda_error("cudaStreamSynchronize", e);
+  }
+  if (rc != B2FIL_OK) return rc;
   int32_t status = 0;
-  return b2fil_forest_status(f, &status);
+  return read_status_word(f, &status);
 }
 
 int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer_kind,
@@ -501,14 +667,28 @@ int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer
   b2fil_forest* f0       = forests[0];
   const size_t out_row_b = static_cast<size_t>(out_elems(f0, infer_kind)) * out_elem_bytes(f0, infer_kind);
   // every device predicts its shard on its own stream; shards of devices other than the first
-  // land in a staging buffer on their device and are pushed to device 0 by a peer copy
+  // land in a staging buffer on their device and are pushed to device 0 by a peer copy.
+  // The forests' locks are taken in address order, so two callers that pass the same forests in
+  // different orders cannot wait for each other.
+  std::vector<b2fil_forest*> by_address(forests, forests + n_devices);
+  std::sort(by_address.begin(), by_address.end(), std::less<b2fil_forest*>());
   std::vector<std::unique_lock<std::mutex>> locks;
-  for (int i = 0; i < n_devices; ++i) locks.emplace_back(forests[i]->host_mu);
+  for (b2fil_forest* f : by_address) locks.emplace_back(f->host_mu);
+  int direct = 1;
+  for (int i = 1; i < n_devices; ++i)
+    direct &= enable_peer_pair(forests[i]->device, f0->device);
+
+  const auto t0  = std::chrono::steady_clock::now();
+  int rc_final   = B2FIL_OK;
   int64_t row_off = 0;
-  for (int i = 0; i < n_devices; ++i) {
+  std::vector<int> fed;  // devices that have work enqueued
+  for (int i = 0; i < n_devices && rc_final == B2FIL_OK; ++i) {
     b2fil_forest* f = forests[i];
     DeviceGuard guard(f->device);
-    if (!guard.ok) return set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+    if (!guard.ok) {
+      rc_final = set_error(B2FIL_ERR_CUDA, "cudaSetDevice failed");
+      break;
+    }
     HostSlot& s     = f->slots[0];
     const int64_t n = shard_rows[i];
     char* dst0      = static_cast<char*>(out_dev0) + static_cast<size_t>(row_off) * out_row_b;
@@ -516,27 +696,53 @@ int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer
     if (n == 0) continue;
     const bool local = f->device == f0->device;
     int rc = ensure_slot(f, s, 0, local ? 0 : static_cast<size_t>(n) * out_row_b);
-    if (rc != B2FIL_OK) return rc;
+    for (auto& ev : s.ev) {
+      if (rc == B2FIL_OK && !ev && cudaEventCreate(&ev) != cudaSuccess)
+        rc = set_error(B2FIL_ERR_CUDA, "cudaEventCreate failed");
+    }
+    if (rc != B2FIL_OK) {
+      rc_final = rc;
+      break;
+    }
+    fed.push_back(i);
+    cudaEventRecord(s.ev[0], s.stream);
     rc = enqueue(f, infer_kind, X_shards[i], n, row_stride, local ? static_cast<void*>(dst0) : s.out,
                  chunk_size, threshold, s.stream);
-    if (rc != B2FIL_OK) return rc;
-    if (!local) {
-      B2FIL_CUDA(cudaMemcpyPeerAsync(dst0, f0->device, s.out, f->device,
-                                     static_cast<size_t>(n) * out_row_b, s.stream));
+    cudaEventRecord(s.ev[1], s.stream);
+    if (rc == B2FIL_OK && !local) {
+      const cudaError_t e = cudaMemcpyPeerAsync(dst0, f0->device, s.out, f->device,
+                                                static_cast<size_t>(n) * out_row_b, s.stream);
+      if (e != cudaSuccess) rc = cuda_error("cudaMemcpyPeerAsync", e);
     }
+    cudaEventRecord(s.ev[2], s.stream);
+    if (rc != B2FIL_OK) rc_final = rc;
   }
-  int rc_final = B2FIL_OK;
-  for (int i = 0; i < n_devices; ++i) {
+  // Wait for every device that was fed, also after an error on a later device: their kernels and
+  // copies still write into the caller's output.
+  ShardTiming timing;
+  for (int i : fed) {
     b2fil_forest* f = forests[i];
     DeviceGuard guard(f->device);
-    if (f->slots[0].stream) {
-      const cudaError_t e = cudaStreamSynchronize(f->slots[0].stream);
-      if (e != cudaSuccess && rc_final == B2FIL_OK) rc_final = cuda_error("cudaStreamSynchronize", e);
+    HostSlot& s         = f->slots[0];
+    const cudaError_t e = cudaStreamSynchronize(s.stream);
+    if (e != cudaSuccess) {
+      if (rc_final == B2FIL_OK) rc_final = cuda_error("cudaStreamSynchronize", e);
+      continue;
     }
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, s.ev[0], s.ev[1]) == cudaSuccess)
+      timing.compute_ms = std::max(timing.compute_ms, static_cast<double>(ms));
+    if (cudaEventElapsedTime(&ms, s.ev[1], s.ev[2]) == cudaSuccess)
+      timing.gather_ms = std::max(timing.gather_ms, static_cast<double>(ms));
     int32_t status = 0;
-    const int rc   = b2fil_forest_status(f, &status);
+    const int rc   = read_status_word(f, &status);
     if (rc != B2FIL_OK && rc_final == B2FIL_OK) rc_final = rc;
   }
+  timing.wall_ms =
+    std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  timing.direct  = direct;
+  timing.valid   = 1;
+  g_shard_timing = timing;
   return rc_final;
 }
 

@@ -67,11 +67,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the barrier did not complete within kSpinLimit tries (each try blocks
+// Bounded wait: false when the barrier did not complete within `limit` tries (each try blocks
 // for a hardware-defined short time, then the warp sleeps briefly).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, uint32_t limit)
 {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     // a waiting warp must not compete for issue slots with the warps that are walking trees
 #if B2FIL_SPIN_NS > 0
@@ -79,6 +79,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 #endif
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+  return mbar_wait_limited(bar, parity, kSpinLimit);
 }
 // Position in a ring of S stages: the stage index and the parity of its current use, advanced
 // without a division.

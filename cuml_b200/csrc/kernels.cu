@@ -28,6 +28,42 @@
 
 namespace b2fil {
 namespace {
+// What the calling thread launched last (see last_launch_variant()).  Plain data: filling it costs
+// a few stores per call, the text is only formatted when somebody asks.
+struct LaunchRecord {
+  const char* prepass = nullptr;  // kernel that ran before the traversal, or null
+  const char* kernel  = nullptr;  // traversal kernel family
+  const char* real    = "";       // float / double
+  int mode = 0, nt = 0, depth = -1, cat = -1, fmt = -1;
+  int R = 0, G = 0, S = 0, K = 0, splits = 1;
+};
+thread_local LaunchRecord g_last_launch;
+
+const char* mode_name(int mode)
+{
+  switch (mode) {
+    case 0: return "scalar";
+    case 1: return "vector";
+    case 2: return "per_tree";
+    default: return "leaf_id";
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bounded-wait self test
+// ---------------------------------------------------------------------------------------------
+__global__ void bounded_wait_selftest_kernel(int32_t* status, const uint32_t tries)
+{
+  __shared__ __align__(8) unsigned long long bar_word;
+  const uint32_t bar = smem_addr(&bar_word);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);  // one arrival expected; nothing ever arrives
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait_limited(bar, 0, tries)) atomicExch(status, 5);
+}
+
 // ---------------------------------------------------------------------------------------------
 // DENSE kernel
 // ---------------------------------------------------------------------------------------------
@@ -755,9 +791,19 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
   } else {
     while (want > 32 && n_rows < static_cast<int64_t>(want) * sm_count) want /= 2;
   }
-  if (const char* e = getenv("B2FIL_Q_SHAPE")) {  // tuning aid: "R,G,NT,S,K"
-    int R, G, NT, S, K;
-    if (sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5 && R >= 32 && R % 32 == 0 &&
+  // tuning aid "R,G,NT,S,K", read from the environment once per process
+  static const struct ForcedShape {
+    bool set = false;
+    int R = 0, G = 0, NT = 0, S = 0, K = 0;
+    ForcedShape()
+    {
+      const char* e = getenv("B2FIL_Q_SHAPE");
+      set = e && sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5;
+    }
+  } forced;
+  if (forced.set) {
+    const int R = forced.R, G = forced.G, NT = forced.NT, S = forced.S, K = forced.K;
+    if (R >= 32 && R % 32 == 0 &&
         R <= 256 && (R & (R - 1)) == 0 && G >= 1 && (R / 32) * G <= 31 &&
         (NT == 1 || NT == 2 || NT == 4 || (NT == 6 && (R / 32) * G <= 24)) && S >= 2 &&
         S <= kMaxStages && K >= 1 && NT <= max_nt) {
@@ -798,15 +844,41 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
 int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err)
 {
   const ForestView& f = L.p.f;
-  if (f.q_has_cat) return launch_q_cat(L, mode, f64, err);
+  LaunchRecord& rec   = g_last_launch;
+  rec                 = LaunchRecord{};
+  rec.prepass         = "quantise_kernel";
+  rec.kernel          = "dense_q_kernel";
+  rec.real            = f64 ? "double" : "float";
+  rec.mode            = mode;
+  rec.nt              = L.c.trees_in_flight;
+  rec.depth           = 0;  // read at run time unless a specialised body is picked below
+  rec.cat             = f.q_has_cat ? 1 : 0;
+  rec.R               = L.c.rows_per_tile;
+  rec.G               = L.c.tree_groups;
+  rec.S               = L.c.stages;
+  rec.K               = L.c.sub_batches;
+  if (f.q_has_cat) {
+    // kernels_q_cat.cu: fp32 scalar leaves of depth 4..8 with four trees in flight are specialised
+    if (!f64 && mode == MODE_SCALAR && L.c.trees_in_flight == 4 && f.dense_depth >= 4 &&
+        f.dense_depth <= 8)
+      rec.depth = f.dense_depth;
+    return launch_q_cat(L, mode, f64, err);
+  }
   const bool specialised = !f64 && mode == MODE_SCALAR && f.dense_depth >= 4 && f.dense_depth <= 10;
   if (specialised && L.c.trees_in_flight == 6) {
     // the common boosted-tree shapes: depth-specialised bodies with six trees in flight
     // (q_max_trees_in_flight offers six only for them)
-    if (L.p.q_top != nullptr && f.n_trees <= kQTopTrees) return launch_q_top6(L, err);
+    rec.depth = f.dense_depth;
+    if (L.p.q_top != nullptr && f.n_trees <= kQTopTrees) {
+      rec.kernel = "dense_q_top_kernel";
+      return launch_q_top6(L, err);
+    }
     return launch_q_plain6(L, err);
   }
-  if (specialised && L.c.trees_in_flight == 4) return launch_q_plain4(L, err);
+  if (specialised && L.c.trees_in_flight == 4) {
+    rec.depth = f.dense_depth;
+    return launch_q_plain4(L, err);
+  }
   return launch_q_generic(L, mode, f64, err);
 }
 
@@ -832,11 +904,15 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   // measured on the 1000-tree depth-8 forest: 64 MB chunks (rank image resident in L2) 2.51e8
   // rows/s, 512 MB chunks 2.62e8: fewer, longer launches beat L2 residency because HBM has
   // plenty of headroom on this path
-  size_t target = size_t(512) << 20;
-  if (const char* e = getenv("B2FIL_Q_CHUNK_MB")) {  // tuning aid: size of the rank scratch
-    const long mb = atol(e);
-    if (mb >= 1 && mb <= 16384) target = static_cast<size_t>(mb) << 20;
-  }
+  // (B2FIL_Q_CHUNK_MB, a tuning aid, overrides the size; the environment is read once)
+  static const size_t target = [] {
+    size_t t = size_t(512) << 20;
+    if (const char* e = getenv("B2FIL_Q_CHUNK_MB")) {
+      const long mb = atol(e);
+      if (mb >= 1 && mb <= 16384) t = static_cast<size_t>(mb) << 20;
+    }
+    return t;
+  }();
   const int64_t waves    = std::max<int64_t>(1, static_cast<int64_t>(target / (tile_b * sm_count)));
   const int64_t chunk    = std::min<int64_t>(wave * waves, (p.n_rows + R - 1) / R * R);
   const int64_t ch_tiles = (chunk + R - 1) / R;
@@ -1069,6 +1145,19 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
       }
     }
     const dim3 grid(gx, n_splits);
+    {
+      LaunchRecord& rec = g_last_launch;
+      rec               = LaunchRecord{};
+      rec.kernel        = "dense_kernel";
+      rec.real          = precision == B2FIL_F32 ? "float" : "double";
+      rec.mode          = mode;
+      rec.nt            = c.trees_in_flight == 2 ? 2 : 1;
+      rec.cat           = f.has_categorical ? 1 : 0;
+      rec.R             = c.rows_per_tile;
+      rec.G             = c.tree_groups;
+      rec.S             = c.stages;
+      rec.splits        = n_splits;
+    }
     if (precision == B2FIL_F32) {
       rc = f.has_categorical
              ? launch_dense_cat<float, true>(p, mode, c, grid, n_splits, partial, stream, err)
@@ -1112,6 +1201,17 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
     const size_t smem     = acc_b + tile_b;
     const int64_t n_tiles = (p.n_rows + R - 1) / R;
     const int grid        = static_cast<int>(std::min<int64_t>(n_tiles, int64_t(sm_count) * 8));
+    {
+      LaunchRecord& rec = g_last_launch;
+      rec               = LaunchRecord{};
+      rec.kernel        = "sparse_kernel";
+      rec.real          = f.format == FMT_SPARSE_16D ? "double" : "float";
+      rec.mode          = mode;
+      rec.nt            = 4;
+      rec.fmt           = f.format;
+      rec.R             = R;
+      rec.G             = G;
+    }
     switch (f.format) {
       case FMT_SPARSE_8:
         rc = launch_sparse_fmt<FMT_SPARSE_8>(p, mode, R, G, rows_in_smem, grid, smem, stream, err);
@@ -1217,6 +1317,38 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
     return B2FIL_ERR_CUDA;
   }
   if (launches) *launches += 2;
+  return B2FIL_OK;
+}
+
+std::string last_launch_variant()
+{
+  const LaunchRecord& r = g_last_launch;
+  if (!r.kernel) return std::string();
+  std::string s;
+  if (r.prepass) s += std::string(r.prepass) + "<" + r.real + "> + ";
+  s += std::string(r.kernel) + "<" + r.real;
+  if (r.fmt >= 0) {
+    s += r.fmt == FMT_SPARSE_8 ? ",node8" : (r.fmt == FMT_SPARSE_16F ? ",node16f" : ",node16d");
+  }
+  s += std::string(",") + mode_name(r.mode) + ",NT=" + std::to_string(r.nt);
+  if (r.depth >= 0) s += ",DEPTH=" + (r.depth ? std::to_string(r.depth) : std::string("runtime"));
+  if (r.cat >= 0) s += r.cat ? ",CAT" : "";
+  s += "> R=" + std::to_string(r.R) + " G=" + std::to_string(r.G);
+  if (r.S) s += " S=" + std::to_string(r.S);
+  if (r.K) s += " K=" + std::to_string(r.K);
+  if (r.splits > 1) s += " forest_splits=" + std::to_string(r.splits) + " + finish_kernel";
+  return s;
+}
+
+int launch_bounded_wait_selftest(int32_t* status, uint32_t tries, cudaStream_t stream,
+                                 std::string& err)
+{
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, tries);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    err = std::string("kernel launch: ") + cudaGetErrorString(e);
+    return B2FIL_ERR_CUDA;
+  }
   return B2FIL_OK;
 }
 

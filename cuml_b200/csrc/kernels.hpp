@@ -57,4 +57,15 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
 int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_count, int device,
                                  cudaStream_t stream, std::string& err, int64_t* launches);
 
+// What the calling thread's most recent launch_predict* call enqueued: kernel family, template
+// arguments and launch shape, e.g. "quantise_kernel<float> + dense_q_top_kernel<float,scalar,
+// NT=6,DEPTH=8> R=256 G=3 S=2 K=2".  Empty before the first launch.
+std::string last_launch_variant();
+
+// Launch a one-CTA kernel whose only work is a bounded wait that nothing ends (an mbarrier that
+// never receives its arrival): after `tries` tries it sets *status exactly like the prediction
+// kernels do when one of their waits runs out, and returns.  Exercises the timeout reporting.
+int launch_bounded_wait_selftest(int32_t* status, uint32_t tries, cudaStream_t stream,
+                                 std::string& err);
+
 }  // namespace b2fil

@@ -101,6 +101,9 @@ class CInfo(C.Structure):
         ("device_bytes", C.c_int64),
         ("default_chunk_size", C.c_int32),
         ("row_quantization", C.c_int32),
+        ("peer_direct", C.c_int32),
+        ("clone_src_device", C.c_int32),
+        ("scratch_pool_bytes", C.c_int64),
     ]
 
 

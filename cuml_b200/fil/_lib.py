@@ -25,14 +25,19 @@ _lib = None
 
 
 def load() -> C.CDLL:
-    """Load libb2fil.so, building it with nvcc when it has never been built."""
+    """Load libb2fil.so, building it with nvcc when it is missing or older than its sources."""
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        from .. import build as _build
+    from .. import build as _build
 
-        _build.build()
+    if not _build.up_to_date():
+        try:
+            _build.build()
+        except Exception:
+            # a stale library on a box without nvcc is still loadable; a missing one is not
+            if not os.path.exists(LIB_PATH):
+                raise
     if not os.path.exists(LIB_PATH):
         raise ImportError(f"{LIB_PATH} is missing and could not be built; "
                           "run `python -m cuml_b200.build`")
@@ -53,6 +58,15 @@ def load() -> C.CDLL:
     lib.b2fil_forest_info.argtypes = [vp, C.POINTER(CInfo)]
     lib.b2fil_forest_status.restype = i32
     lib.b2fil_forest_status.argtypes = [vp, C.POINTER(C.c_int32)]
+    lib.b2fil_forest_selftest_timeout.restype = i32
+    lib.b2fil_forest_selftest_timeout.argtypes = [vp, i32, vp]
+    lib.b2fil_last_variant.restype = i32
+    lib.b2fil_last_variant.argtypes = [C.c_char_p, C.c_size_t]
+    lib.b2fil_enable_peer_access.restype = i32
+    lib.b2fil_enable_peer_access.argtypes = [i32, i32]
+    lib.b2fil_last_sharded_timing.restype = i32
+    lib.b2fil_last_sharded_timing.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                              C.POINTER(C.c_double), C.POINTER(i32)]
     lib.b2fil_output_elems_per_row.restype = i64
     lib.b2fil_output_elems_per_row.argtypes = [vp, i32]
     lib.b2fil_predict.restype = i32
@@ -66,6 +80,13 @@ def load() -> C.CDLL:
                                           C.POINTER(i64), i64, vp, i32, C.c_double]
     _lib = lib
     return lib
+
+
+def last_variant() -> str:
+    """Kernels the calling thread's most recent prediction enqueued (`b2fil_last_variant`)."""
+    buf = C.create_string_buffer(512)
+    load().b2fil_last_variant(buf, len(buf))
+    return buf.value.decode()
 
 
 def check(rc: int) -> None:

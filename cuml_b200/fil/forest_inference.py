@@ -169,8 +169,9 @@ class ForestInference:
 
     @classmethod
     def load(cls, path, *, model_type: Optional[str] = None, **kwargs) -> "ForestInference":
-        """Create from a model file: XGBoost JSON ('xgboost_json'), LightGBM text ('lightgbm'),
-        Treelite JSON dump ('treelite_json') or a saved forest description ('b2fil_npz')."""
+        """Create from a model file: XGBoost JSON ('xgboost_json') or UBJSON ('xgboost_ubjson',
+        *.ubj), LightGBM text ('lightgbm'), Treelite JSON dump ('treelite_json') or a saved
+        forest description ('b2fil_npz').  Without `model_type` the file extension decides."""
         from .loaders import load_file
 
         return cls.load_from_treelite_model(load_file(path, model_type), **kwargs)
@@ -194,9 +195,18 @@ class ForestInference:
     def n_features(self) -> int:
         return int(self.forest.info.n_features)
 
+    def check_status(self) -> None:
+        """Wait for all work on the forest's device and raise `B2FilError` (code -7) if a
+        bounded wait inside a prediction kernel ran out since the last check.  Device-array
+        predictions are stream ordered and do not check this themselves; host-array and sharded
+        predictions do."""
+        st = C.c_int32(0)
+        _lib.check(_lib.load().b2fil_forest_status(self.forest.handle, C.byref(st)))
+
     def describe(self) -> dict:
         """Facts about the packed forest (storage chosen, node size, device bytes...)."""
-        i = self.forest.info
+        i = CInfo()  # asked again on every call: the scratch pool's size changes over time
+        _lib.check(_lib.load().b2fil_forest_info(self.forest.handle, C.byref(i)))
         return {n: getattr(i, n) for n, _ in CInfo._fields_ if n != "reserved"}
 
     # -- pickling: the device forest is dropped and rebuilt on load

@@ -122,3 +122,84 @@ def from_lightgbm_text(text: str) -> ForestDesc:
         class_id=(np.arange(n_trees) % per_iter).astype(np.int32) if k > 1 else None,
         average_tree_output=bool(average), postproc=post, sigmoid_alpha=alpha,
         is_classifier=is_clf, native_precision="double")
+
+
+def to_lightgbm_text(desc: ForestDesc, objective: str = "regression") -> str:
+    """Write a forest description in the text format `from_lightgbm_text` reads (test files and
+    round trips; LightGBM itself is not involved).  The description must use what the format can
+    say: `<=` tests, listed categories going left with missing values going right at categorical
+    nodes, scalar leaves, tree t feeding class t % n_classes.  Internal nodes are renumbered
+    first and leaves after them, as the format prescribes, so leaf ids change."""
+    kinds = np.asarray(desc.node_kind)
+    if desc.leaf_vector_len != 1:
+        raise ValueError("the LightGBM format holds scalar leaves only")
+    ops = np.asarray(desc.op) if desc.op is not None else np.full(len(kinds), desc.op_all)
+    if np.any(ops[kinds == NODE_NUMERICAL] != OP_LE):
+        raise ValueError("the LightGBM format tests x <= threshold only")
+    if np.any(kinds == NODE_CATEGORICAL):
+        cr = np.asarray(desc.cat_right) if desc.cat_right is not None else np.ones(len(kinds))
+        if np.any(cr[kinds == NODE_CATEGORICAL] != 0) or np.any(
+                np.asarray(desc.default_left)[kinds == NODE_CATEGORICAL] != 0):
+            raise ValueError("LightGBM categorical tests send listed categories left and "
+                             "missing values right")
+    k = desc.n_outputs
+    if k > 1 and desc.class_id is not None and np.any(
+            np.asarray(desc.class_id) != np.arange(desc.n_trees) % k):
+        raise ValueError("LightGBM trees feed class t % n_classes")
+    lines = ["tree", "version=v3", f"num_class={k}", f"num_tree_per_iteration={k}",
+             "label_index=0", f"max_feature_idx={desc.n_features - 1}", f"objective={objective}",
+             ""]
+    if desc.average_tree_output:
+        lines.insert(7, "average_output")
+    offs = np.asarray(desc.tree_offsets)
+
+    def fmt(v):
+        return repr(float(v))
+
+    for t in range(desc.n_trees):
+        b, e = int(offs[t]), int(offs[t + 1])
+        internal = [g for g in range(b, e) if kinds[g] != NODE_LEAF]
+        leaves = [g for g in range(b, e) if kinds[g] == NODE_LEAF]
+        ipos = {g: i for i, g in enumerate(internal)}
+        lpos = {g: i for i, g in enumerate(leaves)}
+        if kinds[b] != NODE_LEAF and ipos[b] != 0:
+            raise ValueError("the root must be the tree's first node")
+
+        def child(rel):
+            g = b + int(rel)
+            return ipos[g] if g in ipos else ~lpos[g]
+
+        lines.append(f"Tree={t}")
+        lines.append(f"num_leaves={len(leaves)}")
+        sf, th, dt, lch, rch, cb, ct = [], [], [], [], [], [0], []
+        for g in internal:
+            sf.append(int(desc.feature[g]))
+            lch.append(child(desc.left[g])); rch.append(child(desc.right[g]))
+            if kinds[g] == NODE_CATEGORICAL:
+                mine = [int(c) for c in desc.cat_values[int(desc.cat_ptr[g]):int(desc.cat_ptr[g + 1])]]
+                n_words = (max(mine) // 32 + 1) if mine else 1
+                words = [0] * n_words
+                for c in mine:
+                    words[c // 32] |= 1 << (c % 32)
+                th.append(float(len(cb) - 1))
+                ct.extend(words); cb.append(len(ct))
+                dt.append(1 | (2 << 2))
+            else:
+                th.append(float(desc.threshold[g]))
+                dt.append((int(desc.default_left[g]) << 1) | (2 << 2))  # missing type NaN
+        lines.append(f"num_cat={len(cb) - 1}")
+        if internal:
+            lines.append("split_feature=" + " ".join(map(str, sf)))
+            lines.append("threshold=" + " ".join(fmt(v) for v in th))
+            lines.append("decision_type=" + " ".join(map(str, dt)))
+            lines.append("left_child=" + " ".join(map(str, lch)))
+            lines.append("right_child=" + " ".join(map(str, rch)))
+        lines.append("leaf_value=" + " ".join(fmt(desc.leaf_value[g]) for g in leaves))
+        if len(cb) > 1:
+            lines.append("cat_boundaries=" + " ".join(map(str, cb)))
+            lines.append("cat_threshold=" + " ".join(map(str, ct)))
+        lines.append("shrinkage=1")
+        lines.append("")
+    lines.append("end of trees")
+    lines.append("")
+    return "\n".join(lines)

@@ -57,8 +57,8 @@ def load_desc(path: str) -> ForestDesc:
 def load_file(path: str, model_type: Optional[str] = None) -> ForestDesc:
     if model_type is None:
         ext = os.path.splitext(path)[1].lower()
-        model_type = {".json": "xgboost_json", ".txt": "lightgbm", ".npz": "b2fil_npz",
-                      ".model": "lightgbm"}.get(ext)
+        model_type = {".json": "xgboost_json", ".ubj": "xgboost_ubjson", ".txt": "lightgbm",
+                      ".npz": "b2fil_npz", ".model": "lightgbm"}.get(ext)
         if model_type == "xgboost_json":
             with open(path) as fh:
                 head = json.load(fh)
@@ -78,6 +78,12 @@ def load_file(path: str, model_type: Optional[str] = None) -> ForestDesc:
 
         with open(path) as fh:
             return from_xgboost_json(json.load(fh))
+    if model_type in ("xgboost_ubjson", "xgboost_ubj"):
+        from . import ubjson
+        from .xgboost_json import from_xgboost_json
+
+        with open(path, "rb") as fh:
+            return from_xgboost_json(ubjson.loads(fh.read()))
     if model_type in ("lightgbm", "lightgbm_txt"):
         from .lightgbm_txt import from_lightgbm_text
 

@@ -41,10 +41,25 @@ class ShardedForestInference:
             raise ValueError("the model must live on the first device of device_ids")
         self.model = model
         self.device_ids = list(device_ids)
+        self._lib = _lib.load()
         self._forests = [model.forest] + [model.forest.clone_to(d) for d in device_ids[1:]]
 
-    def _predict(self, shards, kind: int, chunk_size: Optional[int] = None, threshold=0.5):
-        """`shards[i]` is a 2-d torch tensor on device i holding that device's rows."""
+    def last_timing(self) -> dict:
+        """Device-side times of this thread's last sharded call (`b2fil_last_sharded_timing`):
+        the slowest device's kernels, the slowest gather copy, the host's wall time from the
+        first launch to the last device done, and whether the gather went over direct peer
+        paths."""
+        c, g, w = C.c_double(), C.c_double(), C.c_double()
+        d = C.c_int()
+        _lib.check(self._lib.b2fil_last_sharded_timing(C.byref(c), C.byref(g), C.byref(w),
+                                                       C.byref(d)))
+        return {"compute_ms": c.value, "gather_ms": g.value, "wall_ms": w.value,
+                "gather_direct": d.value}
+
+    def _predict(self, shards, kind: int, chunk_size: Optional[int] = None, threshold=0.5,
+                 preds=None):
+        """`shards[i]` is a 2-d torch tensor on device i holding that device's rows.  `preds`, if
+        given, is the output tensor on the first device (right shape and dtype, contiguous)."""
         import torch
 
         lib = _lib.load()
@@ -61,12 +76,19 @@ class ShardedForestInference:
                 raise ValueError(f"shard for device {dev} must be a CUDA tensor on that device")
             if x.ndim != 2 or x.shape[1] != nf:
                 raise ValueError(f"every shard must have shape (rows, {nf})")
-            x = x.to(tdt)
+            if x.dtype != tdt:
+                x = x.to(tdt)
             prepared.append(x if x.is_contiguous() else x.contiguous())
         rows = [int(x.shape[0]) for x in prepared]
         shape, odt = self.model._out_spec(kind, sum(rows))
         todt = {np.int32: torch.int32, np.float32: torch.float32, np.float64: torch.float64}[odt]
-        out = torch.empty(shape, dtype=todt, device=f"cuda:{self.device_ids[0]}")
+        if preds is not None:
+            out = preds
+            if (tuple(out.shape) != tuple(shape) or out.dtype != todt or not out.is_contiguous()
+                    or out.device.index != self.device_ids[0]):
+                raise ValueError("preds has the wrong shape, dtype, layout or device")
+        else:
+            out = torch.empty(shape, dtype=todt, device=f"cuda:{self.device_ids[0]}")
         for dev in self.device_ids:
             torch.cuda.synchronize(dev)  # inputs may still be in flight on the callers' streams
         handles = (C.c_void_p * n_dev)(*[f.handle for f in self._forests])
@@ -76,9 +98,9 @@ class ShardedForestInference:
                                              int(chunk_size or 0), float(threshold)))
         return out
 
-    def predict_proba(self, shards, chunk_size=None):
+    def predict_proba(self, shards, chunk_size=None, preds=None):
         kind = INFER_PROBA2 if self.model.n_outputs == 1 else INFER_DEFAULT
-        return self._predict(shards, kind, chunk_size)
+        return self._predict(shards, kind, chunk_size, preds=preds)
 
     def predict(self, shards, chunk_size=None, threshold=None):
         if not self.model.is_classifier:

@@ -84,3 +84,54 @@ def from_xgboost_json(model: dict) -> ForestDesc:
         cat_right=None, class_id=np.asarray(tree_info, np.int32) if k > 1 else None,
         average_tree_output=False, base_scores=np.full(k, base), postproc=post,
         is_classifier=is_clf, native_precision="single")
+
+
+def to_xgboost_json(desc: ForestDesc, objective: str = "reg:squarederror") -> dict:
+    """Write a forest description in the schema `from_xgboost_json` reads (test files and
+    round trips; XGBoost itself is not involved).  The description must use what the format can
+    say: `<` tests, listed categories going right, scalar leaves, no averaging."""
+    if desc.leaf_vector_len != 1 or desc.average_tree_output:
+        raise ValueError("the XGBoost schema holds scalar leaves and summed trees only")
+    if desc.op is not None and np.any(np.asarray(desc.op)[np.asarray(desc.node_kind) == NODE_NUMERICAL] != OP_LT):
+        raise ValueError("the XGBoost schema tests x < threshold only")
+    if desc.op is None and desc.op_all != OP_LT and np.any(np.asarray(desc.node_kind) == NODE_NUMERICAL):
+        raise ValueError("the XGBoost schema tests x < threshold only")
+    if desc.cat_right is not None and np.any(
+            np.asarray(desc.cat_right)[np.asarray(desc.node_kind) == NODE_CATEGORICAL] == 0):
+        raise ValueError("in the XGBoost schema listed categories go right")
+    trees = []
+    offs = np.asarray(desc.tree_offsets)
+    for t in range(desc.n_trees):
+        b, e = int(offs[t]), int(offs[t + 1])
+        lc, rc, si, sc, dfl, st = [], [], [], [], [], []
+        cats, cnodes, csegs, csizes = [], [], [], []
+        for g in range(b, e):
+            k = int(desc.node_kind[g])
+            if k == NODE_LEAF:
+                lc.append(-1); rc.append(-1); si.append(0); dfl.append(0); st.append(0)
+                sc.append(float(desc.leaf_value[g]))
+                continue
+            lc.append(int(desc.left[g])); rc.append(int(desc.right[g]))
+            si.append(int(desc.feature[g])); dfl.append(int(desc.default_left[g]))
+            if k == NODE_CATEGORICAL:
+                st.append(1); sc.append(0.0)
+                mine = [int(c) for c in desc.cat_values[int(desc.cat_ptr[g]):int(desc.cat_ptr[g + 1])]]
+                cnodes.append(g - b); csegs.append(len(cats)); csizes.append(len(mine))
+                cats.extend(mine)
+            else:
+                st.append(0); sc.append(float(desc.threshold[g]))
+        trees.append({"left_children": lc, "right_children": rc, "split_indices": si,
+                      "split_conditions": sc, "default_left": dfl, "split_type": st,
+                      "categories": cats, "categories_nodes": cnodes,
+                      "categories_segments": csegs, "categories_sizes": csizes,
+                      "tree_param": {"num_nodes": str(e - b)}})
+    k = desc.n_outputs
+    info = ([int(c) for c in desc.class_id] if desc.class_id is not None
+            else [t % k for t in range(desc.n_trees)])
+    return {"learner": {"learner_model_param": {"num_feature": str(desc.n_features),
+                                                "num_class": str(k if k > 1 else 0),
+                                                "base_score": "5E-1" if objective.startswith("binary") else "0E0"},
+                        "objective": {"name": objective},
+                        "gradient_booster": {"name": "gbtree",
+                                             "model": {"trees": trees, "tree_info": info}}},
+            "version": [2, 0, 0]}

@@ -133,8 +133,11 @@ typedef struct b2fil_create_opts {
   int32_t align_bytes; /* 0 or a power of two: pad every tree of a sparse forest to this size    */
   int32_t device_id;   /* CUDA device ordinal that will hold the forest                          */
   int32_t default_chunk_size; /* 0 = choose; else the value predict uses when given chunk_size 0 */
-  int32_t row_quantization;   /* 0 = automatic: dense forests without categorical tests predict on
-                                 16-bit per-feature ranks of the inputs (exact); 1 = never        */
+  int32_t row_quantization;   /* REQUEST: 0 = automatic (dense forests whose categorical tests, if
+                                 any, only list categories below 32 predict on 16-bit per-feature
+                                 ranks of the inputs, which is exact), 1 = never.  What the forest
+                                 actually does is reported by b2fil_info.row_quantization, where
+                                 1 means "on".                                                    */
   int32_t reserved;
 } b2fil_create_opts;
 
@@ -150,6 +153,13 @@ typedef struct b2fil_info {
   int64_t device_bytes;    /* device memory held by the forest                                   */
   int32_t default_chunk_size;
   int32_t row_quantization; /* 1: predictions run on rank-quantised rows                        */
+  int32_t peer_direct;      /* forests made by b2fil_forest_clone_to_device: 1 = the copy went
+                               over a direct peer path (NVLink / PCIe peer-to-peer), 0 = staged
+                               through host memory; -1 for forests made by b2fil_forest_create   */
+  int32_t clone_src_device; /* device the forest was replicated from, or -1                     */
+  int64_t scratch_pool_bytes; /* device memory the forest's scratch pool holds right now (grows
+                                 with the largest batch b2fil_predict has seen; never touched by
+                                 b2fil_predict_fixed_scratch)                                    */
 } b2fil_info;
 
 typedef struct b2fil_forest b2fil_forest; /* opaque */
@@ -182,10 +192,35 @@ int b2fil_forest_free(b2fil_forest* f);
  * (python/cuml/cuml/ensemble/randomforestclassifier.py:333) is info->precision. */
 int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info);
 
-/* Read the forest's device status word (synchronises with the device).  Prediction kernels bound
- * every internal wait; when a bound is hit they set the word, stop working and return.  Returns
- * B2FIL_ERR_TIMEOUT when the word is set.  No counterpart in the reference. */
+/* Read the forest's device status word.  Prediction kernels bound every internal wait; when a
+ * bound is hit they set the word, stop working and return (their outputs are then incomplete).
+ * The call waits for ALL work on the forest's device (cudaDeviceSynchronize, so non-blocking
+ * streams are covered too), reads the word, and returns B2FIL_ERR_TIMEOUT when it is set; the word
+ * is cleared by the read, so one timeout is reported once.  b2fil_predict_host and
+ * b2fil_predict_sharded check the word themselves before they return; callers of the
+ * stream-ordered b2fil_predict / b2fil_predict_fixed_scratch should poll it after they have
+ * synchronised (e.g. once per batch of requests).  No counterpart in the reference. */
 int b2fil_forest_status(const b2fil_forest* f, int32_t* status);
+
+/* Self test of the timeout reporting: enqueues, on cuda_stream of the forest's device, a one-CTA
+ * kernel whose only work is a bounded wait that nothing ends (an mbarrier that never receives
+ * its arrival).  After `tries` tries (1..4096; a try lasts at most a few microseconds) the kernel
+ * sets the forest's status word exactly like a prediction kernel whose wait ran out, and returns;
+ * nothing hangs and the context stays usable.  b2fil_forest_status must then report
+ * B2FIL_ERR_TIMEOUT once.  No counterpart in the reference. */
+int b2fil_forest_selftest_timeout(b2fil_forest* f, int tries, void* cuda_stream);
+
+/* Describe the kernels the calling thread's most recent prediction call enqueued (kernel family,
+ * template arguments, launch shape), e.g. "quantise_kernel<float> + dense_q_top_kernel<float,
+ * scalar,NT=6,DEPTH=8> R=256 G=3 S=2 K=2".  Writes a NUL-terminated string of at most
+ * buf_bytes - 1 characters and returns the full length.  No counterpart in the reference. */
+int b2fil_last_variant(char* buf, size_t buf_bytes);
+
+/* Switch peer access between two devices on, in both directions, if the hardware allows it (a
+ * per-process setting; forest replication and the sharded gather do this themselves).  Returns 1
+ * when copies between the two devices are direct, 0 when they are staged through host memory,
+ * or a negative error code.  No counterpart in the reference. */
+int b2fil_enable_peer_access(int device_a, int device_b);
 
 /* Number of prediction kernels this process has launched through the library so far. */
 int64_t b2fil_kernel_launches(void);
@@ -199,8 +234,8 @@ int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind);
  * chunk_size 0 = the forest's default.  `threshold` is the binary decision threshold of
  * B2FIL_INFER_CLASS for one-output classifiers.  Enqueues on cuda_stream (NULL = default stream)
  * of the forest's device and does not synchronise.  Two cases take stream-ordered scratch from a
- * memory pool owned by the forest (cached between calls): forests with row_quantization = 1 keep
- * the 16-bit rank image of the batch there, and small batches of dense forests (fewer 128-row
+ * memory pool owned by the forest (cached between calls): forests whose b2fil_info reports
+ * row_quantization = 1 keep the 16-bit rank image of the batch there, and small batches of dense forests (fewer 128-row
  * tiles than half the SMs) keep the partial sums of the CTAs that share the forest there.
  * Replaces forest_model.predict(...) (cpp/tests/sg/rf_test.cu:268-275). */
 int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int64_t n_rows,
@@ -213,8 +248,8 @@ int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int6
 /* Batched prediction, device buffers, for callers that must not allocate device memory while
  * they predict.  It has no counterpart in the reference.
  *
- * b2fil_predict keeps the 16-bit rank image of the batch (forests with row_quantization = 1) in
- * scratch that it takes from a CUDA memory pool.  A process whose GPU memory is handed out in
+ * b2fil_predict keeps the 16-bit rank image of the batch (forests whose b2fil_info reports
+ * row_quantization = 1) in scratch that it takes from a CUDA memory pool.  A process whose GPU memory is handed out in
  * full to its own allocator at start-up, or a serving loop that cannot afford the lock and the
  * possible failure of an allocation in the middle of a request, cannot accept that.  For them this
  * call writes the rank image into a B2FIL_FIXED_SCRATCH_BYTES array that is part of the library
@@ -230,7 +265,14 @@ int b2fil_predict(const b2fil_forest* f, int infer_kind, const void* X_dev, int6
  *    streams, two threads) race on it; issue them on one stream or serialise them yourself;
  *  - the first call on each device looks up the array's device address (with that device current)
  *    and caches it; make that first call before any stream capture is started;
- *  - forests that predict without rank scratch (sparse storage, row_quantization = 0) are
+ *  - "allocates nothing" holds from the second call on.  The first call on a device for a given
+ *    forest shape and infer_kind makes the CUDA runtime load the kernels it needs (with lazy module
+ *    loading that is when the driver reserves the array itself and the kernels' code) and raises
+ *    their shared-memory limit.  A process that wants to hand ALL remaining GPU memory to its own
+ *    allocator must make one warm-up call per device and per (forest shape, infer_kind) BEFORE it
+ *    does so; after that warm-up a call changes neither the free device memory nor the forest's
+ *    pool;
+ *  - forests that predict without rank scratch (sparse storage, b2fil_info.row_quantization = 0) are
  *    forwarded to the ordinary kernels with the forest-splitting of small batches switched off,
  *    so nothing is allocated for them either. */
 int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const void* X_dev,
@@ -239,8 +281,9 @@ int b2fil_predict_fixed_scratch(const b2fil_forest* f, int infer_kind, const voi
 
 /* Batched prediction, host buffers: copies row blocks to the device, predicts and copies results
  * back, with copies and kernels overlapped on two internal streams.  Pinned host memory gives
- * full copy bandwidth; pageable memory works.  Synchronous: returns when out_host is complete.
- * This is the call a host-array user of `.predict_proba(X)` reaches. */
+ * full copy bandwidth; pageable memory works.  Synchronous: returns when out_host is complete -
+ * also when it returns an error, every copy that was already enqueued has finished, so the
+ * caller may free its buffers.  This is the call a host-array user of `.predict_proba(X)` reaches. */
 int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int64_t n_rows,
                        int64_t row_stride, void* out_host, int chunk_size, double threshold);
 
@@ -248,12 +291,24 @@ int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int6
  * on device i of the set, rows are split into contiguous shards, shard i is predicted on its
  * device, and results are gathered into out (a device buffer on forests[0]'s device, by peer
  * copies; no collective library).  X_shards[i] is the device pointer of shard i's first row on
- * device i; shard_rows[i] its row count.  Synchronous.
+ * device i; shard_rows[i] its row count.  Synchronous: on return, with or without an error,
+ * nothing the call enqueued is still running.  Peer access between every device and forests[0]'s
+ * device is switched on at the first use, so that the gather crosses NVLink instead of host
+ * memory where the hardware allows it.  Callers may pass the same forests in any order from
+ * several threads (their locks are taken in a fixed order).
  * (python/cuml/cuml/dask/ensemble/base.py:210-218, dask/common/base.py:276-316: model replicated,
  *  row partitions predicted where they live, results concatenated by rows.) */
 int b2fil_predict_sharded(b2fil_forest* const* forests, int n_devices, int infer_kind,
                           const void* const* X_shards, const int64_t* shard_rows,
                           int64_t row_stride, void* out_dev0, int chunk_size, double threshold);
+
+/* Device-side times of the calling thread's last b2fil_predict_sharded call, from CUDA events on
+ * each device's stream: compute_ms = the slowest device's prediction kernels, gather_ms = the
+ * slowest peer copy into forests[0]'s device, wall_ms = host clock from the first launch to the
+ * last device done, gather_direct = 1 when every gather copy used a direct peer path.  Any
+ * pointer may be NULL.  No counterpart in the reference. */
+int b2fil_last_sharded_timing(double* compute_ms, double* gather_ms, double* wall_ms,
+                              int* gather_direct);
 
 #ifdef __cplusplus
 }

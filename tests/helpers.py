@@ -193,3 +193,32 @@ def load_golden(name):
     fields["native_precision"] = str(fields["native_precision"])
     exp = {k: v for k, v in d.items() if not k.startswith("desc_") and k != "X"}
     return ForestDesc(**fields), d["X"], exp
+
+
+def xgboost_style_desc(seed, n_trees=24, n_features=9, max_depth=6, n_classes=1,
+                       categorical=True):
+    """Random ragged forest limited to what an XGBoost model file can say: `<` tests, listed
+    categories go right, float32 thresholds and leaves, class of a tree in `class_id`."""
+    d = random_forest_desc(seed, n_trees=n_trees, n_features=n_features, max_depth=max_depth,
+                           n_outputs=n_classes, categorical=categorical, op=OP_LT,
+                           postproc="softmax" if n_classes > 1 else "sigmoid")
+    if d.cat_right is not None:
+        d.cat_right = np.ones_like(d.cat_right)
+    d.leaf_value = d.leaf_value.astype(np.float32).astype(np.float64)
+    d.sigmoid_alpha = 1.0  # the format has no slope parameter
+    return d
+
+
+def lightgbm_style_desc(seed, n_trees=24, n_features=9, max_depth=6, n_classes=1,
+                        categorical=True):
+    """Random ragged forest limited to what a LightGBM text model can say: `<=` tests, listed
+    categories go left and missing values right at categorical nodes, tree t feeds class t % k."""
+    d = random_forest_desc(seed, n_trees=n_trees, n_features=n_features, max_depth=max_depth,
+                           n_outputs=n_classes, categorical=categorical, op=OP_LE,
+                           postproc="softmax" if n_classes > 1 else "sigmoid")
+    if d.cat_right is not None:
+        d.cat_right = np.zeros_like(d.cat_right)
+        d.default_left = np.where(d.node_kind == NODE_CATEGORICAL, 0, d.default_left).astype(np.uint8)
+    if n_classes > 1:
+        d.class_id = (np.arange(d.n_trees) % n_classes).astype(np.int32)
+    return d

@@ -392,12 +392,15 @@ def test_pickle_round_trip():
     assert np.array_equal(a, fi2.predict_proba(X).cpu().numpy())
 
 
-def test_sharded_prediction_over_available_gpus():
-    """Model replicated, rows sharded, results gathered on the first device by peer copies."""
+def test_sharded_prediction_over_available_gpus(lib):
+    """Model replicated, rows sharded, results gathered on the first device by peer copies: on
+    every device the box has (one process drives them all)."""
+    import ctypes as C
+
     torch = _torch()
     from cuml_b200.fil.multi_gpu import ShardedForestInference
 
-    n_dev = min(torch.cuda.device_count(), 4)
+    n_dev = min(torch.cuda.device_count(), 8)
     desc = random_forest_desc(80, n_trees=31, n_features=10, max_depth=6, n_outputs=3,
                               postproc="softmax")
     fi = ForestInference.load_from_treelite_model(desc, device_id=0)
@@ -412,6 +415,128 @@ def test_sharded_prediction_over_available_gpus():
     assert np.array_equal(ids.astype(np.uint32), oracle.predict(desc, X, INFER_LEAF_ID, "single"))
     cls = sh.predict(shards).cpu().numpy()
     assert np.array_equal(cls, np.argmax(proba, axis=1))
+    t = sh.last_timing()
+    assert t["wall_ms"] > 0 and t["compute_ms"] > 0 and t["gather_direct"] in (0, 1)
+    for f in sh._forests[1:]:
+        assert f.info.clone_src_device == 0 and f.info.peer_direct in (0, 1)
+    assert fi.forest.info.peer_direct == -1
+    # empty shards and a quantised forest large enough for the regular path on every device
+    big = synthetic_complete_forest(64, 6, 16, seed=3)
+    fb = ForestInference.load_from_treelite_model(big, device_id=0)
+    shb = ShardedForestInference(fb, list(range(n_dev)))
+    Xb = np.random.default_rng(4).standard_normal((24_000 * n_dev + 17, 16)).astype(np.float32)
+    got = shb.predict_proba(shb.scatter(Xb)).cpu().numpy()
+    np.testing.assert_allclose(got, oracle.predict(big, Xb, INFER_PROBA2, "single"),
+                               rtol=1e-5, atol=1e-6)
+    parts = shb.scatter(Xb[:3])  # fewer rows than devices: some shards are empty
+    got = shb.apply(parts).cpu().numpy()
+    assert np.array_equal(got.astype(np.uint32), oracle.predict(big, Xb[:3], INFER_LEAF_ID, "single"))
+    if n_dev > 1:
+        assert lib.b2fil_enable_peer_access(0, 1) in (0, 1)
+    assert lib.b2fil_enable_peer_access(0, 99) == -1
+
+
+def test_sharded_prediction_from_two_threads_in_opposite_device_order():
+    """Two host threads that hand the same forests to the sharded call in opposite orders must
+    both finish (the forests' locks are taken in a fixed order)."""
+    import threading
+
+    torch = _torch()
+    from cuml_b200.fil.multi_gpu import ShardedForestInference
+
+    n_dev = min(torch.cuda.device_count(), 8)
+    desc = random_forest_desc(81, n_trees=12, n_features=6, max_depth=5)
+    fi = ForestInference.load_from_treelite_model(desc, device_id=0)
+    sh = ShardedForestInference(fi, list(range(n_dev)))
+    X = random_rows(3, 4000, 6, np.float32)
+    want = oracle.predict(desc, X, INFER_LEAF_ID, "single")
+    import ctypes as C
+
+    lib = sh._lib
+    order = list(range(n_dev))
+    results, errors = {}, []
+
+    def call(devs):
+        """The C-ABI call with the forests listed in the order `devs`; the output lives on the
+        first listed device and holds the shards in that order."""
+        parts = {d: p for d, p in zip(order, sh.scatter(X))}
+        for d in order:
+            torch.cuda.synchronize(d)
+        rows = [int(parts[d].shape[0]) for d in devs]
+        out = torch.empty((sum(rows), desc.n_trees), dtype=torch.int32, device=f"cuda:{devs[0]}")
+        handles = (C.c_void_p * n_dev)(*[sh._forests[d].handle for d in devs])
+        xs = (C.c_void_p * n_dev)(*[parts[d].data_ptr() for d in devs])
+        counts = (C.c_int64 * n_dev)(*rows)
+        rc = lib.b2fil_predict_sharded(handles, n_dev, INFER_LEAF_ID, xs, counts, 6,
+                                       out.data_ptr(), 0, 0.5)
+        assert rc == 0, lib.b2fil_last_error()
+        pieces = np.split(out.cpu().numpy(), np.cumsum(rows)[:-1])
+        return np.concatenate([pieces[devs.index(d)] for d in order])
+
+    def work(name, devs):
+        try:
+            for _ in range(20):
+                results[name] = call(devs)
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    ts = [threading.Thread(target=work, args=("a", order)),
+          threading.Thread(target=work, args=("b", order[::-1]))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(timeout=120)
+    assert not any(t.is_alive() for t in ts), "sharded calls blocked each other"
+    assert not errors, errors
+    for name in ("a", "b"):
+        assert np.array_equal(results[name].astype(np.uint32), want)
+
+
+def test_bounded_wait_runs_out_and_is_reported_once(lib):
+    """A wait inside a kernel that nothing ends gives up after its limit, the kernel returns, the
+    forest's status word says so, the host call reports B2FIL_ERR_TIMEOUT once, and the device
+    keeps working.  (The wait is on an mbarrier that never receives its arrival; the limit is 16
+    tries of a few microseconds, so nothing hangs.)"""
+    import ctypes as C
+
+    torch = _torch()
+    desc = random_forest_desc(62, n_trees=5)
+    fi = ForestInference.load_from_treelite_model(desc)
+    X = _dev(random_rows(1, 300, desc.n_features), "single")
+    before = fi.apply(X).cpu().numpy()
+    st = C.c_int32(-1)
+    assert lib.b2fil_forest_status(fi.forest.handle, C.byref(st)) == 0 and st.value == 0
+    side = torch.cuda.Stream()  # a non-blocking stream: the status call must wait for it too
+    assert lib.b2fil_forest_selftest_timeout(fi.forest.handle, 16, side.cuda_stream) == 0
+    rc = lib.b2fil_forest_status(fi.forest.handle, C.byref(st))
+    assert rc == -7 and st.value == 5
+    assert b"ran out" in lib.b2fil_last_error()
+    with pytest.raises(Exception) as ei:
+        lib.b2fil_forest_selftest_timeout(fi.forest.handle, 16, None)
+        fi.check_status()
+    assert getattr(ei.value, "code", None) == -7
+    # reported once: the word is clear again and predictions are unaffected
+    assert lib.b2fil_forest_status(fi.forest.handle, C.byref(st)) == 0 and st.value == 0
+    assert np.array_equal(fi.apply(X).cpu().numpy(), before)
+    assert lib.b2fil_forest_selftest_timeout(fi.forest.handle, 0, None) == -1
+    assert lib.b2fil_forest_selftest_timeout(None, 4, None) == -1
+
+
+def test_last_variant_names_the_kernels(lib):
+    from cuml_b200.fil import _lib
+
+    desc = synthetic_complete_forest(100, 8, 64, seed=2)
+    fi = ForestInference.load_from_treelite_model(desc)
+    rng = np.random.default_rng(0)
+    fi.predict_proba(_dev(rng.standard_normal((30_000, 64)).astype(np.float32), "single"))
+    v = _lib.last_variant()
+    assert v.startswith("quantise_kernel<float> + dense_q_top_kernel<float,scalar,NT=6,DEPTH=8>")
+    fi.predict_proba(_dev(rng.standard_normal((64, 64)).astype(np.float32), "single"))
+    v = _lib.last_variant()
+    assert v.startswith("dense_kernel<float,scalar") and "forest_splits=" in v
+    sp = ForestInference.load_from_treelite_model(desc, storage="sparse")
+    sp.apply(_dev(rng.standard_normal((500, 64)).astype(np.float32), "single"))
+    assert _lib.last_variant().startswith("sparse_kernel<float,node8,leaf_id")
 
 
 def test_quantised_categorical_edge_values():
@@ -450,6 +575,57 @@ def test_load_from_model_files(tmp_path):
     for path, kind in ((p1, None), (p2, "treelite_json"), (p2, None)):
         fi = ForestInference.load(str(path), model_type=kind, is_classifier=True)
         np.testing.assert_allclose(fi.predict_proba(X), want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("fmt", ["xgboost_json", "xgboost_ubjson", "lightgbm"])
+@pytest.mark.parametrize("n_classes", [1, 4])
+def test_model_files_of_other_libraries_on_the_gpu(tmp_path, fmt, n_classes):
+    """Multi-tree, multi-class model files with categorical tests and missing values, written in
+    the XGBoost JSON / UBJSON and LightGBM text formats (by this library's own writers: neither
+    package is installed), loaded through ForestInference.load(path): scores and leaf ids of the
+    GPU against the oracle on the same loaded description, in both storages."""
+    import json
+
+    from cuml_b200.fil import ubjson
+    from cuml_b200.fil.lightgbm_txt import to_lightgbm_text
+    from cuml_b200.fil.loaders import load_file
+    from cuml_b200.fil.xgboost_json import to_xgboost_json
+    from tests.helpers import lightgbm_style_desc, xgboost_style_desc
+
+    if fmt == "lightgbm":
+        src = lightgbm_style_desc(30 + n_classes, n_trees=40, n_features=11, max_depth=7,
+                                  n_classes=n_classes)
+        path = tmp_path / "model.txt"
+        path.write_text(to_lightgbm_text(src, f"multiclass num_class:{n_classes}"
+                                         if n_classes > 1 else "binary sigmoid:1.5"))
+        precision = "double"
+    else:
+        src = xgboost_style_desc(20 + n_classes, n_trees=40, n_features=11, max_depth=7,
+                                 n_classes=n_classes)
+        obj = to_xgboost_json(src, "multi:softprob" if n_classes > 1 else "binary:logistic")
+        if fmt == "xgboost_json":
+            path = tmp_path / "model.json"
+            path.write_text(json.dumps(obj))
+        else:
+            path = tmp_path / "model.ubj"
+            path.write_bytes(ubjson.dumps(obj))
+        precision = "single"
+    loaded = load_file(str(path))
+    dt = np.float32 if precision == "single" else np.float64
+    X = random_rows(13, 3000, 11, dt, nan_frac=0.08, categories=22)
+    kind = INFER_PROBA2 if n_classes == 1 else INFER_DEFAULT
+    want = oracle.predict(loaded, X, kind, precision)
+    # the file says what the source forest says
+    np.testing.assert_allclose(want, oracle.predict(src, X, kind, precision), rtol=1e-6, atol=1e-7)
+    want_ids = oracle.predict(loaded, X, INFER_LEAF_ID, precision)
+    for storage in ("dense", "sparse"):
+        fi = ForestInference.load(str(path), precision=precision, storage=storage)
+        assert fi.is_classifier and fi.n_trees == 40
+        Xd = _dev(X, precision)
+        np.testing.assert_allclose(fi.predict_proba(Xd).cpu().numpy(), want, **_tol(loaded, precision))
+        assert np.array_equal(fi.apply(Xd).cpu().numpy().astype(np.uint32), want_ids)
+        # chunk_size asks for the regular (quantised, when it exists) path on this small batch
+        assert np.array_equal(fi.apply(Xd, chunk_size=4).cpu().numpy().astype(np.uint32), want_ids)
 
 
 def test_optimize_picks_a_chunk_size_and_keeps_results():

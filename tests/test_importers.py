@@ -169,3 +169,59 @@ def test_concatenate_forests():
     ids = oracle.predict(c, X, INFER_LEAF_ID, "double")
     assert np.array_equal(ids[:, :4], oracle.predict(a, X, INFER_LEAF_ID, "double"))
     assert np.array_equal(ids[:, 4:], oracle.predict(b, X, INFER_LEAF_ID, "double"))
+
+
+def test_ubjson_round_trip_and_hand_made_bytes():
+    from cuml_b200.fil import ubjson
+
+    obj = {"a": [1, 2, 300, -70000], "b": [0.5, -1.25, 3.0], "c": "text", "d": None, "e": True,
+           "f": {"g": [1, "x", 2.5, [False]], "h": 2 ** 40, "i": []}, "j": [2 ** 35, 1]}
+    assert ubjson.loads(ubjson.dumps(obj)) == obj
+    # bytes written by hand from the specification: {"k": [$U#i 3: 1 2 3], "s": "hi", "n": no-op,
+    # "v": 2.5 (float32), "w": int16 -2}
+    raw = (b"{" + b"i\x01k" + b"[$U#i\x03\x01\x02\x03" + b"i\x01s" + b"S" + b"i\x02hi" +
+           b"i\x01v" + b"N" + b"d" + bytes.fromhex("40200000") + b"i\x01w" + b"I\xff\xfe" + b"}")
+    assert ubjson.loads(raw) == {"k": [1, 2, 3], "s": "hi", "v": 2.5, "w": -2}
+    # counted object with a common value type
+    raw = b"{$i#i\x02" + b"i\x01a\x05" + b"i\x01b\xfb"
+    assert ubjson.loads(raw) == {"a": 5, "b": -5}
+    with pytest.raises(ValueError):
+        ubjson.loads(b"[$i#i\x05\x01")  # truncated
+
+
+@pytest.mark.parametrize("n_classes", [1, 3])
+def test_xgboost_json_and_ubjson_files_round_trip(tmp_path, n_classes):
+    from cuml_b200.fil import ubjson
+    from cuml_b200.fil.xgboost_json import to_xgboost_json
+    from tests.helpers import xgboost_style_desc
+
+    desc = xgboost_style_desc(7 + n_classes, n_classes=n_classes)
+    obj = to_xgboost_json(desc, "multi:softprob" if n_classes > 1 else "binary:logistic")
+    pj, pu = tmp_path / "m.json", tmp_path / "m.ubj"
+    pj.write_text(json.dumps(obj))
+    pu.write_bytes(ubjson.dumps(obj))
+    X = random_rows(5, 300, desc.n_features, np.float32, categories=22)
+    want = oracle.predict(desc, X, INFER_DEFAULT, "single")
+    want_ids = oracle.predict(desc, X, INFER_LEAF_ID, "single")
+    for path in (pj, pu):
+        back = load_file(str(path))
+        assert back.n_trees == desc.n_trees and back.n_outputs == desc.n_outputs
+        np.testing.assert_allclose(oracle.predict(back, X, INFER_DEFAULT, "single"), want,
+                                   rtol=1e-6, atol=1e-7)
+        assert np.array_equal(oracle.predict(back, X, INFER_LEAF_ID, "single"), want_ids)
+
+
+@pytest.mark.parametrize("n_classes", [1, 3])
+def test_lightgbm_text_file_round_trip(tmp_path, n_classes):
+    from cuml_b200.fil.lightgbm_txt import to_lightgbm_text
+    from tests.helpers import lightgbm_style_desc
+
+    desc = lightgbm_style_desc(11 + n_classes, n_classes=n_classes)
+    p = tmp_path / "m.txt"
+    p.write_text(to_lightgbm_text(desc, f"multiclass num_class:{n_classes}" if n_classes > 1
+                                  else "binary sigmoid:1.5"))
+    back = load_file(str(p))
+    X = random_rows(6, 300, desc.n_features, np.float64, categories=22)
+    np.testing.assert_allclose(oracle.predict(back, X, INFER_DEFAULT, "double"),
+                               oracle.predict(desc, X, INFER_DEFAULT, "double"),
+                               rtol=1e-12, atol=1e-13)
