@@ -352,6 +352,19 @@ int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* 
     if ((rc = upload(f.get(), pf.out_scale, offsetof(ForestView, out_scale))) != B2FIL_OK)
       return rc;
     if ((rc = upload(f.get(), pf.out_bias, offsetof(ForestView, out_bias))) != B2FIL_OK) return rc;
+    if (pf.view.c_enabled) {
+      if ((rc = upload(f.get(), pf.c_nodes, offsetof(ForestView, c_nodes))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.c_leaves_before, offsetof(ForestView, c_leaves_before))) != B2FIL_OK)
+        return rc;
+      if ((rc = upload(f.get(), pf.c_exact, offsetof(ForestView, c_exact))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.c_leaf_payload, offsetof(ForestView, c_leaf_payload))) != B2FIL_OK)
+        return rc;
+      if ((rc = upload(f.get(), pf.c_leaf_ids, offsetof(ForestView, c_leaf_ids))) != B2FIL_OK)
+        return rc;
+      if ((rc = upload(f.get(), pf.c_top, offsetof(ForestView, c_top))) != B2FIL_OK) return rc;
+      if ((rc = upload(f.get(), pf.c_top_src, offsetof(ForestView, c_top_src))) != B2FIL_OK)
+        return rc;
+    }
     if (pf.view.q_enabled) {
       if ((rc = upload(f.get(), pf.q_nodes, offsetof(ForestView, q_nodes))) != B2FIL_OK) return rc;
       if ((rc = upload(f.get(), pf.q_nodes_ids, offsetof(ForestView, q_nodes_ids))) != B2FIL_OK)
@@ -446,6 +459,8 @@ int b2fil_forest_info(const b2fil_forest* f, b2fil_info* info)
   info->device_bytes       = f->device_bytes;
   info->default_chunk_size = f->default_chunk;
   info->row_quantization   = f->view.q_enabled;
+  info->compact_image      = f->view.c_enabled;
+  info->top_levels         = f->view.c_enabled ? f->view.c_top_levels : 0;
   info->peer_direct        = f->clone_direct;
   info->clone_src_device   = f->clone_src_device;
   if (f->pool) {

@@ -18,6 +18,7 @@
 // thresholds to the next representable value where needed, so the kernels evaluate one operator.
 #pragma once
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <string>
@@ -136,6 +137,59 @@ constexpr uint32_t Q_MAX_RANK_FIELD = 0x3FFFu;  // j of a test that every code p
 // parameter and reads them through the constant cache instead of shared memory.
 constexpr int kQTopTrees = 2048;
 
+// ---- compact image of a sparse forest -----------------------------------------------------------
+// Deep, ragged forests are bound by the chain of dependent node fetches from L2 / HBM.  Sparse
+// forests whose fields fit therefore carry a second image built for exactly that:
+//  * internal nodes only, 8 bytes each {value, meta}, in depth-first order per tree (the left
+//    child of node k is node k + 1), so the node array is half the size of an array that also
+//    holds the leaves and a quarter of the 16-byte fp64 array: it stays in L2;
+//  * leaves live in their own arrays (payload, id), numbered in the same depth-first order.  A
+//    walk carries the pair (k, L) = (internal node, number of leaves that precede it); with
+//    `off` = 1 + internal nodes of the left subtree,
+//        left : k + 1,   L          right : k + off, L + off
+//    (a subtree with m internal nodes has m + 1 leaves), and two flags in the node say when the
+//    child reached is a leaf, whose number is then L (left) or L + off (right);
+//  * meta = default-left << 31 | categorical << 30 | left-is-leaf << 29 | right-is-leaf << 28 |
+//    off << feat_bits | feature;
+//  * fp64 forests keep `value` = the largest float <= threshold.  x < float(value) proves
+//    x < threshold; otherwise the answer is only in doubt when x rounded down to float equals
+//    value, and then the exact threshold is read from `c_exact` (one in 2^24 visits on
+//    continuous data), so the 8-byte node decides every test exactly;
+//  * the top `c_top_levels` levels of every tree are also stored as a complete heap
+//    [2^T nodes {value, feature | flags}][2^T exits], which the kernel streams through shared
+//    memory: a walk starts with T steps that cost no global fetch and leaves the heap through
+//    an exit = internal node to continue at, or leaf reached (bit 31).
+constexpr uint32_t CMETA_LEFT_LEAF  = 0x20000000u;
+constexpr uint32_t CMETA_RIGHT_LEAF = 0x10000000u;
+constexpr uint32_t CMETA_LOW28      = 0x0FFFFFFFu;
+constexpr uint32_t C_EXIT_LEAF      = 0x80000000u;
+constexpr uint32_t C_NO_NODE        = 0xFFFFFFFFu;
+constexpr int kCMaxTopLevels        = 10;
+struct CompactNode {  // 8 bytes
+  uint32_t value;     // float threshold bits (fp64 forests: rounded down) | bitset | pool offset
+  uint32_t meta;
+};
+// Levels of every tree that go into the heap: as many as leave room, next to a row tile, for the
+// heaps of sixteen trees in the 227 KiB of shared memory of one SM (0: no compact image).
+inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs, int max_depth)
+{
+  const size_t budget = 218 * 1024;
+  size_t rest         = 0;
+  for (int R = 128; R >= 32; R /= 2) {
+    const size_t tile = static_cast<size_t>(n_features) * (R + 1) * elem_bytes;
+    const size_t acc  = static_cast<size_t>(8) * n_outputs * R * elem_bytes;
+    if (tile + acc + 16 * 24 <= budget) {
+      rest = budget - tile - acc;
+      break;
+    }
+  }
+  if (rest == 0) return 0;
+  int T = kCMaxTopLevels;
+  while (T > 1 && (static_cast<size_t>(12) << T) * 16 > rest) --T;
+  if ((static_cast<size_t>(12) << T) * 16 > rest) return 0;
+  return std::max(1, std::min(T, max_depth));
+}
+
 enum NodeFormat : int32_t {
   FMT_DENSE_F   = 0,
   FMT_DENSE_D   = 1,
@@ -183,6 +237,19 @@ struct ForestView {
   int64_t q_max_blob_bytes;     // largest group blob
   const unsigned char* q_blob;  // group blobs
   const QGroup* q_groups;       // [q_n_groups]
+  // compact image of a sparse forest (c_enabled != 0), see above
+  int32_t c_enabled;
+  int32_t c_top_levels;         // T
+  int32_t c_feat_bits;
+  int32_t c_bottom_steps;       // most steps a walk takes below the heap
+  int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 12
+  const CompactNode* c_nodes;   // [n_internal]
+  const uint32_t* c_leaves_before;  // [n_internal] L of every internal node (forest-wide leaf numbers)
+  const double* c_exact;        // [n_internal] exact thresholds (fp64 forests), else null
+  const void* c_leaf_payload;   // [n_leaves] scalar in the forest precision or vector index
+  const uint32_t* c_leaf_ids;   // [n_leaves] id of the leaf in the imported model
+  const unsigned char* c_top;   // [n_trees] heaps
+  const uint32_t* c_top_src;    // [n_trees << T] internal node behind every heap node (fp64), C_NO_NODE = padding
 };
 
 // Host-side result of packing, before upload.
@@ -211,6 +278,13 @@ struct PackedForest {
   std::vector<QFeature> q_feats;
   std::vector<QGroup> q_groups;
   std::vector<uint8_t> q_blob;
+  std::vector<uint32_t> c_nodes;          // two words per internal node
+  std::vector<uint32_t> c_leaves_before;
+  std::vector<double> c_exact;
+  std::vector<uint8_t> c_leaf_payload;
+  std::vector<uint32_t> c_leaf_ids;
+  std::vector<uint8_t> c_top;
+  std::vector<uint32_t> c_top_src;
 };
 
 // Bucket of a value in a feature's table; the same expression runs on the device

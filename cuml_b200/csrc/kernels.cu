@@ -34,7 +34,7 @@ struct LaunchRecord {
   const char* prepass = nullptr;  // kernel that ran before the traversal, or null
   const char* kernel  = nullptr;  // traversal kernel family
   const char* real    = "";       // float / double
-  int mode = 0, nt = 0, depth = -1, cat = -1, fmt = -1;
+  int mode = 0, nt = 0, depth = -1, cat = -1, fmt = -1, top = -1;
   int R = 0, G = 0, S = 0, K = 0, splits = 1;
 };
 thread_local LaunchRecord g_last_launch;
@@ -1169,6 +1169,22 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
     }
     if (partial) cudaFreeAsync(partial, stream);
     if (launches && n_splits > 1 && reduce) ++*launches;
+  } else if (CompactCfg cc; compact_config(f, reduce, pick_rows_per_tile(p.n_rows, chunk_size, sm_count),
+                                          p.n_rows, sm_count, cc)) {
+    // deep / ragged forests with a compact image: heaps of the top levels through shared memory,
+    // 8-byte internal nodes below
+    LaunchRecord& rec = g_last_launch;
+    rec               = LaunchRecord{};
+    rec.kernel        = "sparse_compact_kernel";
+    rec.real          = f.format == FMT_SPARSE_16D ? "double" : "float";
+    rec.mode          = mode;
+    rec.nt            = kCompactTreesInFlight;
+    rec.cat           = f.has_categorical ? 1 : 0;
+    rec.top           = f.c_top_levels;
+    rec.R             = cc.rows_per_tile;
+    rec.G             = cc.tree_groups;
+    rec.S             = cc.stages;
+    rc = launch_sparse_compact(p, mode, cc, stream, err);
   } else {
     const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
     int R           = pick_rows_per_tile(p.n_rows, chunk_size, sm_count);
@@ -1333,6 +1349,7 @@ std::string last_launch_variant()
   s += std::string(",") + mode_name(r.mode) + ",NT=" + std::to_string(r.nt);
   if (r.depth >= 0) s += ",DEPTH=" + (r.depth ? std::to_string(r.depth) : std::string("runtime"));
   if (r.cat >= 0) s += r.cat ? ",CAT" : "";
+  if (r.top >= 0) s += ",TOP=" + std::to_string(r.top);
   s += "> R=" + std::to_string(r.R) + " G=" + std::to_string(r.G);
   if (r.S) s += " S=" + std::to_string(r.S);
   if (r.K) s += " K=" + std::to_string(r.K);

@@ -36,4 +36,21 @@ int launch_q_cat(const QLaunch& L, int mode, bool f64, std::string& err);
 // Everything else: generic depth, every precision and output mode; 1, 2 or 4 trees in flight.
 int launch_q_generic(const QLaunch& L, int mode, bool f64, std::string& err);
 
+// Sparse forests with a compact image (kernels_sparse_c.cu).
+constexpr int kCompactTreesInFlight = 4;
+struct CompactCfg {
+  int rows_per_tile;  // R
+  int tree_groups;    // G
+  int stages;         // S: depth of the ring of heap batches
+  size_t smem_bytes;
+  int threads;
+  int grid;
+};
+// Launch shape for `n_rows` rows starting from tiles of `rows_per_tile`; false when the forest has
+// no compact image or no shape fits shared memory (the plain sparse kernel runs then).
+bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t n_rows,
+                    int sm_count, CompactCfg& cfg);
+int launch_sparse_compact(const PredictParams& p, int mode, const CompactCfg& c,
+                          cudaStream_t stream, std::string& err);
+
 }  // namespace b2fil

@@ -779,7 +779,190 @@ struct Packer {
     out.storage          = B2FIL_STORAGE_SPARSE;
     out.node_bytes       = static_cast<int32_t>(nb);
     out.n_nodes_packed   = n_packed;
+    if (o.compact_image == 0) build_compact(pos, nb, format);
     return B2FIL_OK;
+  }
+
+  // Largest float that is <= t (t itself when it is a float).
+  static float round_down_to_float(double t)
+  {
+    float f = static_cast<float>(t);
+    if (static_cast<double>(f) > t) f = std::nextafter(f, -std::numeric_limits<float>::infinity());
+    return f;
+  }
+
+  // Second image of a sparse forest (see forest.hpp): internal nodes only, depth first, 8 bytes
+  // each; leaves apart; the top levels of every tree as a heap.  Values and payloads are taken
+  // from the primary image, so both images agree bit for bit.  Leaves the image out (and the
+  // view's c_enabled at 0) when a field does not fit.
+  void build_compact(const std::vector<uint32_t>& pos, size_t nb, int format)
+  {
+    const bool sp    = precision == B2FIL_F32;
+    const int nt     = d.n_trees;
+    const int es     = sp ? 4 : 8;
+    const int fb     = bits_for(static_cast<uint32_t>(d.n_features - 1));
+    const int maxd   = *std::max_element(tree_depth.begin(), tree_depth.end());
+    const int T      = compact_pick_top_levels(es, d.n_features, d.n_outputs, maxd);
+    if (T < 1 || fb >= 28) return;
+    auto primary_value = [&](int64_t g) -> uint64_t {
+      const uint8_t* at = out.nodes.data() + static_cast<size_t>(pos[g]) * nb;
+      if (format == FMT_SPARSE_16D) {
+        uint64_t v;
+        std::memcpy(&v, at, 8);
+        return v;
+      }
+      uint32_t v;
+      std::memcpy(&v, at, 4);
+      return v;
+    };
+    auto primary_meta = [&](int64_t g) -> uint32_t {
+      uint32_t m;
+      std::memcpy(&m, out.nodes.data() + static_cast<size_t>(pos[g]) * nb + (format == FMT_SPARSE_16D ? 8 : 4), 4);
+      return m;
+    };
+    // value word of the compact node of test g
+    auto compact_value = [&](int64_t g, bool is_cat) -> uint32_t {
+      const uint64_t v = primary_value(g);
+      if (is_cat || sp) return static_cast<uint32_t>(v);
+      double thr;
+      std::memcpy(&thr, &v, 8);
+      const float lo = round_down_to_float(thr);
+      uint32_t bits;
+      std::memcpy(&bits, &lo, 4);
+      return bits;
+    };
+
+    std::vector<uint32_t> cn;      // {value, meta without the offset field} per internal node
+    std::vector<uint32_t> coff;    // offset field per internal node
+    std::vector<uint32_t>& lb = out.c_leaves_before;
+    std::vector<double>& ex   = out.c_exact;
+    std::vector<uint32_t> number;  // per node of the current tree: its internal or leaf number
+    struct Frame {
+      int32_t rel;
+      int64_t parent;   // forest-wide internal number of the parent, -1 for the root
+      bool is_right;
+    };
+    std::vector<Frame> stack;
+    std::vector<int32_t> heap;
+    const size_t heap_n    = size_t(1) << T;
+    const size_t top_bytes = heap_n * 12;
+    out.c_top.assign(static_cast<size_t>(nt) * top_bytes, 0);
+    if (!sp) out.c_top_src.assign(static_cast<size_t>(nt) * heap_n, C_NO_NODE);
+    uint32_t max_off = 0;
+    uint64_t n_leaf  = 0;
+    for (int p = 0; p < nt; ++p) {
+      const int t        = out.tree_orig[p];
+      const int64_t base = d.tree_offsets[t];
+      const int64_t n    = d.tree_offsets[t + 1] - base;
+      number.assign(static_cast<size_t>(n), 0);
+      stack.clear();
+      stack.push_back({0, -1, false});
+      while (!stack.empty()) {
+        const Frame fr = stack.back();
+        stack.pop_back();
+        const int64_t g = base + fr.rel;
+        const uint64_t n_int = cn.size() / 2;
+        if (fr.is_right) {
+          // everything between the parent and here is the parent's left subtree
+          const uint64_t off = n_int - static_cast<uint64_t>(fr.parent);
+          coff[static_cast<size_t>(fr.parent)] = static_cast<uint32_t>(off);
+          max_off = std::max<uint64_t>(max_off, off);
+        }
+        if (d.node_kind[g] == B2FIL_NODE_LEAF) {
+          number[fr.rel] = static_cast<uint32_t>(n_leaf++);
+          const uint64_t pay = primary_value(g);
+          const size_t at    = out.c_leaf_payload.size();
+          out.c_leaf_payload.resize(at + es);
+          if (sp) {
+            const uint32_t v = static_cast<uint32_t>(pay);
+            std::memcpy(out.c_leaf_payload.data() + at, &v, 4);
+          } else {
+            std::memcpy(out.c_leaf_payload.data() + at, &pay, 8);
+          }
+          out.c_leaf_ids.push_back(static_cast<uint32_t>(fr.rel));
+          if (fr.parent >= 0)
+            cn[static_cast<size_t>(fr.parent) * 2 + 1] |= fr.is_right ? CMETA_RIGHT_LEAF : CMETA_LEFT_LEAF;
+          continue;
+        }
+        const Test ts = normalise(d, g, precision);
+        number[fr.rel] = static_cast<uint32_t>(n_int);
+        uint32_t meta  = static_cast<uint32_t>(d.feature[g]);
+        meta |= primary_meta(g) & (META_DEFAULT_LEFT | META_CATEGORICAL);
+        cn.push_back(compact_value(g, ts.is_cat));
+        cn.push_back(meta);
+        coff.push_back(1);
+        lb.push_back(static_cast<uint32_t>(n_leaf));
+        if (!sp) {
+          double thr = 0;
+          if (!ts.is_cat) {
+            const uint64_t v = primary_value(g);
+            std::memcpy(&thr, &v, 8);
+          }
+          ex.push_back(thr);
+        }
+        stack.push_back({ts.right, static_cast<int64_t>(n_int), true});
+        stack.push_back({ts.left, static_cast<int64_t>(n_int), false});  // popped next
+      }
+      if (cn.size() / 2 >= (uint64_t(1) << 31) || n_leaf >= (uint64_t(1) << 31)) {
+        clear_compact();
+        return;
+      }
+      // the top T levels as a complete heap; a leaf above the last level fills its whole subtree
+      heap.assign(heap_n * 2, 0);
+      heap[1] = 0;
+      uint8_t* top = out.c_top.data() + static_cast<size_t>(p) * top_bytes;
+      for (size_t h = 1; h < heap_n; ++h) {
+        const int32_t rel = heap[h];
+        const int64_t g   = base + rel;
+        uint32_t value = 0x7F800000u, meta = 0;  // padding: "x < +inf", both children the same leaf
+        if (d.node_kind[g] == B2FIL_NODE_LEAF) {
+          heap[2 * h] = heap[2 * h + 1] = rel;
+        } else {
+          const Test ts   = normalise(d, g, precision);
+          heap[2 * h]     = ts.left;
+          heap[2 * h + 1] = ts.right;
+          const uint32_t k = number[rel];
+          value            = cn[static_cast<size_t>(k) * 2];
+          meta             = cn[static_cast<size_t>(k) * 2 + 1] & ~(CMETA_LEFT_LEAF | CMETA_RIGHT_LEAF);
+          if (!sp) out.c_top_src[static_cast<size_t>(p) * heap_n + h] = k;
+        }
+        std::memcpy(top + h * 8, &value, 4);
+        std::memcpy(top + h * 8 + 4, &meta, 4);
+      }
+      for (size_t e = 0; e < heap_n; ++e) {
+        const int32_t rel = heap[heap_n + e];
+        uint32_t exit     = number[rel];
+        if (d.node_kind[base + rel] == B2FIL_NODE_LEAF) exit |= C_EXIT_LEAF;
+        std::memcpy(top + heap_n * 8 + e * 4, &exit, 4);
+      }
+    }
+    if (fb + bits_for(max_off) > 28) {
+      clear_compact();
+      return;
+    }
+    const size_t n_int = cn.size() / 2;
+    for (size_t k = 0; k < n_int; ++k) cn[k * 2 + 1] |= coff[k] << fb;
+    out.c_nodes.swap(cn);
+    if (out.c_nodes.empty()) out.c_nodes.assign(2, 0);  // forests of single leaves: keep the arrays non-empty
+    if (lb.empty()) lb.push_back(0);
+    if (!sp && ex.empty()) ex.push_back(0.0);
+    out.view.c_enabled      = 1;
+    out.view.c_top_levels   = T;
+    out.view.c_feat_bits    = fb;
+    out.view.c_bottom_steps = std::max(0, maxd - T);
+    out.view.c_top_stride   = static_cast<int64_t>(top_bytes);
+  }
+
+  void clear_compact()
+  {
+    out.c_nodes.clear();
+    out.c_leaves_before.clear();
+    out.c_exact.clear();
+    out.c_leaf_payload.clear();
+    out.c_leaf_ids.clear();
+    out.c_top.clear();
+    out.c_top_src.clear();
+    out.view.c_enabled = 0;
   }
 };
 

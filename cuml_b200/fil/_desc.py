@@ -76,7 +76,7 @@ class CCreateOpts(C.Structure):
         ("device_id", C.c_int32),
         ("default_chunk_size", C.c_int32),
         ("row_quantization", C.c_int32),
-        ("reserved", C.c_int32),
+        ("compact_image", C.c_int32),
     ]
 
 
@@ -103,6 +103,8 @@ class CInfo(C.Structure):
         ("row_quantization", C.c_int32),
         ("peer_direct", C.c_int32),
         ("clone_src_device", C.c_int32),
+        ("compact_image", C.c_int32),
+        ("top_levels", C.c_int32),
         ("scratch_pool_bytes", C.c_int64),
     ]
 

@@ -41,11 +41,11 @@ class _Forest:
     @classmethod
     def create(cls, desc: ForestDesc, precision: int, layout: int, storage: int,
                align_bytes: int, device_id: int, default_chunk_size: int,
-               row_quantization: int = 0) -> "_Forest":
+               row_quantization: int = 0, compact_image: int = 0) -> "_Forest":
         lib = _lib.load()
         cd = desc.to_c()
         opts = CCreateOpts(precision, layout, storage, align_bytes, device_id, default_chunk_size,
-                           row_quantization, 0)
+                           row_quantization, compact_image)
         out = C.c_void_p()
         _lib.check(lib.b2fil_forest_create(C.byref(cd), C.byref(opts), C.byref(out)))
         return cls(out.value)
@@ -83,8 +83,12 @@ class ForestInference:
     is_classifier : whether `predict` returns classes and `predict_proba` is available.
     storage : 'auto' | 'dense' | 'sparse' - 'dense' pads trees to complete binary trees with
         implicit child indexing; 'auto' chooses it for shallow forests.
-    quantize_rows : dense forests without categorical splits predict on 16-bit per-feature ranks
-        of the inputs (exact: rank(x) <= j  <=>  x < threshold_j); False keeps the raw values.
+    quantize_rows : dense forests (categorical splits only with categories below 32) predict on
+        16-bit per-feature ranks of the inputs (exact: rank(x) <= j  <=>  x < threshold_j); False
+        keeps the raw values.
+    compact_nodes : sparse forests also get a compact image (8-byte internal nodes in depth-first
+        order, leaves apart, the top levels of every tree as a heap that the kernel keeps in
+        shared memory) whenever their fields fit; False keeps only the plain node array.
     device_id : CUDA device that holds the forest.
     output_type : 'input' (same kind of array as X), 'numpy' or 'torch'.
     """
@@ -93,7 +97,7 @@ class ForestInference:
                  verbose=False, is_classifier: Optional[bool] = None, layout: str = "depth_first",
                  default_chunk_size: Optional[int] = None, align_bytes: Optional[int] = None,
                  precision: str = "single", device_id: int = 0, storage: str = "auto",
-                 quantize_rows: bool = True):
+                 quantize_rows: bool = True, compact_nodes: bool = True):
         if layout not in LAYOUTS:
             raise ValueError(f"layout must be one of {sorted(LAYOUTS)}, got {layout!r}")
         if precision not in _PRECISIONS:
@@ -110,6 +114,7 @@ class ForestInference:
         self.device_id = int(device_id)
         self.storage = storage
         self.quantize_rows = bool(quantize_rows)
+        self.compact_nodes = bool(compact_nodes)
         self.output_type = output_type or "input"
         self.verbose = verbose
         self.handle = handle
@@ -137,7 +142,7 @@ class ForestInference:
         self._forest = _Forest.create(
             desc, F32 if prec == "single" else F64, LAYOUTS[self.layout], STORAGES[self.storage],
             int(self.align_bytes or 0), self.device_id, int(self.default_chunk_size or 0),
-            0 if self.quantize_rows else 1)
+            0 if self.quantize_rows else 1, 0 if getattr(self, "compact_nodes", True) else 1)
         self._cache_facts()
 
     def _cache_facts(self):

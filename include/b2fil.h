@@ -138,7 +138,11 @@ typedef struct b2fil_create_opts {
                                  ranks of the inputs, which is exact), 1 = never.  What the forest
                                  actually does is reported by b2fil_info.row_quantization, where
                                  1 means "on".                                                    */
-  int32_t reserved;
+  int32_t compact_image;      /* REQUEST, sparse storage: 0 = automatic (forests whose fields fit
+                                 also get the compact image - 8-byte internal nodes, leaves apart,
+                                 top levels of every tree as a heap for shared memory - that the
+                                 fast sparse kernel reads), 1 = never.  b2fil_info.compact_image
+                                 says whether it exists.                                          */
 } b2fil_create_opts;
 
 typedef struct b2fil_info {
@@ -157,6 +161,8 @@ typedef struct b2fil_info {
                                over a direct peer path (NVLink / PCIe peer-to-peer), 0 = staged
                                through host memory; -1 for forests made by b2fil_forest_create   */
   int32_t clone_src_device; /* device the forest was replicated from, or -1                     */
+  int32_t compact_image;    /* 1: sparse forest with the compact image                          */
+  int32_t top_levels;       /* levels of every tree kept as a heap for shared memory, else 0    */
   int64_t scratch_pool_bytes; /* device memory the forest's scratch pool holds right now (grows
                                  with the largest batch b2fil_predict has seen; never touched by
                                  b2fil_predict_fixed_scratch)                                    */

@@ -160,17 +160,17 @@ def py_predict(desc: ForestDesc, X, precision="single"):
 
 
 def run_pack_check(pack_check, desc: ForestDesc, X, precision="single", layout="depth_first",
-                   storage="auto", align_bytes=0, row_quantization=0):
+                   storage="auto", align_bytes=0, row_quantization=0, compact_image=0):
     """Pack `desc` with the product packer and walk the packed arrays on the host."""
     dt = np.float32 if precision == "single" else np.float64
     X = np.ascontiguousarray(X, dt)
     n = X.shape[0]
     ids = np.zeros((n, desc.n_trees), np.uint32)
     pay = np.zeros((n, desc.n_trees), np.float64)
-    info = np.zeros(12, np.int64)
+    info = np.zeros(16, np.int64)
     cd = desc.to_c()
     opts = CCreateOpts(0 if precision == "single" else 1, LAYOUTS[layout], STORAGES[storage],
-                       align_bytes, 0, 0, row_quantization, 0)
+                       align_bytes, 0, 0, row_quantization, compact_image)
     rc = pack_check.pack_check(C.byref(cd), C.byref(opts), X.ctypes.data, n, X.shape[1],
                                ids.ctypes.data, pay.ctypes.data, info.ctypes.data)
     return rc, ids, pay, info

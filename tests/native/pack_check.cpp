@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <limits>
 #include <string>
 #include <vector>
 
@@ -189,6 +190,105 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
   }
   return bad;
 }
+// Walk the compact image of a sparse forest the way the fast sparse kernel does: T steps through
+// the tree's heap, leave through an exit, then (k, L) steps over the 8-byte internal nodes; fp64
+// tests look the exact threshold up only when the float bound leaves the answer open.  Returns
+// the number of (row, tree) pairs whose leaf id or payload differs from the primary walk, and
+// counts the exact look-ups in *n_exact.
+template <typename T>
+int64_t walk_compact(const PackedForest& pf, const T* X, int64_t n_rows, int64_t stride,
+                     const uint32_t* ids, const double* payload, int64_t* n_exact)
+{
+  const ForestView& v = pf.view;
+  using V             = typename std::conditional<sizeof(T) == 4, uint32_t, uint64_t>::type;
+  const int TL        = v.c_top_levels;
+  const size_t heap_n = size_t(1) << TL;
+  const int fb        = v.c_feat_bits;
+  int64_t bad         = 0;
+  auto test = [&](uint32_t value, uint32_t meta, T x, uint32_t k) -> bool {
+    if (meta & META_CATEGORICAL) return goes_right<T, V>(static_cast<V>(value), meta, x, pf);
+    bool left;
+    if (sizeof(T) == 4) {
+      float thr;
+      std::memcpy(&thr, &value, 4);
+      left = x < static_cast<T>(thr);
+    } else {
+      float lo;
+      std::memcpy(&lo, &value, 4);
+      left = static_cast<double>(x) < static_cast<double>(lo);
+      if (!left && k != C_NO_NODE) {
+        // x rounded down to float
+        float xf = static_cast<float>(x);
+        if (static_cast<double>(xf) > static_cast<double>(x))
+          xf = std::nextafter(xf, -std::numeric_limits<float>::infinity());
+        if (xf == lo) {
+          ++*n_exact;
+          left = static_cast<double>(x) < pf.c_exact[k];
+        }
+      }
+    }
+    if (x != x) left = (meta & META_DEFAULT_LEFT) != 0;
+    return !left;
+  };
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const T* row = X + r * stride;
+    for (int p = 0; p < v.n_trees; ++p) {
+      const uint8_t* top = pf.c_top.data() + static_cast<size_t>(v.c_top_stride) * p;
+      uint32_t h         = 1;
+      for (int l = 0; l < TL; ++l) {
+        uint32_t value, meta;
+        std::memcpy(&value, top + h * 8, 4);
+        std::memcpy(&meta, top + h * 8 + 4, 4);
+        const uint32_t feat = meta & CMETA_LOW28;
+        const uint32_t src  = pf.c_top_src.empty() ? C_NO_NODE : pf.c_top_src[p * heap_n + h];
+        h = 2 * h + (test(value, meta, row[feat], src) ? 1 : 0);
+      }
+      uint32_t exit;
+      std::memcpy(&exit, top + heap_n * 8 + (h - heap_n) * 4, 4);
+      uint32_t leaf;
+      if (exit & C_EXIT_LEAF) {
+        leaf = exit & ~C_EXIT_LEAF;
+      } else {
+        uint32_t k = exit, L = pf.c_leaves_before[k];
+        int steps  = 0;
+        for (;;) {
+          if (++steps > v.c_bottom_steps) {
+            ++bad;  // the kernel's loop bound would have cut this walk short
+          }
+          const uint32_t value = pf.c_nodes[size_t(k) * 2], meta = pf.c_nodes[size_t(k) * 2 + 1];
+          const uint32_t feat  = meta & ((1u << fb) - 1u);
+          const uint32_t off   = (meta & CMETA_LOW28) >> fb;
+          const bool right     = test(value, meta, row[feat], k);
+          bool at_leaf;
+          if (right) {
+            at_leaf = (meta & CMETA_RIGHT_LEAF) != 0;
+            L += off;
+            k += off;
+          } else {
+            at_leaf = (meta & CMETA_LEFT_LEAF) != 0;
+            k += 1;
+          }
+          if (at_leaf) break;
+        }
+        leaf = L;
+      }
+      const int orig = pf.tree_orig[p];
+      if (pf.c_leaf_ids[leaf] != ids[r * v.n_trees + orig]) ++bad;
+      V pay;
+      std::memcpy(&pay, pf.c_leaf_payload.data() + size_t(leaf) * sizeof(V), sizeof(V));
+      double got;
+      if (v.leaf_vector_len > 1) {
+        got = static_cast<double>(static_cast<uint32_t>(pay));
+      } else {
+        T val;
+        std::memcpy(&val, &pay, sizeof(T));
+        got = static_cast<double>(val);
+      }
+      if (got != payload[r * v.n_trees + orig]) ++bad;
+    }
+  }
+  return bad;
+}
 }  // namespace
 
 extern "C" {
@@ -199,7 +299,9 @@ const char* pack_check_error() { return g_err.c_str(); }
 // n_nodes_packed, feat_bits; info[6] = 1 when a rank-quantised copy was built, info[7] = number of
 // (row, tree) pairs where the walk over that copy reaches another leaf; info[8..11] = feature
 // groups of the quantised copy, most halvings of a group's search window, largest group blob in
-// bytes, features in the first group.  force_dense_ok: 1 = let AUTO/DENSE accept any depth <= 16.
+// bytes, features in the first group; info[12] = 1 when a sparse forest got its compact image,
+// info[13] = (row, tree) pairs where the walk over that image reaches another leaf or payload,
+// info[14] = heap levels, info[15] = exact-threshold look-ups of that walk (fp64).
 int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, const void* X,
                int64_t n_rows, int64_t stride, uint32_t* ids, double* payload, int64_t* info)
 {
@@ -221,15 +323,24 @@ int pack_check(const b2fil_forest_desc* desc, const b2fil_create_opts* opts, con
     info[10] = std::max<int64_t>(info[10], g.blob_bytes);
   }
   if (!pf.q_groups.empty()) info[11] = pf.q_groups[0].f_end - pf.q_groups[0].f_begin;
+  info[12] = pf.view.c_enabled;
+  info[13] = info[15] = 0;
+  info[14] = pf.view.c_enabled ? pf.view.c_top_levels : 0;
   if (n_rows > 0) {
     if (opts->precision == B2FIL_F32) {
       walk<float>(pf, static_cast<const float*>(X), n_rows, stride, ids, payload);
       if (pf.view.q_enabled)
         info[7] = walk_quantised<float>(pf, static_cast<const float*>(X), n_rows, stride, ids);
+      if (pf.view.c_enabled)
+        info[13] = walk_compact<float>(pf, static_cast<const float*>(X), n_rows, stride, ids,
+                                       payload, &info[15]);
     } else {
       walk<double>(pf, static_cast<const double*>(X), n_rows, stride, ids, payload);
       if (pf.view.q_enabled)
         info[7] = walk_quantised<double>(pf, static_cast<const double*>(X), n_rows, stride, ids);
+      if (pf.view.c_enabled)
+        info[13] = walk_compact<double>(pf, static_cast<const double*>(X), n_rows, stride, ids,
+                                        payload, &info[15]);
     }
   }
   return B2FIL_OK;

@@ -47,11 +47,12 @@ def _tol(desc, precision):
 
 
 def _all_kinds(desc, X, precision, layout, storage, chunk_size=None, host=False,
-               quantize_rows=True):
+               quantize_rows=True, compact_nodes=True):
     """Run every output kind on the GPU and compare with the oracle."""
     tol = _tol(desc, precision)
     fi = ForestInference.load_from_treelite_model(desc, precision=precision, layout=layout,
-                                                  storage=storage, quantize_rows=quantize_rows)
+                                                  storage=storage, quantize_rows=quantize_rows,
+                                                  compact_nodes=compact_nodes)
     Xo = np.ascontiguousarray(X, np.float32 if precision == "single" else np.float64)
     Xd = Xo if host else _dev(Xo, precision)
 
@@ -86,6 +87,9 @@ def test_random_forests_operators_nan(layout, storage, precision):
                               postproc="sigmoid")
     X = random_rows(2, 777, desc.n_features, np.float64, nan_frac=0.15, integer=True)
     _all_kinds(desc, X, precision, layout, storage)
+    if storage == "sparse":  # the plain sparse kernel, which forests without a compact image use
+        fi = _all_kinds(desc, X, precision, layout, storage, compact_nodes=False)
+        assert fi.describe()["compact_image"] == 0
 
 
 @pytest.mark.parametrize("precision", ["single", "double"])
@@ -102,6 +106,41 @@ def test_dense_with_and_without_row_quantisation(precision, quantize_rows):
         # size asks for the regular path (rank pre-pass + quantised walk when it exists)
         _all_kinds(desc, X, precision, "depth_first", "dense", quantize_rows=quantize_rows,
                    chunk_size=4)
+
+
+@pytest.mark.parametrize("precision", ["single", "double"])
+def test_sparse_compact_image_deep_ragged_trees(precision):
+    """The kernel over the compact image on what it is for: ragged trees much deeper than the
+    heap of top levels, rows made of the thresholds and their neighbours (fp64: the float bound
+    in the 8-byte node cannot decide them, the exact threshold must), NaN and infinities,
+    single-leaf trees in the same forest, batches that fill 32-, 64- and 128-row tiles with a
+    ragged tail, and a tree count that leaves the last batch of heaps half empty."""
+    from cuml_b200.fil import _lib, concatenate
+
+    deep = random_forest_desc(35, n_trees=37, n_features=9, max_depth=16, p_leaf=0.25,
+                              mixed_ops=True, postproc="sigmoid")
+    stumps = random_forest_desc(36, n_trees=3, n_features=9, max_depth=0, postproc="sigmoid")
+    desc = concatenate([deep, stumps])
+    dt = np.float32 if precision == "single" else np.float64
+    thr = desc.threshold[desc.node_kind == 1]
+    rng = np.random.default_rng(4)
+    vals = np.concatenate([thr, np.nextafter(thr, np.inf), np.nextafter(thr, -np.inf),
+                           thr.astype(np.float32).astype(np.float64),
+                           [np.nan, np.inf, -np.inf, 0.0, -0.0]]).astype(dt)
+    for n in (70, 9_600, 23_001):
+        X = rng.choice(vals, size=(n, 9)).astype(dt)
+        X[: n // 2] = random_rows(5, n // 2, 9, dt, nan_frac=0.05)
+        fi = _all_kinds(desc, X, precision, "depth_first", "sparse")
+        d = fi.describe()
+        assert d["compact_image"] == 1 and d["top_levels"] >= 8
+        assert _lib.last_variant().startswith("sparse_compact_kernel<")
+    # vector leaves and several classes through the same kernel
+    vec = random_forest_desc(37, n_trees=21, n_outputs=3, vector=True, average=True, max_depth=13,
+                             p_leaf=0.12)
+    _all_kinds(vec, random_rows(6, 3000, vec.n_features, dt), precision, "breadth_first", "sparse")
+    multi = random_forest_desc(38, n_trees=30, n_outputs=4, max_depth=12, p_leaf=0.12,
+                               postproc="softmax")
+    _all_kinds(multi, random_rows(7, 3000, multi.n_features, dt), precision, "layered", "sparse")
 
 
 def test_row_quantisation_edge_values():
@@ -137,6 +176,9 @@ def test_categorical(layout, storage, big):
     X = random_rows(4, 500, desc.n_features, np.float32, nan_frac=0.1, categories=75 if big else 22)
     _all_kinds(desc, X, "single", layout, storage)
     _all_kinds(desc, X, "double", layout, storage)
+    if storage == "sparse":
+        _all_kinds(desc, X, "single", layout, storage, compact_nodes=False)
+        _all_kinds(desc, X, "double", layout, storage, compact_nodes=False)
 
 
 @pytest.mark.parametrize("layout,storage", CONFIGS)
@@ -145,6 +187,8 @@ def test_vector_leaves(layout, storage, precision):
     desc = random_forest_desc(5, n_trees=13, n_outputs=5, vector=True, average=True)
     X = random_rows(6, 300, desc.n_features, np.float32)
     _all_kinds(desc, X, precision, layout, storage)
+    if storage == "sparse":
+        _all_kinds(desc, X, precision, layout, storage, compact_nodes=False)
 
 
 @pytest.mark.parametrize("post", ["identity", "sigmoid", "exponential", "logarithm_one_plus_exp",
@@ -528,9 +572,14 @@ def test_last_variant_names_the_kernels(lib):
     desc = synthetic_complete_forest(100, 8, 64, seed=2)
     fi = ForestInference.load_from_treelite_model(desc)
     rng = np.random.default_rng(0)
-    fi.predict_proba(_dev(rng.standard_normal((30_000, 64)).astype(np.float32), "single"))
+    # 256-row tiles on every SM: the shape of large batches
+    fi.predict_proba(_dev(rng.standard_normal((60_000, 64)).astype(np.float32), "single"))
     v = _lib.last_variant()
     assert v.startswith("quantise_kernel<float> + dense_q_top_kernel<float,scalar,NT=6,DEPTH=8>")
+    # fewer rows than that: 128-row tiles, more warps, four trees in flight
+    fi.predict_proba(_dev(rng.standard_normal((30_000, 64)).astype(np.float32), "single"))
+    v = _lib.last_variant()
+    assert v.startswith("quantise_kernel<float> + dense_q_kernel<float,scalar,NT=4,DEPTH=8>")
     fi.predict_proba(_dev(rng.standard_normal((64, 64)).astype(np.float32), "single"))
     v = _lib.last_variant()
     assert v.startswith("dense_kernel<float,scalar") and "forest_splits=" in v

@@ -25,6 +25,11 @@ def _check(pack_check, desc, X, precision, layout, storage, align=0):
     if info[1] == 1 and desc.cat_ptr is None:
         assert info[6] == 1
     assert info[7] == 0
+    # sparse forests whose fields fit also carry the compact image (internal nodes only, heap of
+    # the top levels); the walk over it must reach the same leaves and payloads
+    if info[1] == 2 and desc.n_features <= 4096:
+        assert info[12] == 1 and info[14] >= 1
+    assert info[13] == 0
     if desc.leaf_vector_len == 1:
         pt = oracle.predict(desc, X, INFER_PER_TREE, precision)
         assert np.array_equal(pay.astype(pt.dtype), pt)
@@ -236,3 +241,38 @@ def test_rank_quantisation_threshold_limit(pack_check):
     rc, ids, _, info = run_pack_check(pack_check, desc, X, storage="dense")
     assert rc == 0 and info[1] == 1 and info[6] == 0
     assert np.array_equal(ids, oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+
+
+@pytest.mark.parametrize("layout", ["depth_first", "breadth_first", "layered"])
+def test_compact_image_of_sparse_forests(pack_check, layout):
+    """The compact image on what it was made for: deep ragged trees (deeper than the heap), fp64
+    thresholds that only an exact look-up can decide, single-leaf trees, vector leaves,
+    categorical tests, and the option that switches it off."""
+    desc = random_forest_desc(31, n_trees=12, n_features=7, max_depth=14, p_leaf=0.12,
+                              mixed_ops=True)
+    thr = desc.threshold[desc.node_kind == 1]
+    rng = np.random.default_rng(3)
+    # rows made of thresholds and their fp64 neighbours: the float bound cannot decide them
+    vals = np.concatenate([thr, np.nextafter(thr, np.inf), np.nextafter(thr, -np.inf),
+                           thr.astype(np.float32).astype(np.float64), [np.nan, np.inf, -np.inf]])
+    X = rng.choice(vals, size=(600, 7))
+    for precision in ("single", "double"):
+        info = _check(pack_check, desc, X, precision, layout, "sparse")
+        assert info[12] == 1 and 1 <= info[14] <= 10
+        if precision == "double":
+            assert info[15] > 0  # exact look-ups happened and agreed
+    rc, ids, pay, info = run_pack_check(pack_check, desc, X, "double", layout, "sparse",
+                                        compact_image=1)
+    assert rc == 0 and info[12] == 0
+    # shallower than the heap, single-leaf trees included
+    tiny = random_forest_desc(32, n_trees=6, max_depth=1, p_leaf=0.6)
+    _check(pack_check, tiny, random_rows(1, 50, tiny.n_features, np.float32), "single", layout,
+           "sparse")
+    vec = random_forest_desc(33, n_trees=7, n_outputs=3, vector=True, max_depth=12, p_leaf=0.15)
+    _check(pack_check, vec, random_rows(2, 200, vec.n_features, np.float64), "double", layout,
+           "sparse")
+    cat = random_forest_desc(34, n_trees=8, max_depth=11, p_leaf=0.15, categorical=True,
+                             big_categories=True)
+    Xc = random_rows(3, 300, cat.n_features, np.float64, categories=75)
+    _check(pack_check, cat, Xc, "double", layout, "sparse")
+    _check(pack_check, cat, Xc, "single", layout, "sparse")
