@@ -125,7 +125,9 @@ def _print_line(line):
     print(json.dumps(line), flush=True)
 
 
-def run(config: str, steps: int, scale: float, cpu: bool = True, emit=_print_line):
+def run(config: str, steps: int, scale: float, cpu: bool = True, emit=_print_line,
+        c3_options=None):
+    c3_options = c3_options or {}
     import torch
 
     from cuml_b200.fil import ForestInference, _lib, synthetic_complete_forest
@@ -196,7 +198,7 @@ def run(config: str, steps: int, scale: float, cpu: bool = True, emit=_print_lin
         m = RandomForestRegressor(n_estimators=200, max_depth=20, min_samples_leaf=1,
                                   random_state=0, n_jobs=-1).fit(X, y)
         n = int(5_000_000 * scale)
-        fi = ForestInference.load_from_sklearn(m, precision="double")
+        fi = ForestInference.load_from_sklearn(m, precision="double", **c3_options)
         Xd = _randn_rows(n, 64, torch.float64, 1)
         out = torch.empty((n, 1), device="cuda:0", dtype=torch.float64)
         ms = _time(lambda: fi.predict(Xd, preds=out), steps)

@@ -16,6 +16,7 @@
 
 #include "forest.hpp"
 #include "kernels.hpp"
+#include "kernels_q.hpp"
 
 using namespace b2fil;
 
@@ -534,6 +535,13 @@ int b2fil_enable_peer_access(int device_a, int device_b)
   if (device_a < 0 || device_b < 0 || device_a >= n_dev || device_b >= n_dev)
     return set_error(B2FIL_ERR_INVALID_ARG, "device ordinal out of range");
   return enable_peer_pair(device_a, device_b);
+}
+
+int b2fil_set_tuning(const char* key, int value)
+{
+  if (!key) return set_error(B2FIL_ERR_INVALID_ARG, "key is NULL");
+  set_tuning_value(key, value);
+  return B2FIL_OK;
 }
 
 int b2fil_last_variant(char* buf, size_t buf_bytes)

@@ -169,25 +169,24 @@ struct CompactNode {  // 8 bytes
   uint32_t value;     // float threshold bits (fp64 forests: rounded down) | bitset | pool offset
   uint32_t meta;
 };
-// Levels of every tree that go into the heap: as many as leave room, next to a row tile, for the
-// heaps of sixteen trees in the 227 KiB of shared memory of one SM (0: no compact image).
+// Levels of every tree that go into the heap (0: no compact image).  Measured on a 200-tree
+// depth-20 forest: what bounds the walk below the heap is the rate at which an SM's L1 can look
+// up the 32 unrelated cache lines of a warp's node fetches, and how many of those misses it can
+// keep in flight - and the second shrinks with the L1, i.e. grows with the shared memory left
+// unused.  Six levels (0.75 KB per tree) were the best trade: deeper heaps save few line
+// look-ups (a level costs min(32, 2^level) of them) and cost L1 capacity.
+constexpr int kCDefaultTopLevels = 6;
 inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs, int max_depth)
 {
   const size_t budget = 218 * 1024;
-  size_t rest         = 0;
-  for (int R = 128; R >= 32; R /= 2) {
+  bool fits           = false;
+  for (int R = 128; R >= 32 && !fits; R /= 2) {
     const size_t tile = static_cast<size_t>(n_features) * (R + 1) * elem_bytes;
     const size_t acc  = static_cast<size_t>(8) * n_outputs * R * elem_bytes;
-    if (tile + acc + 16 * 24 <= budget) {
-      rest = budget - tile - acc;
-      break;
-    }
+    fits = tile + acc + (static_cast<size_t>(12) << kCDefaultTopLevels) * 8 <= budget;
   }
-  if (rest == 0) return 0;
-  int T = kCMaxTopLevels;
-  while (T > 1 && (static_cast<size_t>(12) << T) * 16 > rest) --T;
-  if ((static_cast<size_t>(12) << T) * 16 > rest) return 0;
-  return std::max(1, std::min(T, max_depth));
+  if (!fits) return 0;
+  return std::max(1, std::min(kCDefaultTopLevels, max_depth));
 }
 
 enum NodeFormat : int32_t {
@@ -242,7 +241,7 @@ struct ForestView {
   int32_t c_top_levels;         // T
   int32_t c_feat_bits;
   int32_t c_bottom_steps;       // most steps a walk takes below the heap
-  int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 12
+  int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 12, rounded up to 16
   const CompactNode* c_nodes;   // [n_internal]
   const uint32_t* c_leaves_before;  // [n_internal] L of every internal node (forest-wide leaf numbers)
   const double* c_exact;        // [n_internal] exact thresholds (fp64 forests), else null

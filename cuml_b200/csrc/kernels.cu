@@ -791,7 +791,8 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
   } else {
     while (want > 32 && n_rows < static_cast<int64_t>(want) * sm_count) want /= 2;
   }
-  // tuning aid "R,G,NT,S,K", read from the environment once per process
+  // tuning aid "R,G,NT,S,K": from the environment (read once per process) or, taking
+  // precedence, from the knobs q_R, q_G, q_NT, q_S, q_K of b2fil_set_tuning
   static const struct ForcedShape {
     bool set = false;
     int R = 0, G = 0, NT = 0, S = 0, K = 0;
@@ -800,7 +801,16 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
       const char* e = getenv("B2FIL_Q_SHAPE");
       set = e && sscanf(e, "%d,%d,%d,%d,%d", &R, &G, &NT, &S, &K) == 5;
     }
-  } forced;
+  } from_env;
+  ForcedShape forced = from_env;
+  if (const int R = tuning_value("q_R", 0); R > 0) {
+    forced.set = true;
+    forced.R   = R;
+    forced.G   = tuning_value("q_G", 1);
+    forced.NT  = tuning_value("q_NT", 1);
+    forced.S   = tuning_value("q_S", 2);
+    forced.K   = tuning_value("q_K", 1);
+  }
   if (forced.set) {
     const int R = forced.R, G = forced.G, NT = forced.NT, S = forced.S, K = forced.K;
     if (R >= 32 && R % 32 == 0 &&
@@ -1020,7 +1030,22 @@ int pick_rows_per_tile(int64_t n_rows, int chunk_size, int sm_count)
 
 std::mutex g_smem_mu;
 std::map<std::pair<int, const void*>, size_t> g_smem_set;
+std::mutex g_tuning_mu;
+std::map<std::string, int> g_tuning;
 }  // namespace
+
+int tuning_value(const char* key, int fallback)
+{
+  std::lock_guard<std::mutex> lock(g_tuning_mu);
+  if (g_tuning.empty()) return fallback;
+  const auto it = g_tuning.find(key);
+  return it == g_tuning.end() ? fallback : it->second;
+}
+void set_tuning_value(const char* key, int value)
+{
+  std::lock_guard<std::mutex> lock(g_tuning_mu);
+  g_tuning[key] = value;
+}
 
 int set_smem_bytes(const void* kernel, size_t bytes, std::string& err)
 {

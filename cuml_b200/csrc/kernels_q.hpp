@@ -45,7 +45,11 @@ struct CompactCfg {
   size_t smem_bytes;
   int threads;
   int grid;
+  int node_load;      // how nodes below the heap are fetched (NodeLoad in kernels_sparse_c.cu)
 };
+// Value of a named tuning knob (b2fil_set_tuning), or `fallback` when it was never set.
+int tuning_value(const char* key, int fallback);
+void set_tuning_value(const char* key, int value);
 // Launch shape for `n_rows` rows starting from tiles of `rows_per_tile`; false when the forest has
 // no compact image or no shape fits shared memory (the plain sparse kernel runs then).
 bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t n_rows,

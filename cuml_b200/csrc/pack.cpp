@@ -779,7 +779,7 @@ struct Packer {
     out.storage          = B2FIL_STORAGE_SPARSE;
     out.node_bytes       = static_cast<int32_t>(nb);
     out.n_nodes_packed   = n_packed;
-    if (o.compact_image == 0) build_compact(pos, nb, format);
+    if (o.compact_image != 1) build_compact(pos, nb, format);
     return B2FIL_OK;
   }
 
@@ -802,7 +802,9 @@ struct Packer {
     const int es     = sp ? 4 : 8;
     const int fb     = bits_for(static_cast<uint32_t>(d.n_features - 1));
     const int maxd   = *std::max_element(tree_depth.begin(), tree_depth.end());
-    const int T      = compact_pick_top_levels(es, d.n_features, d.n_outputs, maxd);
+    int T            = compact_pick_top_levels(es, d.n_features, d.n_outputs, maxd);
+    if (o.compact_image > 100 && T >= 1)  // tuning aid: another number of heap levels
+      T = std::max(1, std::min({o.compact_image - 100, kCMaxTopLevels, std::max(1, maxd)}));
     if (T < 1 || fb >= 28) return;
     auto primary_value = [&](int64_t g) -> uint64_t {
       const uint8_t* at = out.nodes.data() + static_cast<size_t>(pos[g]) * nb;
@@ -845,7 +847,7 @@ struct Packer {
     std::vector<Frame> stack;
     std::vector<int32_t> heap;
     const size_t heap_n    = size_t(1) << T;
-    const size_t top_bytes = heap_n * 12;
+    const size_t top_bytes = (heap_n * 12 + 15) / 16 * 16;  // bulk copies move 16-byte multiples
     out.c_top.assign(static_cast<size_t>(nt) * top_bytes, 0);
     if (!sp) out.c_top_src.assign(static_cast<size_t>(nt) * heap_n, C_NO_NODE);
     uint32_t max_off = 0;

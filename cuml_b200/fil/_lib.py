@@ -60,6 +60,8 @@ def load() -> C.CDLL:
     lib.b2fil_forest_status.argtypes = [vp, C.POINTER(C.c_int32)]
     lib.b2fil_forest_selftest_timeout.restype = i32
     lib.b2fil_forest_selftest_timeout.argtypes = [vp, i32, vp]
+    lib.b2fil_set_tuning.restype = i32
+    lib.b2fil_set_tuning.argtypes = [C.c_char_p, i32]
     lib.b2fil_last_variant.restype = i32
     lib.b2fil_last_variant.argtypes = [C.c_char_p, C.c_size_t]
     lib.b2fil_enable_peer_access.restype = i32

@@ -114,7 +114,7 @@ class ForestInference:
         self.device_id = int(device_id)
         self.storage = storage
         self.quantize_rows = bool(quantize_rows)
-        self.compact_nodes = bool(compact_nodes)
+        self.compact_nodes = compact_nodes if isinstance(compact_nodes, int) else bool(compact_nodes)
         self.output_type = output_type or "input"
         self.verbose = verbose
         self.handle = handle
@@ -142,8 +142,16 @@ class ForestInference:
         self._forest = _Forest.create(
             desc, F32 if prec == "single" else F64, LAYOUTS[self.layout], STORAGES[self.storage],
             int(self.align_bytes or 0), self.device_id, int(self.default_chunk_size or 0),
-            0 if self.quantize_rows else 1, 0 if getattr(self, "compact_nodes", True) else 1)
+            0 if self.quantize_rows else 1, self._compact_option())
         self._cache_facts()
+
+    def _compact_option(self) -> int:
+        """`compact_image` of the create options: True / False, or an int = at most that many
+        heap levels (tuning aid)."""
+        c = getattr(self, "compact_nodes", True)
+        if isinstance(c, bool):
+            return 0 if c else 1
+        return 100 + int(c)
 
     def _cache_facts(self):
         """Plain-Python copies of what every call needs (ctypes field reads are slow)."""

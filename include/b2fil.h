@@ -141,8 +141,9 @@ typedef struct b2fil_create_opts {
   int32_t compact_image;      /* REQUEST, sparse storage: 0 = automatic (forests whose fields fit
                                  also get the compact image - 8-byte internal nodes, leaves apart,
                                  top levels of every tree as a heap for shared memory - that the
-                                 fast sparse kernel reads), 1 = never.  b2fil_info.compact_image
-                                 says whether it exists.                                          */
+                                 fast sparse kernel reads), 1 = never, 100 + T = automatic with at
+                                 most T heap levels (tuning aid).  b2fil_info.compact_image says
+                                 whether it exists.                                               */
 } b2fil_create_opts;
 
 typedef struct b2fil_info {
@@ -221,6 +222,18 @@ int b2fil_forest_selftest_timeout(b2fil_forest* f, int tries, void* cuda_stream)
  * scalar,NT=6,DEPTH=8> R=256 G=3 S=2 K=2".  Writes a NUL-terminated string of at most
  * buf_bytes - 1 characters and returns the full length.  No counterpart in the reference. */
 int b2fil_last_variant(char* buf, size_t buf_bytes);
+
+/* Tuning aid for experiments (defaults are the measured best; nothing needs it in normal use):
+ * set a named integer knob for the whole process.  Knobs: "q_R", "q_G", "q_NT", "q_S", "q_K" force
+ * the launch shape of the traversal over rank-quantised rows (rows per tile, tree groups, trees
+ * in flight per warp, ring depth, sub-batches per stage; q_R = 0: automatic);
+ * "compact_R", "compact_G", "compact_S"
+ * force the launch shape of the kernel over the compact image of sparse forests (rows per tile,
+ * tree groups, ring depth; 0 = automatic), "compact_load" picks the cache policy of its node
+ * fetches (0 read-only path, 1 L2 only, 2 read-only path without L1 allocation), "compact_top"
+ * caps the heap levels of compact images packed afterwards.  Unknown keys are stored and ignored.
+ * No counterpart in the reference. */
+int b2fil_set_tuning(const char* key, int value);
 
 /* Switch peer access between two devices on, in both directions, if the hardware allows it (a
  * per-process setting; forest replication and the sharded gather do this themselves).  Returns 1

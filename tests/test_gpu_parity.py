@@ -132,8 +132,13 @@ def test_sparse_compact_image_deep_ragged_trees(precision):
         X[: n // 2] = random_rows(5, n // 2, 9, dt, nan_frac=0.05)
         fi = _all_kinds(desc, X, precision, "depth_first", "sparse")
         d = fi.describe()
-        assert d["compact_image"] == 1 and d["top_levels"] >= 8
+        assert d["compact_image"] == 1 and d["top_levels"] >= 4
         assert _lib.last_variant().startswith("sparse_compact_kernel<")
+    # other heap depths (a tuning option) give the same answers
+    X = rng.choice(vals, size=(5000, 9)).astype(dt)
+    for levels in (1, 3, 9, 10):
+        fi = _all_kinds(desc, X, precision, "depth_first", "sparse", compact_nodes=levels)
+        assert fi.describe()["top_levels"] == levels
     # vector leaves and several classes through the same kernel
     vec = random_forest_desc(37, n_trees=21, n_outputs=3, vector=True, average=True, max_depth=13,
                              p_leaf=0.12)
@@ -584,6 +589,9 @@ def test_last_variant_names_the_kernels(lib):
     v = _lib.last_variant()
     assert v.startswith("dense_kernel<float,scalar") and "forest_splits=" in v
     sp = ForestInference.load_from_treelite_model(desc, storage="sparse")
+    sp.apply(_dev(rng.standard_normal((500, 64)).astype(np.float32), "single"))
+    assert _lib.last_variant().startswith("sparse_compact_kernel<float,leaf_id,NT=4,TOP=6>")
+    sp = ForestInference.load_from_treelite_model(desc, storage="sparse", compact_nodes=False)
     sp.apply(_dev(rng.standard_normal((500, 64)).astype(np.float32), "single"))
     assert _lib.last_variant().startswith("sparse_kernel<float,node8,leaf_id")
 
