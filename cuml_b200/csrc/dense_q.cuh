@@ -37,9 +37,21 @@ struct QTop {
   uint32_t w[3 * kQTopTrees];
 };
 
+__device__ __forceinline__ uint2 lds_u32x2(uint32_t a)
+{
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+
 // DEPTH > 0 fixes the tree depth at compile time (the level loop is fully unrolled); DEPTH == 0
 // reads it from the forest.  TOPC: the first two levels take their nodes from `top`.
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
+// PAIR: the walk for launch shapes that shared memory keeps small (few warps, few trees in
+// flight), where the latency of one step, not the shared-memory pipe, is the limit: both children
+// of the current node (heap words 2i and 2i + 1, one aligned 8-byte load) are requested together
+// with the row's rank, before the test is decided, so the next node is already there when the
+// test is known; a step costs one shared-memory latency instead of two, and one more wavefront.
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false>
 struct DenseQWalker {
   using TR = Traits<T>;
   // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
@@ -53,6 +65,8 @@ struct DenseQWalker {
                                               const QTop* top)
   {
     static_assert(!TOPC || (DEPTH >= 2 && !CAT), "top nodes need two plain levels");
+    static_assert(!PAIR || (!CAT && !TOPC && MODE == MODE_SCALAR && sizeof(T) == 4),
+                  "the child-pair walk exists for fp32 scalar leaves without categorical tests");
     const ForestView& f    = p.f;
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
@@ -133,6 +147,31 @@ struct DenseQWalker {
           a[k]   = idx[k] * 4u + base[k];
         }
       };
+      if constexpr (PAIR) {
+        uint32_t node[NT], d[NT];
+#pragma unroll
+        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);  // the root
+#pragma unroll 2
+        for (int lvl = 0; lvl < D; ++lvl) {
+          // children of node i are heap words 2i and 2i + 1; below the last level these are the
+          // two leaf payloads (4-byte payloads continue the heap)
+          uint2 pair[NT];
+#pragma unroll
+          for (int k = 0; k < NT; ++k) pair[k] = lds_u32x2(base[k] + idx[k] * 8u);
+          test(node, d);
+#pragma unroll
+          for (int k = 0; k < NT; ++k) {
+            idx[k]  = __funnelshift_l(d[k], idx[k], 1);
+            node[k] = static_cast<int32_t>(d[k]) < 0 ? pair[k].y : pair[k].x;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          if (FULL || k < n_act)
+            take_leaf<T, MODE>(p, first + k, node[k], 0u, acc_group, R, r, row, run);
+        }
+        return;
+      }
       if (TOPC) {
         // root and children from the constant bank: the same words in every lane
         uint32_t n1[NT], n2[NT], n3[NT], node[NT], d[NT];
@@ -262,7 +301,7 @@ struct DenseQWalker {
   }
 };
 
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC>
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false>
 __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint16_t* __restrict__ Q,
                                              const int32_t* __restrict__ tile_flags, const int R,
                                              const int G, const int S, const int K,
@@ -364,11 +403,11 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
     Running<T> run{T(0), 0};
     if (ok) {
       if (nans) {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<true>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR>::template walk<true>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, pos, run, top);
       } else {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC>::template walk<false>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR>::template walk<false>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, pos, run, top);
       }
@@ -393,6 +432,16 @@ dense_q_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
                const int K)
 {
   dense_q_body<T, MODE, NT, DEPTH, CAT, false>(p, Q, tile_flags, R, G, S, K, nullptr);
+}
+
+// Same kernel with the child-pair walk (see DenseQWalker).
+template <int NT>
+__global__ void __launch_bounds__(1024, 1)
+dense_q_pair_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
+                    const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
+                    const int K)
+{
+  dense_q_body<float, MODE_SCALAR, NT, 0, false, false, true>(p, Q, tile_flags, R, G, S, K, nullptr);
 }
 
 // Same kernel with the top nodes of every tree in the parameter block.

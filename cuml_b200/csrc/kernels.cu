@@ -783,7 +783,8 @@ int q_max_trees_in_flight(const ForestView& f, int mode)
 // as fit (31 consumer warps at most), then as many trees in flight per warp as there is a kernel
 // for, then the deepest tree ring that still fits.
 bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bool reduce,
-                    int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg)
+                    int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg,
+                    int depth_hint = 0)
 {
   int want = 256;
   if (chunk_size > 0) {
@@ -815,7 +816,8 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
     const int R = forced.R, G = forced.G, NT = forced.NT, S = forced.S, K = forced.K;
     if (R >= 32 && R % 32 == 0 &&
         R <= 256 && (R & (R - 1)) == 0 && G >= 1 && (R / 32) * G <= 31 &&
-        (NT == 1 || NT == 2 || NT == 4 || (NT == 6 && (R / 32) * G <= 24)) && S >= 2 &&
+        (NT == 1 || NT == 2 || NT == 4 || (NT == 6 && (R / 32) * G <= 24) ||
+         (NT == 3 && max_nt == 6 && depth_hint >= 9)) && S >= 2 &&
         S <= kMaxStages && K >= 1 && NT <= max_nt) {
       const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
@@ -826,28 +828,43 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
   }
   for (int R = want; R >= 32; R /= 2) {
     const int rw = R / 32;
+    // Among the (tree groups, trees in flight) pairs that fit with a two-stage ring, take the one
+    // with the most walks in flight per CTA (row warps x groups x trees): that is what hides the
+    // latency of a step, and shapes that shared memory keeps small are bound by exactly it
+    // (measured on 2000 depth-10 trees over 512 features, where only 12 trees fit: 3 groups x 2
+    // trees 7.2e7 rows/s, 5 groups x 1 tree 6.3e7).  Ties go to more warps.
+    int best_g = 0, best_nt = 0;
     // a CTA holds at most 32 warps and one of them is the producer
     for (int G = std::min(8, 31 / rw); G >= 1; --G) {
       for (int NT = max_nt; NT >= 1; NT = NT == 6 ? 4 : NT / 2) {
         // the six-tree kernels are built for at most 24 consumer warps (80 registers a thread)
         if (NT > 4 && rw * G > 24) continue;
-        // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees.
-        // Trees in flight per warp come before ring depth: two stages already hide the bulk
-        // copies (measured: S = 2 and S = 3 run alike), while 6 trees against 4 is 5 % faster.
-        for (int K = 2; K >= 1; K /= 2) {
-          for (int S = 3; S >= 2; --S) {
-            const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
-            if (b <= kMaxSmemBytes) {
-              cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, K};
-              return true;
-            }
-          }
+        if (dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, 2, 1) > kMaxSmemBytes) continue;
+        if (G * NT > best_g * best_nt) {
+          best_g  = G;
+          best_nt = NT;
+        }
+        break;  // smaller NT with the same G only has fewer walks
+      }
+    }
+    if (best_g == 0) continue;
+    // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees.
+    // Two stages already hide the bulk copies (measured: S = 2 and S = 3 run alike).
+    for (int K = 2; K >= 1; K /= 2) {
+      for (int S = 3; S >= 2; --S) {
+        const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, best_g, best_nt, S, K);
+        if (b <= kMaxSmemBytes) {
+          cfg = DenseCfg{R, best_g, best_nt, S, b, (rw * best_g + 1) * 32, K};
+          return true;
         }
       }
     }
   }
   return false;
 }
+
+// Launch shapes with at most this many walks in flight per CTA take the child-pair walk.
+constexpr int kPairWalkLimit = 0;  // 0: never automatically (set from measurements)
 
 // Pick the kernel family for a launch of the quantised traversal; the families are instantiated
 // in the kernels_q_*.cu translation units.
@@ -874,6 +891,15 @@ int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err
       rec.depth = f.dense_depth;
     return launch_q_cat(L, mode, f64, err);
   }
+  // Few walks in flight (shapes that shared memory keeps small): the latency of a step is the
+  // limit, and the walk that fetches both children ahead of the test halves it.
+  const int walks  = (L.c.rows_per_tile / 32) * L.c.tree_groups * L.c.trees_in_flight;
+  const int pair   = tuning_value("q_pair", -1);
+  const bool can_pair = !f64 && mode == MODE_SCALAR && L.c.trees_in_flight <= 4 && f.dense_depth >= 1;
+  if (can_pair && (pair == 1 || (pair < 0 && walks <= kPairWalkLimit))) {
+    rec.kernel = "dense_q_pair_kernel";
+    return launch_q_pair(L, err);
+  }
   const bool specialised = !f64 && mode == MODE_SCALAR && f.dense_depth >= 4 && f.dense_depth <= 10;
   if (specialised && L.c.trees_in_flight == 6) {
     // the common boosted-tree shapes: depth-specialised bodies with six trees in flight
@@ -889,6 +915,10 @@ int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err
     rec.depth = f.dense_depth;
     return launch_q_plain4(L, err);
   }
+  if (specialised && f.dense_depth >= 9 && (L.c.trees_in_flight == 2 || L.c.trees_in_flight == 3)) {
+    rec.depth = f.dense_depth;
+    return launch_q_plain23(L, err);
+  }
   return launch_q_generic(L, mode, f64, err);
 }
 
@@ -903,7 +933,8 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   const bool reduce   = mode <= MODE_VECTOR;
   DenseCfg c;
   if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
-                      f.n_features, f.n_outputs, reduce, p.n_rows, chunk_size, sm_count, c)) {
+                      f.n_features, f.n_outputs, reduce, p.n_rows, chunk_size, sm_count, c,
+                      f.dense_depth)) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }
@@ -1304,7 +1335,7 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
   DenseCfg c;
   if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
                       f.n_features, f.n_outputs, mode <= MODE_VECTOR, p.n_rows, chunk_size,
-                      sm_count, c)) {
+                      sm_count, c, f.dense_depth)) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }

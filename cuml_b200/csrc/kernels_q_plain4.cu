@@ -14,4 +14,17 @@ int launch_q_plain4(const QLaunch& L, std::string& err)
     default: return launch_q<float, MODE_SCALAR, 4, 10, false>(L, err);
   }
 }
+
+// Depth 9 and 10 with two or three trees in flight: shapes whose trees are so large (8 KB at depth
+// 10) that shared memory holds only a dozen of them next to the row tile.
+int launch_q_plain23(const QLaunch& L, std::string& err)
+{
+  const int d = L.p.f.dense_depth;
+  if (L.c.trees_in_flight == 3) {
+    return d == 9 ? launch_q<float, MODE_SCALAR, 3, 9, false>(L, err)
+                  : launch_q<float, MODE_SCALAR, 3, 10, false>(L, err);
+  }
+  return d == 9 ? launch_q<float, MODE_SCALAR, 2, 9, false>(L, err)
+                : launch_q<float, MODE_SCALAR, 2, 10, false>(L, err);
+}
 }  // namespace b2fil

@@ -226,7 +226,8 @@ int b2fil_last_variant(char* buf, size_t buf_bytes);
 /* Tuning aid for experiments (defaults are the measured best; nothing needs it in normal use):
  * set a named integer knob for the whole process.  Knobs: "q_R", "q_G", "q_NT", "q_S", "q_K" force
  * the launch shape of the traversal over rank-quantised rows (rows per tile, tree groups, trees
- * in flight per warp, ring depth, sub-batches per stage; q_R = 0: automatic);
+ * in flight per warp, ring depth, sub-batches per stage; q_R = 0: automatic), "q_pair" = 1 / 0
+ * forces / forbids its variant that fetches both children of a node ahead of the test (-1: automatic);
  * "compact_R", "compact_G", "compact_S"
  * force the launch shape of the kernel over the compact image of sparse forests (rows per tile,
  * tree groups, ring depth; 0 = automatic), "compact_load" picks the cache policy of its node

@@ -581,10 +581,10 @@ def test_last_variant_names_the_kernels(lib):
     fi.predict_proba(_dev(rng.standard_normal((60_000, 64)).astype(np.float32), "single"))
     v = _lib.last_variant()
     assert v.startswith("quantise_kernel<float> + dense_q_top_kernel<float,scalar,NT=6,DEPTH=8>")
-    # fewer rows than that: 128-row tiles, more warps, four trees in flight
+    # fewer rows than that: 128-row tiles and more tree groups
     fi.predict_proba(_dev(rng.standard_normal((30_000, 64)).astype(np.float32), "single"))
     v = _lib.last_variant()
-    assert v.startswith("quantise_kernel<float> + dense_q_kernel<float,scalar,NT=4,DEPTH=8>")
+    assert v.startswith("quantise_kernel<float> + dense_q_top_kernel<float,scalar,NT=6,DEPTH=8> R=128")
     fi.predict_proba(_dev(rng.standard_normal((64, 64)).astype(np.float32), "single"))
     v = _lib.last_variant()
     assert v.startswith("dense_kernel<float,scalar") and "forest_splits=" in v
@@ -831,13 +831,29 @@ def test_quantised_traversal_kernel_variants(n_trees, depth, n_classes):
     fi = ForestInference.load_from_treelite_model(desc)
     assert fi.describe()["row_quantization"] == 1
     Xd = _dev(X, "single")
-    for chunk_size in (8, 2):  # 256-row and 64-row tiles of the quantised path
-        raw = fi._run(Xd, INFER_DEFAULT, chunk_size).cpu().numpy()
-        np.testing.assert_allclose(raw, oracle.predict(desc, X, INFER_DEFAULT, "single"),
-                                   **_tol(desc, "single"))
-        ids = fi.apply(Xd, chunk_size=chunk_size).cpu().numpy()
-        assert np.array_equal(ids.astype(np.uint32),
-                              oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+    from cuml_b200.fil import _lib
+
+    lib = _lib.load()
+    try:
+        # q_pair = 1 forces the walk that fetches both children of a node ahead of the test (the
+        # variant for launch shapes with few walks in flight), 0 forbids it
+        for pair, shape in ((0, None), (1, None), (1, (128, 2, 2, 2, 1)), (1, (64, 3, 4, 2, 1)),
+                            (1, (32, 1, 1, 2, 1))):
+            lib.b2fil_set_tuning(b"q_pair", pair)
+            for key, v in zip((b"q_R", b"q_G", b"q_NT", b"q_S", b"q_K"), shape or (0, 0, 0, 0, 0)):
+                lib.b2fil_set_tuning(key, v)
+            for chunk_size in (8, 2):  # 256-row and 64-row tiles of the quantised path
+                raw = fi._run(Xd, INFER_DEFAULT, chunk_size).cpu().numpy()
+                if pair and (shape or n_trees != 2100):
+                    assert "dense_q_pair_kernel" in _lib.last_variant() or shape is None
+                np.testing.assert_allclose(raw, oracle.predict(desc, X, INFER_DEFAULT, "single"),
+                                           **_tol(desc, "single"))
+                ids = fi.apply(Xd, chunk_size=chunk_size).cpu().numpy()
+                assert np.array_equal(ids.astype(np.uint32),
+                                      oracle.predict(desc, X, INFER_LEAF_ID, "single"))
+    finally:
+        lib.b2fil_set_tuning(b"q_pair", -1)
+        lib.b2fil_set_tuning(b"q_R", 0)
 
 
 @pytest.mark.parametrize("precision", ["single", "double"])
