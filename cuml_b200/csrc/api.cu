@@ -355,8 +355,6 @@ int b2fil_forest_create(const b2fil_forest_desc* desc, const b2fil_create_opts* 
     if ((rc = upload(f.get(), pf.out_bias, offsetof(ForestView, out_bias))) != B2FIL_OK) return rc;
     if (pf.view.c_enabled) {
       if ((rc = upload(f.get(), pf.c_nodes, offsetof(ForestView, c_nodes))) != B2FIL_OK) return rc;
-      if ((rc = upload(f.get(), pf.c_leaves_before, offsetof(ForestView, c_leaves_before))) != B2FIL_OK)
-        return rc;
       if ((rc = upload(f.get(), pf.c_exact, offsetof(ForestView, c_exact))) != B2FIL_OK) return rc;
       if ((rc = upload(f.get(), pf.c_leaf_payload, offsetof(ForestView, c_leaf_payload))) != B2FIL_OK)
         return rc;

@@ -99,11 +99,10 @@ struct DenseQWalker {
         uint32_t q[NT];
 #pragma unroll
         for (int k = 0; k < NT; ++k)
-          // the low half of a node is feature * 4 (plus the categorical flag): without
-          // categorical tests one dot-product instruction (low half x byte 0 of fstride, high
-          // half x byte 1 = 0) turns it into the address of the row's rank of that feature
-          q[k] = lds_u16(CAT ? (node[k] & Q_FEATURE_FIELD) * fstride + row_addr
-                             : __dp2a_lo(node[k], fstride, row_addr));
+          // the low half of a node is feature * 4: one dot-product instruction (low half x byte 0
+          // of fstride, high half x byte 1 = 0) turns it into the address of the row's rank of
+          // that feature
+          q[k] = lds_u16(__dp2a_lo(node[k], fstride, row_addr));
         // forests with categorical tests: the 32-bit category set of every node, fetched for
         // all nodes (numerical ones hold an empty set) to keep the walk free of branches
         uint32_t bits[CAT ? NT : 1];

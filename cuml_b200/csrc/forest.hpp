@@ -71,7 +71,7 @@ struct SparseNode16D {  // fp64
 // A pre-pass kernel turns each row into 16-bit ranks (NaN becomes 0x3FFF); the traversal kernel
 // then reads 2-byte values and 4-byte nodes
 //     bits 31..17: j (0x7FFF = never left)   bit 16: missing goes right
-//     bits 15..2: feature                    bit 0: categorical
+//     bits 15..2: feature                    bits 1..0: zero
 // so a test is one signed subtraction: right <=> int(node) - (rank << 17) < 0 (the flag in bit 16
 // is below the weight of one rank and cannot change the sign), and the low half is the feature
 // times four: one 16-bit x 8-bit dot-product instruction scales it by a quarter of the byte
@@ -80,7 +80,8 @@ struct SparseNode16D {  // fp64
 // their place in the same scheme: the "rank" of a value is its category (Q_NO_CATEGORY when it is
 // negative, fractional-truncated out of range or too large), and a categorical node looks its
 // 32-bit category set up in a third per-tree array indexed like the nodes; a set bit sends the
-// row right.  The sets are stored bit-reversed (category c in bit 31 - c) and a categorical node
+// row right.  (A categorical node is recognisable by j = Q_MAX_RANK_FIELD; the walk does not need
+// to know, and the low half of every node stays a clean feature * 4 for the address arithmetic.)  The sets are stored bit-reversed (category c in bit 31 - c) and a categorical node
 // carries the largest rank, so its rank comparison always says "left" and the walk can simply OR
 // the two answers: sign(node - (code << 17)) | sign(set << code).
 // The rank is found through a per-feature bucket table: bucket(x) = clamp(int(fma(x, scale,
@@ -127,7 +128,6 @@ constexpr uint32_t Q_NO_CATEGORY   = 0x3FFEu;
 constexpr uint32_t Q_MAX_FEATURES  = 0x4000u;
 constexpr uint32_t Q_FEATURE_FIELD = 0xFFFCu;  // feature << 2
 constexpr uint32_t Q_FEATURE_SHIFT = 2;
-constexpr uint32_t Q_CATEGORICAL   = 0x1u;
 constexpr uint32_t Q_DEFAULT_RIGHT = 0x10000u;  // missing values go right (stored in this sense: << 15 makes it the sign)
 constexpr uint32_t Q_RANK_SHIFT    = 17;
 constexpr uint32_t Q_NEVER_LEFT    = 0x7FFFu;  // j of a test that no value passes
@@ -156,9 +156,9 @@ constexpr int kQTopTrees = 2048;
 //    value, and then the exact threshold is read from `c_exact` (one in 2^24 visits on
 //    continuous data), so the 8-byte node decides every test exactly;
 //  * the top `c_top_levels` levels of every tree are also stored as a complete heap
-//    [2^T nodes {value, feature | flags}][2^T exits], which the kernel streams through shared
-//    memory: a walk starts with T steps that cost no global fetch and leaves the heap through
-//    an exit = internal node to continue at, or leaf reached (bit 31).
+//    [2^T nodes {value, feature | flags}][2^T exits {k, L}], which the kernel streams through
+//    shared memory: a walk starts with T steps that cost no global fetch and leaves the heap
+//    through an exit = the pair (k, L) to continue at, or the leaf reached (bit 31 of k).
 constexpr uint32_t CMETA_LEFT_LEAF  = 0x20000000u;
 constexpr uint32_t CMETA_RIGHT_LEAF = 0x10000000u;
 constexpr uint32_t CMETA_LOW28      = 0x0FFFFFFFu;
@@ -173,7 +173,7 @@ struct CompactNode {  // 8 bytes
 // depth-20 forest: what bounds the walk below the heap is the rate at which an SM's L1 can look
 // up the 32 unrelated cache lines of a warp's node fetches, and how many of those misses it can
 // keep in flight - and the second shrinks with the L1, i.e. grows with the shared memory left
-// unused.  Six levels (0.75 KB per tree) were the best trade: deeper heaps save few line
+// unused.  Six levels (1 KB per tree) were the best trade: deeper heaps save few line
 // look-ups (a level costs min(32, 2^level) of them) and cost L1 capacity.
 constexpr int kCDefaultTopLevels = 6;
 inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs, int max_depth)
@@ -183,7 +183,7 @@ inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs
   for (int R = 128; R >= 32 && !fits; R /= 2) {
     const size_t tile = static_cast<size_t>(n_features) * (R + 1) * elem_bytes;
     const size_t acc  = static_cast<size_t>(8) * n_outputs * R * elem_bytes;
-    fits = tile + acc + (static_cast<size_t>(12) << kCDefaultTopLevels) * 8 <= budget;
+    fits = tile + acc + (static_cast<size_t>(16) << kCDefaultTopLevels) * 8 <= budget;
   }
   if (!fits) return 0;
   return std::max(1, std::min(kCDefaultTopLevels, max_depth));
@@ -241,9 +241,8 @@ struct ForestView {
   int32_t c_top_levels;         // T
   int32_t c_feat_bits;
   int32_t c_bottom_steps;       // most steps a walk takes below the heap
-  int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 12, rounded up to 16
+  int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 16
   const CompactNode* c_nodes;   // [n_internal]
-  const uint32_t* c_leaves_before;  // [n_internal] L of every internal node (forest-wide leaf numbers)
   const double* c_exact;        // [n_internal] exact thresholds (fp64 forests), else null
   const void* c_leaf_payload;   // [n_leaves] scalar in the forest precision or vector index
   const uint32_t* c_leaf_ids;   // [n_leaves] id of the leaf in the imported model
@@ -278,7 +277,7 @@ struct PackedForest {
   std::vector<QGroup> q_groups;
   std::vector<uint8_t> q_blob;
   std::vector<uint32_t> c_nodes;          // two words per internal node
-  std::vector<uint32_t> c_leaves_before;
+  std::vector<uint32_t> c_leaves_before;  // L of every internal node (host only: the exits carry it)
   std::vector<double> c_exact;
   std::vector<uint8_t> c_leaf_payload;
   std::vector<uint32_t> c_leaf_ids;

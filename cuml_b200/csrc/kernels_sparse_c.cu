@@ -194,10 +194,12 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
         }
 #pragma unroll
         for (int kk = 0; kk < NT; ++kk) {
-          const uint32_t exit = lds_u32(base[kk] + heap_n * 8u + (h[kk] - heap_n) * 4u);
-          live[kk]            = (exit & C_EXIT_LEAF) == 0u;
-          k[kk]               = live[kk] ? exit : 0u;  // a finished walk keeps fetching node 0: harmless
-          L[kk]               = exit & ~C_EXIT_LEAF;   // the leaf, when the walk ended in the heap
+          // the exits follow the 2^T node slots: exit e sits at 8 * (2^T + e) = 8 * h
+          uint32_t ek, eL;
+          lds_node(base[kk] + h[kk] * 8u, ek, eL);
+          live[kk] = (ek & C_EXIT_LEAF) == 0u;
+          k[kk]    = live[kk] ? ek : 0u;  // a finished walk keeps fetching node 0: harmless
+          L[kk]    = live[kk] ? eL : (ek & ~C_EXIT_LEAF);  // leaves before k, or the leaf itself
         }
       }
       // the heaps of this batch are no longer needed: let the producer refill the stage
@@ -206,10 +208,6 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       pos.advance(S);
       if (n_act > 0) {
         // part 2: compact nodes in global memory
-#pragma unroll
-        for (int kk = 0; kk < NT; ++kk) {
-          if (live[kk]) L[kk] = __ldg(f.c_leaves_before + k[kk]);
-        }
         for (int step = 0; step < f.c_bottom_steps; ++step) {
           uint2 node[NT];
 #pragma unroll

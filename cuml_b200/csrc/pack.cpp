@@ -590,7 +590,7 @@ struct Packer {
           for (int c = 0; c < 32; ++c) rev |= ((bits >> c) & 1u) << (31 - c);
           std::memcpy(sets + i * 4, &rev, 4);
           // the rank comparison of such a node must never say "right": the largest rank field
-          node |= Q_CATEGORICAL | (Q_MAX_RANK_FIELD << Q_RANK_SHIFT);
+          node |= Q_MAX_RANK_FIELD << Q_RANK_SHIFT;  // the largest rank marks a categorical node
         } else {
           uint32_t j;
           if (std::isnan(thr)) {
@@ -847,7 +847,7 @@ struct Packer {
     std::vector<Frame> stack;
     std::vector<int32_t> heap;
     const size_t heap_n    = size_t(1) << T;
-    const size_t top_bytes = (heap_n * 12 + 15) / 16 * 16;  // bulk copies move 16-byte multiples
+    const size_t top_bytes = heap_n * 16;  // 8-byte nodes, 8-byte exits
     out.c_top.assign(static_cast<size_t>(nt) * top_bytes, 0);
     if (!sp) out.c_top_src.assign(static_cast<size_t>(nt) * heap_n, C_NO_NODE);
     uint32_t max_off = 0;
@@ -932,10 +932,16 @@ struct Packer {
         std::memcpy(top + h * 8 + 4, &meta, 4);
       }
       for (size_t e = 0; e < heap_n; ++e) {
-        const int32_t rel = heap[heap_n + e];
-        uint32_t exit     = number[rel];
-        if (d.node_kind[base + rel] == B2FIL_NODE_LEAF) exit |= C_EXIT_LEAF;
-        std::memcpy(top + heap_n * 8 + e * 4, &exit, 4);
+        // exit = {internal node to continue at, leaves before it} or {leaf | flag, unused}
+        const int32_t rel  = heap[heap_n + e];
+        const bool is_leaf = d.node_kind[base + rel] == B2FIL_NODE_LEAF;
+        uint32_t exit[2]   = {number[rel], 0u};
+        if (is_leaf) {
+          exit[0] |= C_EXIT_LEAF;
+        } else {
+          exit[1] = lb[number[rel]];
+        }
+        std::memcpy(top + heap_n * 8 + e * 8, exit, 8);
       }
     }
     if (fb + bits_for(max_off) > 28) {

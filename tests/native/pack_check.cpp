@@ -178,7 +178,8 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
           std::memcpy(&bits, t + (size_t(1) << D) * (4 + es) + i * 4, 4);
           const uint32_t shifted = qq < 32u ? bits << qq : 0u;
           right = right || (shifted >> 31) != 0u;
-          if (!(node & Q_CATEGORICAL) && bits != 0u) ++bad;  // numerical nodes hold empty sets
+          // numerical nodes hold empty sets (a categorical node carries the largest rank)
+          if ((node >> Q_RANK_SHIFT) != Q_MAX_RANK_FIELD && bits != 0u) ++bad;
         }
         if (qq == Q_NAN_CODE) right = (node & Q_DEFAULT_RIGHT) != 0u;
         i = 2 * i + (right ? 1 : 0);
@@ -243,13 +244,14 @@ int64_t walk_compact(const PackedForest& pf, const T* X, int64_t n_rows, int64_t
         const uint32_t src  = pf.c_top_src.empty() ? C_NO_NODE : pf.c_top_src[p * heap_n + h];
         h = 2 * h + (test(value, meta, row[feat], src) ? 1 : 0);
       }
-      uint32_t exit;
-      std::memcpy(&exit, top + heap_n * 8 + (h - heap_n) * 4, 4);
+      uint32_t exit[2];
+      std::memcpy(exit, top + size_t(h) * 8, 8);  // exit e follows the 2^T node slots
       uint32_t leaf;
-      if (exit & C_EXIT_LEAF) {
-        leaf = exit & ~C_EXIT_LEAF;
+      if (exit[0] & C_EXIT_LEAF) {
+        leaf = exit[0] & ~C_EXIT_LEAF;
       } else {
-        uint32_t k = exit, L = pf.c_leaves_before[k];
+        uint32_t k = exit[0], L = exit[1];
+        if (L != pf.c_leaves_before[k]) ++bad;
         int steps  = 0;
         for (;;) {
           if (++steps > v.c_bottom_steps) {
