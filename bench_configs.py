@@ -2,6 +2,7 @@
 oracle in the run that times it.
 
     python bench_configs.py [--config c1 c2 c3 c4 c5 sweep] [--steps K] [--rows-scale S] [--no-cpu]
+                            [--plain-sparse]
 
 Prints one JSON line per configuration and call: rows/s with device-resident rows (CUDA events on
 the launching stream), the algorithmic bytes per row (features read once + outputs written once),
@@ -275,9 +276,12 @@ def main():
                     help="multiply every configuration's row count (smaller runs)")
     ap.add_argument("--no-cpu", action="store_true",
                     help="skip the CPU baseline / parity leg (profiling runs)")
+    ap.add_argument("--plain-sparse", action="store_true",
+                    help="c3: build the forest without the compact image (plain sparse kernel)")
     args = ap.parse_args()
     for c in args.config:
-        run(c, args.steps, args.rows_scale, cpu=not args.no_cpu)
+        run(c, args.steps, args.rows_scale, cpu=not args.no_cpu,
+            c3_options={"compact_nodes": False} if args.plain_sparse else None)
         import torch
 
         torch.cuda.empty_cache()
