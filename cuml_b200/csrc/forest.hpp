@@ -140,28 +140,33 @@ constexpr int kQTopTrees = 2048;
 // ---- compact image of a sparse forest -----------------------------------------------------------
 // Deep, ragged forests are bound by the chain of dependent node fetches from L2 / HBM.  Sparse
 // forests whose fields fit therefore carry a second image built for exactly that:
-//  * internal nodes only, 8 bytes each {value, meta}, in depth-first order per tree (the left
-//    child of node k is node k + 1), so the node array is half the size of an array that also
-//    holds the leaves and a quarter of the 16-byte fp64 array: it stays in L2;
+//  * internal nodes only, 8 bytes each {value, meta}, in depth-first order per tree, the child
+//    with the larger subtree first (rows are more likely to go where the training data went), so
+//    the node array is half the size of an array that also holds the leaves and a quarter of the
+//    16-byte fp64 array: it stays in L2.  The first child of node k is node k + 1: an aligned
+//    16-byte load brings a node and its neighbour, and half of the steps to a first child need no
+//    fetch at all;
 //  * leaves live in their own arrays (payload, id), numbered in the same depth-first order.  A
 //    walk carries the pair (k, L) = (internal node, number of leaves that precede it); with
-//    `off` = 1 + internal nodes of the left subtree,
-//        left : k + 1,   L          right : k + off, L + off
+//    `off` = 1 + internal nodes of the first child's subtree,
+//        first child : k + 1,   L          second child : k + off, L + off
 //    (a subtree with m internal nodes has m + 1 leaves), and two flags in the node say when the
-//    child reached is a leaf, whose number is then L (left) or L + off (right);
-//  * meta = default-left << 31 | categorical << 30 | left-is-leaf << 29 | right-is-leaf << 28 |
-//    off << feat_bits | feature;
-//  * fp64 forests keep `value` = the largest float <= threshold.  x < float(value) proves
-//    x < threshold; otherwise the answer is only in doubt when x rounded down to float equals
-//    value, and then the exact threshold is read from `c_exact` (one in 2^24 visits on
-//    continuous data), so the 8-byte node decides every test exactly;
+//    child reached is a leaf, whose number is then L (first) or L + off (second);
+//  * meta = default-left << 31 | categorical << 30 | first-is-leaf << 29 | second-is-leaf << 28 |
+//    first-child-is-the-right-child << 27 | off << feat_bits | feature;
+//  * fp64 forests keep `value` = the largest float <= threshold, and the kernel stages rows as
+//    floats rounded down: xl < value proves x < threshold, xl > value proves x > threshold, and
+//    only when xl == value the row's double and the exact threshold (`c_exact`) are read (one in
+//    2^24 visits on continuous data), so 8-byte nodes and 4-byte row values decide every fp64
+//    test exactly;
 //  * the top `c_top_levels` levels of every tree are also stored as a complete heap
 //    [2^T nodes {value, feature | flags}][2^T exits {k, L}], which the kernel streams through
 //    shared memory: a walk starts with T steps that cost no global fetch and leaves the heap
 //    through an exit = the pair (k, L) to continue at, or the leaf reached (bit 31 of k).
-constexpr uint32_t CMETA_LEFT_LEAF  = 0x20000000u;
-constexpr uint32_t CMETA_RIGHT_LEAF = 0x10000000u;
-constexpr uint32_t CMETA_LOW28      = 0x0FFFFFFFu;
+constexpr uint32_t CMETA_FIRST_LEAF  = 0x20000000u;
+constexpr uint32_t CMETA_SECOND_LEAF = 0x10000000u;
+constexpr uint32_t CMETA_SWAPPED     = 0x08000000u;  // the first (adjacent) child is the right child
+constexpr uint32_t CMETA_LOW27       = 0x07FFFFFFu;
 constexpr uint32_t C_EXIT_LEAF      = 0x80000000u;
 constexpr uint32_t C_NO_NODE        = 0xFFFFFFFFu;
 constexpr int kCMaxTopLevels        = 10;
@@ -170,18 +175,18 @@ struct CompactNode {  // 8 bytes
   uint32_t meta;
 };
 // Levels of every tree that go into the heap (0: no compact image).  Measured on a 200-tree
-// depth-20 forest: what bounds the walk below the heap is the rate at which an SM's L1 can look
-// up the 32 unrelated cache lines of a warp's node fetches, and how many of those misses it can
-// keep in flight - and the second shrinks with the L1, i.e. grows with the shared memory left
-// unused.  Six levels (1 KB per tree) were the best trade: deeper heaps save few line
-// look-ups (a level costs min(32, 2^level) of them) and cost L1 capacity.
-constexpr int kCDefaultTopLevels = 6;
+// depth-20 forest: the walk below the heap is bound by how many dependent fetches an SM keeps in
+// flight (warps x walks per warp, and the L1 that tracks the misses: it shrinks as shared memory
+// grows), so heap levels are only worth their shared memory while they do not cost warps.  Eight
+// levels (4 KB per tree) with 28 warps on 128-row tiles were the best trade (9.5e7 rows/s; six
+// levels 8.9e7, nine levels - room for 12 warps only - 5.8e7).
+constexpr int kCDefaultTopLevels = 8;
 inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs, int max_depth)
 {
   const size_t budget = 218 * 1024;
   bool fits           = false;
   for (int R = 128; R >= 32 && !fits; R /= 2) {
-    const size_t tile = static_cast<size_t>(n_features) * (R + 1) * elem_bytes;
+    const size_t tile = static_cast<size_t>(n_features) * (R + 1) * 4;  // rows are staged as floats
     const size_t acc  = static_cast<size_t>(8) * n_outputs * R * elem_bytes;
     fits = tile + acc + (static_cast<size_t>(16) << kCDefaultTopLevels) * 8 <= budget;
   }
@@ -242,7 +247,7 @@ struct ForestView {
   int32_t c_feat_bits;
   int32_t c_bottom_steps;       // most steps a walk takes below the heap
   int64_t c_top_stride;         // bytes between the heaps of two trees: 2^T * 16
-  const CompactNode* c_nodes;   // [n_internal]
+  const CompactNode* c_nodes;   // [n_internal, rounded up to even]: pairs are loaded together
   const double* c_exact;        // [n_internal] exact thresholds (fp64 forests), else null
   const void* c_leaf_payload;   // [n_leaves] scalar in the forest precision or vector index
   const uint32_t* c_leaf_ids;   // [n_leaves] id of the leaf in the imported model

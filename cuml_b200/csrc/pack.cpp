@@ -805,7 +805,7 @@ struct Packer {
     int T            = compact_pick_top_levels(es, d.n_features, d.n_outputs, maxd);
     if (o.compact_image > 100 && T >= 1)  // tuning aid: another number of heap levels
       T = std::max(1, std::min({o.compact_image - 100, kCMaxTopLevels, std::max(1, maxd)}));
-    if (T < 1 || fb >= 28) return;
+    if (T < 1 || fb >= 27) return;
     auto primary_value = [&](int64_t g) -> uint64_t {
       const uint8_t* at = out.nodes.data() + static_cast<size_t>(pos[g]) * nb;
       if (format == FMT_SPARSE_16D) {
@@ -842,10 +842,11 @@ struct Packer {
     struct Frame {
       int32_t rel;
       int64_t parent;   // forest-wide internal number of the parent, -1 for the root
-      bool is_right;
+      bool is_second;   // the parent's second (far) child
     };
     std::vector<Frame> stack;
-    std::vector<int32_t> heap;
+    std::vector<int32_t> heap, order;
+    std::vector<uint32_t> weight;  // internal nodes in the subtree of every node of the current tree
     const size_t heap_n    = size_t(1) << T;
     const size_t top_bytes = heap_n * 16;  // 8-byte nodes, 8-byte exits
     out.c_top.assign(static_cast<size_t>(nt) * top_bytes, 0);
@@ -857,6 +858,23 @@ struct Packer {
       const int64_t base = d.tree_offsets[t];
       const int64_t n    = d.tree_offsets[t + 1] - base;
       number.assign(static_cast<size_t>(n), 0);
+      // subtree sizes, children before parents (reverse of a pre-order listing)
+      weight.assign(static_cast<size_t>(n), 0);
+      order.clear();
+      order.push_back(0);
+      for (size_t i = 0; i < order.size(); ++i) {
+        const int64_t g = base + order[i];
+        if (d.node_kind[g] == B2FIL_NODE_LEAF) continue;
+        const Test ts = normalise(d, g, precision);
+        order.push_back(ts.left);
+        order.push_back(ts.right);
+      }
+      for (size_t i = order.size(); i-- > 0;) {
+        const int64_t g = base + order[i];
+        if (d.node_kind[g] == B2FIL_NODE_LEAF) continue;
+        const Test ts    = normalise(d, g, precision);
+        weight[order[i]] = 1 + weight[ts.left] + weight[ts.right];
+      }
       stack.clear();
       stack.push_back({0, -1, false});
       while (!stack.empty()) {
@@ -864,8 +882,8 @@ struct Packer {
         stack.pop_back();
         const int64_t g = base + fr.rel;
         const uint64_t n_int = cn.size() / 2;
-        if (fr.is_right) {
-          // everything between the parent and here is the parent's left subtree
+        if (fr.is_second) {
+          // everything between the parent and here is the subtree of the parent's first child
           const uint64_t off = n_int - static_cast<uint64_t>(fr.parent);
           coff[static_cast<size_t>(fr.parent)] = static_cast<uint32_t>(off);
           max_off = std::max<uint64_t>(max_off, off);
@@ -883,13 +901,16 @@ struct Packer {
           }
           out.c_leaf_ids.push_back(static_cast<uint32_t>(fr.rel));
           if (fr.parent >= 0)
-            cn[static_cast<size_t>(fr.parent) * 2 + 1] |= fr.is_right ? CMETA_RIGHT_LEAF : CMETA_LEFT_LEAF;
+            cn[static_cast<size_t>(fr.parent) * 2 + 1] |= fr.is_second ? CMETA_SECOND_LEAF : CMETA_FIRST_LEAF;
           continue;
         }
         const Test ts = normalise(d, g, precision);
         number[fr.rel] = static_cast<uint32_t>(n_int);
-        uint32_t meta  = static_cast<uint32_t>(d.feature[g]);
+        // the child with the larger subtree comes first (ties: the left one)
+        const bool swapped = weight[ts.right] > weight[ts.left];
+        uint32_t meta      = static_cast<uint32_t>(d.feature[g]);
         meta |= primary_meta(g) & (META_DEFAULT_LEFT | META_CATEGORICAL);
+        if (swapped) meta |= CMETA_SWAPPED;
         cn.push_back(compact_value(g, ts.is_cat));
         cn.push_back(meta);
         coff.push_back(1);
@@ -902,8 +923,8 @@ struct Packer {
           }
           ex.push_back(thr);
         }
-        stack.push_back({ts.right, static_cast<int64_t>(n_int), true});
-        stack.push_back({ts.left, static_cast<int64_t>(n_int), false});  // popped next
+        stack.push_back({swapped ? ts.left : ts.right, static_cast<int64_t>(n_int), true});
+        stack.push_back({swapped ? ts.right : ts.left, static_cast<int64_t>(n_int), false});  // popped next
       }
       if (cn.size() / 2 >= (uint64_t(1) << 31) || n_leaf >= (uint64_t(1) << 31)) {
         clear_compact();
@@ -925,7 +946,8 @@ struct Packer {
           heap[2 * h + 1] = ts.right;
           const uint32_t k = number[rel];
           value            = cn[static_cast<size_t>(k) * 2];
-          meta             = cn[static_cast<size_t>(k) * 2 + 1] & ~(CMETA_LEFT_LEAF | CMETA_RIGHT_LEAF);
+          meta             = cn[static_cast<size_t>(k) * 2 + 1] &
+                 ~(CMETA_FIRST_LEAF | CMETA_SECOND_LEAF | CMETA_SWAPPED);
           if (!sp) out.c_top_src[static_cast<size_t>(p) * heap_n + h] = k;
         }
         std::memcpy(top + h * 8, &value, 4);
@@ -944,14 +966,15 @@ struct Packer {
         std::memcpy(top + heap_n * 8 + e * 8, exit, 8);
       }
     }
-    if (fb + bits_for(max_off) > 28) {
+    if (fb + bits_for(max_off) > 27) {
       clear_compact();
       return;
     }
     const size_t n_int = cn.size() / 2;
     for (size_t k = 0; k < n_int; ++k) cn[k * 2 + 1] |= coff[k] << fb;
     out.c_nodes.swap(cn);
-    if (out.c_nodes.empty()) out.c_nodes.assign(2, 0);  // forests of single leaves: keep the arrays non-empty
+    // nodes are fetched as aligned pairs: an even count, and never an empty array
+    if (out.c_nodes.empty() || (out.c_nodes.size() / 2) % 2 != 0) out.c_nodes.resize(out.c_nodes.size() + 2, 0);
     if (lb.empty()) lb.push_back(0);
     if (!sp && ex.empty()) ex.push_back(0.0);
     out.view.c_enabled      = 1;

@@ -240,7 +240,7 @@ int64_t walk_compact(const PackedForest& pf, const T* X, int64_t n_rows, int64_t
         uint32_t value, meta;
         std::memcpy(&value, top + h * 8, 4);
         std::memcpy(&meta, top + h * 8 + 4, 4);
-        const uint32_t feat = meta & CMETA_LOW28;
+        const uint32_t feat = meta & CMETA_LOW27;
         const uint32_t src  = pf.c_top_src.empty() ? C_NO_NODE : pf.c_top_src[p * heap_n + h];
         h = 2 * h + (test(value, meta, row[feat], src) ? 1 : 0);
       }
@@ -259,15 +259,17 @@ int64_t walk_compact(const PackedForest& pf, const T* X, int64_t n_rows, int64_t
           }
           const uint32_t value = pf.c_nodes[size_t(k) * 2], meta = pf.c_nodes[size_t(k) * 2 + 1];
           const uint32_t feat  = meta & ((1u << fb) - 1u);
-          const uint32_t off   = (meta & CMETA_LOW28) >> fb;
+          const uint32_t off   = (meta & CMETA_LOW27) >> fb;
           const bool right     = test(value, meta, row[feat], k);
+          // the first child (adjacent) is the left one unless the node says otherwise
+          const bool second    = right != ((meta & CMETA_SWAPPED) != 0);
           bool at_leaf;
-          if (right) {
-            at_leaf = (meta & CMETA_RIGHT_LEAF) != 0;
+          if (second) {
+            at_leaf = (meta & CMETA_SECOND_LEAF) != 0;
             L += off;
             k += off;
           } else {
-            at_leaf = (meta & CMETA_LEFT_LEAF) != 0;
+            at_leaf = (meta & CMETA_FIRST_LEAF) != 0;
             k += 1;
           }
           if (at_leaf) break;

@@ -590,7 +590,7 @@ def test_last_variant_names_the_kernels(lib):
     assert v.startswith("dense_kernel<float,scalar") and "forest_splits=" in v
     sp = ForestInference.load_from_treelite_model(desc, storage="sparse")
     sp.apply(_dev(rng.standard_normal((500, 64)).astype(np.float32), "single"))
-    assert _lib.last_variant().startswith("sparse_compact_kernel<float,leaf_id,NT=4,TOP=6>")
+    assert _lib.last_variant().startswith("sparse_compact_kernel<float,leaf_id,NT=4,TOP=8>")
     sp = ForestInference.load_from_treelite_model(desc, storage="sparse", compact_nodes=False)
     sp.apply(_dev(rng.standard_normal((500, 64)).astype(np.float32), "single"))
     assert _lib.last_variant().startswith("sparse_kernel<float,node8,leaf_id")
