@@ -12,6 +12,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "forest.hpp"
@@ -109,8 +110,22 @@ constexpr int kMaxHostSlots = 4;
 struct HostPipeCfg {
   size_t block_bytes = size_t(256) << 20;
   int slots          = 2;
+  // pageable arrays: smaller blocks through three pinned staging buffers, filled by a few threads
+  size_t staged_block_bytes = size_t(64) << 20;
+  int staged_slots          = 3;
+  int copy_threads          = 0;
   HostPipeCfg()
   {
+    const unsigned hw = std::thread::hardware_concurrency();
+    copy_threads      = static_cast<int>(std::max(1u, std::min(8u, hw / 2)));
+    if (const char* e = getenv("B2FIL_HOST_COPY_THREADS")) {
+      const long n = atol(e);
+      if (n >= 1 && n <= 64) copy_threads = static_cast<int>(n);
+    }
+    if (const char* e = getenv("B2FIL_HOST_STAGED_BLOCK_MB")) {
+      const long mb = atol(e);
+      if (mb >= 1 && mb <= 1024) staged_block_bytes = static_cast<size_t>(mb) << 20;
+    }
     if (const char* e = getenv("B2FIL_HOST_BLOCK_MB")) {
       const long mb = atol(e);
       if (mb >= 1 && mb <= 4096) block_bytes = static_cast<size_t>(mb) << 20;
@@ -137,6 +152,13 @@ struct HostSlot {
   size_t x_bytes      = 0;
   size_t out_bytes    = 0;
   cudaEvent_t ev[3]   = {nullptr, nullptr, nullptr};  // sharded prediction: begin, kernels done, gathered
+  // pageable host arrays: pinned staging on the host side of the copies
+  void* pin_in         = nullptr;
+  void* pin_out        = nullptr;
+  size_t pin_in_bytes  = 0;
+  size_t pin_out_bytes = 0;
+  int64_t pending_r0   = -1;  // rows whose results sit in pin_out, not yet handed to the caller
+  int64_t pending_n    = 0;
 };
 
 struct b2fil_forest {
@@ -169,6 +191,8 @@ struct b2fil_forest {
       if (s.stream) cudaStreamDestroy(s.stream);
       for (auto& e : s.ev)
         if (e) cudaEventDestroy(e);
+      if (s.pin_in) cudaFreeHost(s.pin_in);
+      if (s.pin_out) cudaFreeHost(s.pin_out);
     }
   }
 };
@@ -292,6 +316,154 @@ int ensure_slot(b2fil_forest* f, HostSlot& s, size_t x_bytes, size_t out_bytes)
   }
   (void)f;
   return B2FIL_OK;
+}
+
+// Read and clear the status word.  The caller has already waited for the work it cares about.
+int read_status_word(const b2fil_forest* f, int32_t* status)
+{
+  B2FIL_CUDA(cudaMemcpy(status, f->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (*status != 0) {
+    // reported once: the next prediction starts from a clean word
+    B2FIL_CUDA(cudaMemset(f->status, 0, sizeof(int32_t)));
+    static const char* const where[] = {"", "tree ring (producer)", "tree ring (consumer)",
+                                        "row-tile buffer", "rank tables", "self test"};
+    const char* w = (*status >= 1 && *status <= 5) ? where[*status] : "unknown";
+    return set_error(B2FIL_ERR_TIMEOUT, std::string("a bounded wait inside a kernel ran out: ") +
+                                          w + " (status " + std::to_string(*status) + ")");
+  }
+  return B2FIL_OK;
+}
+
+// True when the CUDA runtime does not know the host pointer: ordinary (pageable) memory.  Copies
+// from such memory are staged by the driver through a small internal buffer and run at a
+// fraction of the link; the library stages them itself instead.
+bool is_pageable(const void* p)
+{
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return true;
+  }
+  return a.type == cudaMemoryTypeUnregistered;
+}
+
+int ensure_pinned(void** buf, size_t* have, size_t want)
+{
+  if (*have >= want) return B2FIL_OK;
+  if (*buf) cudaFreeHost(*buf);
+  *buf  = nullptr;
+  *have = 0;
+  const cudaError_t e = cudaHostAlloc(buf, want, cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(B2FIL_ERR_NO_MEMORY, std::string("pinned staging buffer: ") + cudaGetErrorString(e));
+  }
+  *have = want;
+  return B2FIL_OK;
+}
+
+// Copy `n_rows` rows of `row_bytes` bytes (source rows `src_stride` bytes apart) into a dense
+// buffer with `threads` host threads: one thread cannot fill a PCIe 5 link from pageable memory.
+void parallel_rows_copy(char* dst, const char* src, int64_t n_rows, size_t row_bytes,
+                        size_t src_stride, int threads)
+{
+  auto work = [=](int64_t b, int64_t e) {
+    if (src_stride == row_bytes) {
+      std::memcpy(dst + static_cast<size_t>(b) * row_bytes, src + static_cast<size_t>(b) * src_stride,
+                  static_cast<size_t>(e - b) * row_bytes);
+    } else {
+      for (int64_t r = b; r < e; ++r)
+        std::memcpy(dst + static_cast<size_t>(r) * row_bytes, src + static_cast<size_t>(r) * src_stride,
+                    row_bytes);
+    }
+  };
+  const int64_t min_rows = std::max<int64_t>(1, static_cast<int64_t>((size_t(4) << 20) / std::max<size_t>(1, row_bytes)));
+  const int t = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(threads, n_rows / min_rows)));
+  if (t <= 1) {
+    work(0, n_rows);
+    return;
+  }
+  std::vector<std::thread> pool;
+  pool.reserve(t - 1);
+  for (int i = 1; i < t; ++i) pool.emplace_back(work, n_rows * i / t, n_rows * (i + 1) / t);
+  work(0, n_rows / t);
+  for (auto& th : pool) th.join();
+}
+
+// Host-array prediction for pageable inputs: row blocks are gathered into pinned staging buffers
+// by several host threads while the previous blocks are copied and predicted; results come back
+// through pinned buffers too.  The caller holds the forest's host mutex and has made its device
+// current.
+int predict_host_staged(b2fil_forest* f, int infer_kind, const char* xin, int64_t n_rows,
+                        int64_t row_stride, char* yout, int chunk_size, double threshold)
+{
+  const HostPipeCfg& pipe = host_pipe_cfg();
+  const size_t es        = elem_bytes(f);
+  const int64_t F        = f->view.n_features;
+  const size_t in_row_b  = static_cast<size_t>(F) * es;
+  const size_t out_row_b = static_cast<size_t>(out_elems(f, infer_kind)) * out_elem_bytes(f, infer_kind);
+  int64_t block_rows = static_cast<int64_t>(
+    std::max<size_t>(1, pipe.staged_block_bytes / std::max(in_row_b, out_row_b)));
+  block_rows = std::max<int64_t>(block_rows / 128 * 128, 128);
+  block_rows = std::min(block_rows, n_rows);
+  const int S = pipe.staged_slots;
+  int rc      = B2FIL_OK;
+  for (int i = 0; i < S && rc == B2FIL_OK; ++i) {
+    HostSlot& s = f->slots[i];
+    rc = ensure_slot(f, s, static_cast<size_t>(block_rows) * in_row_b,
+                     static_cast<size_t>(block_rows) * out_row_b);
+    if (rc == B2FIL_OK) rc = ensure_pinned(&s.pin_in, &s.pin_in_bytes, static_cast<size_t>(block_rows) * in_row_b);
+    if (rc == B2FIL_OK) rc = ensure_pinned(&s.pin_out, &s.pin_out_bytes, static_cast<size_t>(block_rows) * out_row_b);
+    s.pending_r0 = -1;
+  }
+  if (rc != B2FIL_OK) return rc;  // nothing has been enqueued yet
+  // hand a slot's finished results to the caller (after its stream has drained)
+  auto flush = [&](HostSlot& s) -> int {
+    if (s.pending_r0 < 0) return B2FIL_OK;
+    const cudaError_t e = cudaStreamSynchronize(s.stream);
+    if (e != cudaSuccess) return cuda_error("cudaStreamSynchronize", e);
+    std::memcpy(yout + static_cast<size_t>(s.pending_r0) * out_row_b, s.pin_out,
+                static_cast<size_t>(s.pending_n) * out_row_b);
+    s.pending_r0 = -1;
+    return B2FIL_OK;
+  };
+  int which = 0;
+  for (int64_t r0 = 0; r0 < n_rows && rc == B2FIL_OK; r0 += block_rows, which = (which + 1) % S) {
+    HostSlot& s     = f->slots[which];
+    const int64_t n = std::min(block_rows, n_rows - r0);
+    if ((rc = flush(s)) != B2FIL_OK) break;  // also frees the slot's staging buffers for reuse
+    parallel_rows_copy(static_cast<char*>(s.pin_in), xin + static_cast<size_t>(r0) * row_stride * es,
+                       n, in_row_b, static_cast<size_t>(row_stride) * es, pipe.copy_threads);
+    cudaError_t e = cudaMemcpyAsync(s.x, s.pin_in, static_cast<size_t>(n) * in_row_b,
+                                    cudaMemcpyHostToDevice, s.stream);
+    if (e != cudaSuccess) {
+      rc = cuda_error("host-to-device copy of a row block", e);
+      break;
+    }
+    rc = enqueue(f, infer_kind, s.x, n, F, s.out, chunk_size, threshold, s.stream);
+    if (rc != B2FIL_OK) break;
+    e = cudaMemcpyAsync(s.pin_out, s.out, static_cast<size_t>(n) * out_row_b, cudaMemcpyDeviceToHost,
+                        s.stream);
+    if (e != cudaSuccess) {
+      rc = cuda_error("device-to-host copy of a result block", e);
+      break;
+    }
+    s.pending_r0 = r0;
+    s.pending_n  = n;
+  }
+  // drain every slot, also after an error: copies in flight still use the staging buffers
+  for (int i = 0; i < S; ++i) {
+    HostSlot& s = f->slots[i];
+    if (rc == B2FIL_OK) {
+      rc = flush(s);
+    } else if (s.stream) {
+      cudaStreamSynchronize(s.stream);
+      s.pending_r0 = -1;
+    }
+  }
+  if (rc != B2FIL_OK) return rc;
+  int32_t status = 0;
+  return read_status_word(f, &status);
 }
 
 }  // namespace
@@ -483,23 +655,6 @@ int64_t b2fil_output_elems_per_row(const b2fil_forest* f, int infer_kind)
   return n;
 }
 
-namespace {
-// Read and clear the status word.  The caller has already waited for the work it cares about.
-int read_status_word(const b2fil_forest* f, int32_t* status)
-{
-  B2FIL_CUDA(cudaMemcpy(status, f->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
-  if (*status != 0) {
-    // reported once: the next prediction starts from a clean word
-    B2FIL_CUDA(cudaMemset(f->status, 0, sizeof(int32_t)));
-    static const char* const where[] = {"", "tree ring (producer)", "tree ring (consumer)",
-                                        "row-tile buffer", "rank tables", "self test"};
-    const char* w = (*status >= 1 && *status <= 5) ? where[*status] : "unknown";
-    return set_error(B2FIL_ERR_TIMEOUT, std::string("a bounded wait inside a kernel ran out: ") +
-                                          w + " (status " + std::to_string(*status) + ")");
-  }
-  return B2FIL_OK;
-}
-}  // namespace
 
 int b2fil_forest_status(const b2fil_forest* f, int32_t* status)
 {
@@ -617,6 +772,10 @@ int b2fil_predict_host(b2fil_forest* f, int infer_kind, const void* X_host, int6
   const int64_t F        = f->view.n_features;
   const size_t in_row_b  = static_cast<size_t>(F) * es;
   const size_t out_row_b = static_cast<size_t>(out_elems(f, infer_kind)) * out_elem_bytes(f, infer_kind);
+  // ordinary (pageable) arrays of some size go through the library's own pinned staging
+  if (static_cast<size_t>(n_rows) * in_row_b >= (size_t(8) << 20) && is_pageable(X_host))
+    return predict_host_staged(f, infer_kind, static_cast<const char*>(X_host), n_rows, row_stride,
+                               static_cast<char*>(out_host), chunk_size, threshold);
   // row blocks of about 256 MiB of input (and at most 256 MiB of output) keep both copy engines
   // and the SMs busy while two blocks are in flight
   const HostPipeCfg& pipe = host_pipe_cfg();

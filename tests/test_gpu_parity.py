@@ -272,6 +272,45 @@ def test_row_stride_and_host_buffers():
     _all_kinds(desc, X, "double", "depth_first", "sparse", host=True)
 
 
+def test_pageable_host_arrays_take_the_staged_pipeline(lib):
+    """An ordinary NumPy array of several hundred MB: the library gathers row blocks into its own
+    pinned staging buffers with a few host threads (three slots, 64 MiB blocks, so slots are
+    reused) instead of leaving the staging to the driver.  Leaf ids must equal the device path bit
+    for bit and scores within the parity tolerance (row blocks choose their own tile shapes, and
+    with them the order of the sums); a strided input through the C ABI as well."""
+    import ctypes as C
+
+    torch = _torch()
+    desc = synthetic_complete_forest(60, 6, 256, seed=12)
+    fi = ForestInference.load_from_treelite_model(desc)
+    rng = np.random.default_rng(13)
+    n = 330_000  # 338 MB of fp32 rows: six blocks
+    X = rng.standard_normal((n, 256), dtype=np.float32)
+    X[::1000, 7] = np.nan
+    want = fi.predict_proba(torch.as_tensor(X, device="cuda:0")).cpu().numpy()
+    got = fi.predict_proba(X)
+    assert isinstance(got, np.ndarray)
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-7)
+    idx = rng.choice(n, 3000, replace=False)
+    np.testing.assert_allclose(got[idx], oracle.predict(desc, X[idx], INFER_PROBA2, "single"),
+                               rtol=1e-5, atol=1e-6)
+    ids = fi.apply(X[:70_000])  # 72 MB: two blocks, uint32 outputs of 240 bytes per row
+    assert np.array_equal(ids, fi.apply(torch.as_tensor(X[:70_000], device="cuda:0")).cpu().numpy())
+    # rows 256 elements apart of which the forest uses the first 200
+    narrow = synthetic_complete_forest(40, 5, 200, seed=14)
+    fn = ForestInference.load_from_treelite_model(narrow)
+    out = np.empty((n, 2), np.float32)
+    rc = lib.b2fil_predict_host(fn.forest.handle, INFER_PROBA2, X.ctypes.data, n, 256,
+                                out.ctypes.data, 0, 0.5)
+    assert rc == 0, lib.b2fil_last_error()
+    ref = fn.predict_proba(torch.as_tensor(np.ascontiguousarray(X[:, :200]), device="cuda:0"))
+    np.testing.assert_allclose(out, ref.cpu().numpy(), rtol=1e-6, atol=1e-7)
+    # pinned arrays keep the direct path and agree too
+    Xp = torch.empty((100_000, 256), dtype=torch.float32, pin_memory=True)
+    Xp.copy_(torch.as_tensor(X[:100_000]))
+    np.testing.assert_allclose(fi.predict_proba(Xp.numpy()), want[:100_000], rtol=1e-6, atol=1e-7)
+
+
 def test_golden_rfc_depth8():
     desc, X, exp = load_golden("rfc_depth8")
     for storage in ("dense", "sparse"):
