@@ -70,8 +70,8 @@ struct DenseQWalker {
     const ForestView& f    = p.f;
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
-    const uint32_t width_b = (1u << D) * 4u;
-    const uint32_t cat_off = (1u << D) * (4u + TR::ES);  // node address -> its category set
+    constexpr uint32_t QNB = CAT ? 8u : 4u;  // bytes per test node: {node, category set} or node
+    const uint32_t width_b = (1u << D) * QNB;
     const uint32_t fstride = stride_b >> Q_FEATURE_SHIFT;  // R / 2 <= 128: fits a byte
     const int per_sub      = G * NT;
     const int per_batch    = per_sub * K;
@@ -90,12 +90,12 @@ struct DenseQWalker {
         // slots past the end of the forest repeat the last live tree; results are dropped
         base[k] = base0 + static_cast<uint32_t>(FULL ? k : min(k, n_act - 1)) * tstride;
         idx[k]  = 1u;  // heap index of the root
-        a[k]    = base[k] + 4u;
+        a[k]    = base[k] + QNB;
       }
       // the NT walks are independent: all node loads are issued first, then all rank loads,
       // so that their shared-memory latencies overlap inside one warp.
       // test(): the rows' ranks against NT nodes; the sign bit of d[k] is the step to the right.
-      auto test = [&](const uint32_t(&node)[NT], uint32_t(&d)[NT]) {
+      auto test = [&](const uint32_t(&node)[NT], const uint32_t(&bits)[CAT ? NT : 1], uint32_t(&d)[NT]) {
         uint32_t q[NT];
 #pragma unroll
         for (int k = 0; k < NT; ++k)
@@ -103,23 +103,17 @@ struct DenseQWalker {
           // of fstride, high half x byte 1 = 0) turns it into the address of the row's rank of
           // that feature
           q[k] = lds_u16(__dp2a_lo(node[k], fstride, row_addr));
-        // forests with categorical tests: the 32-bit category set of every node, fetched for
-        // all nodes (numerical ones hold an empty set) to keep the walk free of branches
-        uint32_t bits[CAT ? NT : 1];
-        if (CAT) {
-#pragma unroll
-          for (int k = 0; k < NT; ++k) bits[k] = lds_u32(a[k] + cat_off);
-        }
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           // rank j in the high half: x < T[j] <=> rank(x) <= j, so right <=> j - rank < 0
           d[k] = rank_diff(node[k], q[k]);
           if (CAT) {
-            // the code of a categorical value is its category and the node's set is stored
-            // bit-reversed: the clamped funnel shift by the code moves the category's bit to the
-            // sign position and yields 0 for every code of 32 and above (no category, NaN).  A
-            // categorical node carries the largest rank (its comparison never says "right") and
-            // a numerical node an empty set, so the two answers are simply ORed.
+            // the code of a categorical value is its category and the node's set (fetched with
+            // the node; numerical nodes hold an empty one) is stored bit-reversed: the clamped
+            // funnel shift by the code moves the category's bit to the sign position and yields 0
+            // for every code of 32 and above (no category, NaN).  A categorical node carries the
+            // largest rank (its comparison never says "right"), so the two answers are simply
+            // ORed and the walk has no data-dependent branch.
             d[k] |= __funnelshift_lc(0u, bits[k], q[k]);
           }
           if (NANS) {
@@ -135,17 +129,26 @@ struct DenseQWalker {
         }
       };
       auto level = [&]() {
-        uint32_t node[NT], d[NT];
+        uint32_t node[NT], d[NT], bits[CAT ? NT : 1];
 #pragma unroll
-        for (int k = 0; k < NT; ++k) node[k] = lds_u32(a[k]);
-        test(node, d);
+        for (int k = 0; k < NT; ++k) {
+          if (CAT) {
+            const uint2 both = lds_u32x2(a[k]);
+            node[k]          = both.x;
+            bits[k]          = both.y;
+          } else {
+            node[k] = lds_u32(a[k]);
+          }
+        }
+        test(node, bits, d);
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           // heap index 2i + right in one funnel shift: (i << 1) | (d >> 31)
           idx[k] = __funnelshift_l(d[k], idx[k], 1);
-          a[k]   = idx[k] * 4u + base[k];
+          a[k]   = idx[k] * QNB + base[k];
         }
       };
+      const uint32_t no_bits[1] = {0u};  // walks without categorical tests
       if constexpr (PAIR) {
         uint32_t node[NT], d[NT];
 #pragma unroll
@@ -157,7 +160,7 @@ struct DenseQWalker {
           uint2 pair[NT];
 #pragma unroll
           for (int k = 0; k < NT; ++k) pair[k] = lds_u32x2(base[k] + idx[k] * 8u);
-          test(node, d);
+          test(node, reinterpret_cast<const uint32_t(&)[CAT ? NT : 1]>(no_bits), d);
 #pragma unroll
           for (int k = 0; k < NT; ++k) {
             idx[k]  = __funnelshift_l(d[k], idx[k], 1);
@@ -181,13 +184,13 @@ struct DenseQWalker {
           n2[k]       = top->w[t + 1];
           n3[k]       = top->w[t + 2];
         }
-        test(n1, d);
+        test(n1, reinterpret_cast<const uint32_t(&)[CAT ? NT : 1]>(no_bits), d);
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           node[k] = static_cast<int32_t>(d[k]) < 0 ? n3[k] : n2[k];
           idx[k]  = __funnelshift_l(d[k], 1u, 1);
         }
-        test(node, d);
+        test(node, reinterpret_cast<const uint32_t(&)[CAT ? NT : 1]>(no_bits), d);
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           idx[k] = __funnelshift_l(d[k], idx[k], 1);
@@ -219,7 +222,7 @@ struct DenseQWalker {
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
           const uint32_t slot   = idx[k] - (1u << D);
-          const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
+          const uint32_t leaf_a = (TR::ES == 4 && !CAT) ? a[k] : base[k] + width_b + slot * TR::ES;
           val[k]                = TR::ld_val(leaf_a);
         }
         const bool scalar_out = MODE == MODE_LEAFID || f.leaf_vector_len <= 1;
@@ -263,7 +266,7 @@ struct DenseQWalker {
             // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
             // address of leaf slot j is exactly the address the walk ended on
             const uint32_t slot   = idx[k] - (1u << D);
-            const uint32_t leaf_a = TR::ES == 4 ? a[k] : base[k] + width_b + slot * TR::ES;
+            const uint32_t leaf_a = (TR::ES == 4 && !CAT) ? a[k] : base[k] + width_b + slot * TR::ES;
             const typename TR::Val payload = TR::ld_val(leaf_a);
             if (MODE == MODE_SCALAR && CAT && same_class) {
               run.sum += TR::as_real(payload);

@@ -78,9 +78,9 @@ struct SparseNode16D {  // fp64
 // stride between features and adds the row's address.
 // Categorical features (every test on them is categorical, every listed category below 32) keep
 // their place in the same scheme: the "rank" of a value is its category (Q_NO_CATEGORY when it is
-// negative, fractional-truncated out of range or too large), and a categorical node looks its
-// 32-bit category set up in a third per-tree array indexed like the nodes; a set bit sends the
-// row right.  (A categorical node is recognisable by j = Q_MAX_RANK_FIELD; the walk does not need
+// negative, fractional-truncated out of range or too large), and in such forests every node is
+// 8 bytes {node, 32-bit category set} (a numerical node holds an empty set), fetched with one
+// load; a set bit sends the row right.  (A categorical node is recognisable by j = Q_MAX_RANK_FIELD; the walk does not need
 // to know, and the low half of every node stays a clean feature * 4 for the address arithmetic.)  The sets are stored bit-reversed (category c in bit 31 - c) and a categorical node
 // carries the largest rank, so its rank comparison always says "left" and the walk can simply OR
 // the two answers: sign(node - (code << 17)) | sign(set << code).
@@ -233,9 +233,9 @@ struct ForestView {
   int32_t q_n_groups;
   int32_t q_has_cat;            // 1: tree blocks carry a third array of 32-bit category sets
   int32_t q_trees_in_order;     // 1: packed tree t is the caller's tree t (tree_orig is the identity)
-  int64_t q_tree_stride;        // bytes between trees: 2^D * (4 + element size [+ 4]), 16-byte multiple
-  const void* q_nodes;          // [n_trees] blocks of [2^D nodes uint32][2^D leaf payloads]
-                                //           [2^D category sets uint32, when q_has_cat]
+  int64_t q_tree_stride;        // bytes between trees: 2^D * (node bytes + element size), 16-byte multiple
+  const void* q_nodes;          // [n_trees] blocks of [2^D nodes][2^D leaf payloads]; a node is a
+                                // uint32, or {uint32 node, uint32 category set} when q_has_cat
   const void* q_nodes_ids;      // same blocks with the leaf id (uint32) in every leaf payload slot:
                                 // what the traversal streams when it reports leaf ids
   int64_t q_max_blob_bytes;     // largest group blob

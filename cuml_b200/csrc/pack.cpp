@@ -562,18 +562,19 @@ struct Packer {
       out.q_groups.push_back(g);
       f += n;
     }
-    // 4. nodes: same heap layout as the dense blocks, 4 bytes per test node; forests with
-    //    categorical tests carry a third array with the 32-bit category set of every node
+    // 4. nodes: same heap layout as the dense blocks, 4 bytes per test node; in forests with
+    //    categorical tests a node is 8 bytes {node, 32-bit category set}, so that one load brings
+    //    both (a numerical node holds an empty set)
     const size_t nb      = sizeof(T) == 4 ? sizeof(DenseNodeF) : sizeof(DenseNodeD);
     const size_t es      = sizeof(T);
     const int64_t width  = int64_t(1) << D;
-    int64_t qstride      = width * static_cast<int64_t>(4 + es + (has_cat ? 4 : 0));
+    const int64_t qnb    = has_cat ? 8 : 4;  // bytes per test node in the quantised image
+    int64_t qstride      = width * static_cast<int64_t>(qnb + es);
     qstride              = (qstride + 15) / 16 * 16;
     out.q_nodes.assign(static_cast<size_t>(qstride) * nt, 0);
     for (int p = 0; p < nt; ++p) {
       const uint8_t* src = out.nodes.data() + static_cast<size_t>(out.view.tree_stride) * p;
       uint8_t* dst       = out.q_nodes.data() + static_cast<size_t>(qstride) * p;
-      uint8_t* sets      = dst + width * (4 + es);
       for (int64_t i = 1; i < width; ++i) {
         T thr;
         uint32_t meta;
@@ -588,7 +589,7 @@ struct Packer {
           // category then puts the answer in the sign bit
           uint32_t rev = 0;
           for (int c = 0; c < 32; ++c) rev |= ((bits >> c) & 1u) << (31 - c);
-          std::memcpy(sets + i * 4, &rev, 4);
+          std::memcpy(dst + i * qnb + 4, &rev, 4);
           // the rank comparison of such a node must never say "right": the largest rank field
           node |= Q_MAX_RANK_FIELD << Q_RANK_SHIFT;  // the largest rank marks a categorical node
         } else {
@@ -603,14 +604,14 @@ struct Packer {
           }
           node |= j << Q_RANK_SHIFT;
         }
-        std::memcpy(dst + i * 4, &node, 4);
+        std::memcpy(dst + i * qnb, &node, 4);
       }
-      std::memcpy(dst + width * 4, src + width * nb, static_cast<size_t>(width) * es);
+      std::memcpy(dst + width * qnb, src + width * nb, static_cast<size_t>(width) * es);
     }
     // the same image with the leaf id in every payload slot, for predictions that report leaves
     out.q_nodes_ids = out.q_nodes;
     for (int p = 0; p < nt; ++p) {
-      uint8_t* leaves = out.q_nodes_ids.data() + static_cast<size_t>(qstride) * p + width * 4;
+      uint8_t* leaves = out.q_nodes_ids.data() + static_cast<size_t>(qstride) * p + width * qnb;
       std::memset(leaves, 0, static_cast<size_t>(width) * es);
       for (int64_t s = 0; s < width; ++s) {
         const uint32_t id = out.leaf_ids[static_cast<size_t>(width) * p + s];

@@ -363,9 +363,16 @@ class ForestInference:
 
     def optimize(self, *, data=None, batch_size: int = 1024, unique_batches: int = 10,
                  timeout: float = 0.2, predict_method: str = "predict",
-                 max_chunk_size: Optional[int] = None, seed: int = 0):
-        """Time `predict_method` for every chunk size on device batches and keep the fastest as
-        the default chunk size.  Returns the chosen value."""
+                 max_chunk_size: Optional[int] = None, seed: int = 0, layouts=None):
+        """Time `predict_method` on device batches for every chunk size and keep the fastest as
+        the default chunk size; returns it.
+
+        `layouts`: node orders to try as well (the reference's tests sweep all three,
+        python/cuml/tests/test_random_forest.py:902-1024).  The node order only matters to
+        forests that run the plain sparse kernel, so by default (None) the sweep covers the three
+        orders exactly for those (sparse storage without a compact image) and is skipped
+        otherwise; pass a list to force it.  Trying an order re-packs the forest from its
+        description; the fastest (layout, chunk size) pair is kept and `self.layout` updated."""
         torch = _torch()
         dev = torch.device(f"cuda:{self.forest.info.device_id}")
         tdt = torch.float32 if self.forest.get_dtype() == np.float32 else torch.float64
@@ -378,26 +385,49 @@ class ForestInference:
             data = torch.as_tensor(data, device=dev, dtype=tdt)
             if data.ndim == 2:
                 data = data.unsqueeze(0)
-        fn = getattr(self, predict_method)
-        best, best_t = None, float("inf")
-        for cs in (1, 2, 4, 8, 16, 32):
-            if max_chunk_size is not None and cs > max_chunk_size:
-                break
-            fn(data[0], chunk_size=cs)
-            torch.cuda.synchronize(dev)
-            t0, reps = time.perf_counter(), 0
-            while True:
-                for b in range(data.shape[0]):
-                    fn(data[b], chunk_size=cs)
-                torch.cuda.synchronize(dev)
-                reps += 1
-                if time.perf_counter() - t0 > timeout / 6 or reps >= 20:
+
+        def sweep_chunks():
+            fn = getattr(self, predict_method)
+            best, best_t = None, float("inf")
+            for cs in (1, 2, 4, 8, 16, 32):
+                if max_chunk_size is not None and cs > max_chunk_size:
                     break
-            t = (time.perf_counter() - t0) / reps
-            if t < best_t:
-                best, best_t = cs, t
-        self.default_chunk_size = best
-        return best
+                fn(data[0], chunk_size=cs)
+                torch.cuda.synchronize(dev)
+                t0, reps = time.perf_counter(), 0
+                while True:
+                    for b in range(data.shape[0]):
+                        fn(data[b], chunk_size=cs)
+                    torch.cuda.synchronize(dev)
+                    reps += 1
+                    if time.perf_counter() - t0 > timeout / 6 or reps >= 20:
+                        break
+                t = (time.perf_counter() - t0) / reps
+                if t < best_t:
+                    best, best_t = cs, t
+            return best, best_t
+
+        if layouts is None:
+            d = self.describe()
+            plain_sparse = d["storage"] == STORAGES["sparse"] and not d["compact_image"]
+            layouts = list(LAYOUTS) if (plain_sparse and self._desc is not None) else []
+        layouts = [l for l in layouts if l in LAYOUTS]
+        if not layouts or self._desc is None:
+            best, _ = sweep_chunks()
+            self.default_chunk_size = best
+            return best
+        results = {}
+        for layout in layouts:
+            if layout != self.layout:
+                self.layout = layout
+                self._build()
+            results[layout] = sweep_chunks()
+        best_layout = min(results, key=lambda l: results[l][1])
+        if best_layout != self.layout:
+            self.layout = best_layout
+            self._build()
+        self.default_chunk_size = results[best_layout][0]
+        return self.default_chunk_size
 
 
 class GraphedPredictor:

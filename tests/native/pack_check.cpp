@@ -164,18 +164,18 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
     }
     for (int p = 0; p < v.n_trees; ++p) {
       const uint8_t* t = pf.q_nodes.data() + static_cast<size_t>(v.q_tree_stride) * p;
+      const size_t qnb = pf.view.q_has_cat ? 8 : 4;  // {node, category set} or node alone
       uint32_t i       = 1;
       for (int l = 0; l < D; ++l) {
         uint32_t node;
-        std::memcpy(&node, t + i * 4, 4);
+        std::memcpy(&node, t + i * qnb, 4);
         const uint32_t qq = q[(node & Q_FEATURE_FIELD) >> Q_FEATURE_SHIFT];
         bool right = static_cast<int32_t>(node - (qq << Q_RANK_SHIFT)) < 0;
         if (pf.view.q_has_cat) {
           // the kernel's arithmetic: OR of the rank comparison (never "right" on a categorical
           // node) and the bit-reversed category set shifted left by the code (0 from 32 up)
-          const size_t es = sizeof(T);
           uint32_t bits;
-          std::memcpy(&bits, t + (size_t(1) << D) * (4 + es) + i * 4, 4);
+          std::memcpy(&bits, t + i * qnb + 4, 4);
           const uint32_t shifted = qq < 32u ? bits << qq : 0u;
           right = right || (shifted >> 31) != 0u;
           // numerical nodes hold empty sets (a categorical node carries the largest rank)

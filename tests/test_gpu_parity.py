@@ -736,6 +736,26 @@ def test_optimize_picks_a_chunk_size_and_keeps_results():
     np.testing.assert_allclose(after, before, rtol=1e-5, atol=1e-6)
 
 
+def test_optimize_sweeps_node_orders_for_the_plain_sparse_kernel():
+    desc = random_forest_desc(92, n_trees=40, n_features=8, max_depth=11, p_leaf=0.2)
+    X = _dev(random_rows(13, 3000, 8, np.float32), "single")
+    want = oracle.predict(desc, X.cpu().numpy(), INFER_LEAF_ID, "single")
+    # without a compact image the node order matters: all three are tried by default
+    fi = ForestInference.load_from_treelite_model(desc, storage="sparse", compact_nodes=False,
+                                                  layout="layered")
+    best = fi.optimize(batch_size=1024, unique_batches=2, timeout=0.05)
+    assert best in (1, 2, 4, 8, 16, 32) and fi.layout in ("depth_first", "breadth_first", "layered")
+    assert fi.describe()["layout"] == {"depth_first": 0, "breadth_first": 1, "layered": 2}[fi.layout]
+    assert np.array_equal(fi.apply(X).cpu().numpy().astype(np.uint32), want)
+    # with it the sweep is skipped unless asked for
+    fc = ForestInference.load_from_treelite_model(desc, storage="sparse")
+    fc.optimize(batch_size=1024, unique_batches=2, timeout=0.05)
+    assert fc.layout == "depth_first"
+    fc.optimize(batch_size=1024, unique_batches=2, timeout=0.05, layouts=["breadth_first"])
+    assert fc.layout == "breadth_first"
+    assert np.array_equal(fc.apply(X).cpu().numpy().astype(np.uint32), want)
+
+
 def test_module_level_constructor_matches_reference_call():
     # the call cuML makes: python/cuml/cuml/ensemble/randomforest_common.pyx:402-409
     from cuml_b200 import fil as nvforest
