@@ -72,6 +72,9 @@ struct DenseQWalker {
     const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
     constexpr uint32_t QNB = CAT ? 8u : 4u;  // bytes per test node: {node, category set} or node
     const uint32_t width_b = (1u << D) * QNB;
+    // bytes per leaf payload: the element size, except where vector leaves sit in the tree block
+    const uint32_t lbytes  = MODE == MODE_SCALAR ? TR::ES : static_cast<uint32_t>(f.q_leaf_bytes);
+    const bool inline_vec  = MODE != MODE_SCALAR && lbytes > TR::ES;
     const uint32_t fstride = stride_b >> Q_FEATURE_SHIFT;  // R / 2 <= 128: fits a byte
     const int per_sub      = G * NT;
     const int per_batch    = per_sub * K;
@@ -219,11 +222,12 @@ struct DenseQWalker {
         // contiguous and leave as 16-byte stores: scalar 4-byte stores at a stride of a whole
         // output row cost one sector request each and bound these predictions otherwise.
         typename TR::Val val[NT];
+        uint32_t leaf_at[NT];
 #pragma unroll
         for (int k = 0; k < NT; ++k) {
-          const uint32_t slot   = idx[k] - (1u << D);
-          const uint32_t leaf_a = (TR::ES == 4 && !CAT) ? a[k] : base[k] + width_b + slot * TR::ES;
-          val[k]                = TR::ld_val(leaf_a);
+          const uint32_t slot = idx[k] - (1u << D);
+          leaf_at[k]          = base[k] + width_b + slot * lbytes;
+          val[k]              = TR::ld_val(leaf_at[k]);
         }
         const bool scalar_out = MODE == MODE_LEAFID || f.leaf_vector_len <= 1;
         const bool wide = FULL && NT == 4 && scalar_out && f.q_trees_in_order != 0 &&
@@ -253,6 +257,13 @@ struct DenseQWalker {
                   const int orig = __ldg(f.tree_orig + first + k);
                   static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = TR::low32(val[k]);
                 }
+              } else if (inline_vec) {
+                // per-tree outputs of vector leaves that sit in the tree block
+                if (row < p.n_rows) {
+                  const int orig = __ldg(f.tree_orig + first + k);
+                  T* out = static_cast<T*>(p.out) + (row * f.n_trees + orig) * f.n_outputs;
+                  for (int c = 0; c < f.n_outputs; ++c) out[c] = TR::ld_real(leaf_at[k] + c * TR::ES);
+                }
               } else {
                 take_leaf<T, MODE>(p, first + k, val[k], 0u, acc_group, R, r, row, run);
               }
@@ -266,7 +277,17 @@ struct DenseQWalker {
             // the leaf payloads follow the 2^D node words: for 4-byte payloads the heap
             // address of leaf slot j is exactly the address the walk ended on
             const uint32_t slot   = idx[k] - (1u << D);
-            const uint32_t leaf_a = (TR::ES == 4 && !CAT) ? a[k] : base[k] + width_b + slot * TR::ES;
+            const uint32_t leaf_a = (MODE == MODE_SCALAR && TR::ES == 4 && !CAT)
+                                      ? a[k]
+                                      : base[k] + width_b + slot * lbytes;
+            if (MODE == MODE_VECTOR && inline_vec) {
+              // the leaf's vector sits in the tree block: one sum per output, in registers
+#pragma unroll
+              for (int c = 0; c < kRegClasses; ++c) {
+                if (c < f.n_outputs) run.v[c] += TR::ld_real(leaf_a + c * TR::ES);
+              }
+              continue;
+            }
             const typename TR::Val payload = TR::ld_val(leaf_a);
             if (MODE == MODE_SCALAR && CAT && same_class) {
               run.sum += TR::as_real(payload);
@@ -402,7 +423,7 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
     const bool nans = __ldg(tile_flags + t) != 0;
     consumer_sync(n_ct);
     if (ok) ok = mbar_wait(bar_tfull, n_done & 1u);
-    Running<T> run{T(0), 0};
+    Running<T> run{T(0), 0, {}};
     if (ok) {
       if (nans) {
         ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR>::template walk<true>(
@@ -417,7 +438,7 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_tempty);
-    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    flush_running<T, MODE>(f, run, acc_group, R, r);
     consumer_sync(n_ct);
     if (MODE <= MODE_VECTOR) {
       if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);

@@ -382,11 +382,15 @@ constexpr int MODE_VECTOR  = 1;  // vector leaves, reduced outputs
 constexpr int MODE_PERTREE = 2;  // raw per-tree outputs
 constexpr int MODE_LEAFID  = 3;  // id of the leaf reached
 
-// Per-thread running state of the reduced modes.
+// Per-thread running state of the reduced modes: the sum of the class that scalar leaves are
+// currently feeding, or, for vector leaves of up to kRegClasses outputs, one sum per output
+// (forests with more outputs add every leaf vector to shared memory directly).
+constexpr int kRegClasses = kQInlineClasses;
 template <typename T>
 struct Running {
   T sum;
   int cls;
+  T v[kRegClasses];
 };
 
 // Consume one leaf.  `payload` is the leaf's scalar (as bits) or the index of its vector;
@@ -411,7 +415,16 @@ __device__ __forceinline__ void take_leaf(const PredictParams& p, int tree,
   } else if (MODE == MODE_VECTOR) {
     const T* lv = static_cast<const T*>(f.leaf_vectors) +
                   static_cast<size_t>(Traits<T>::low32(payload)) * NC;
-    for (int c = 0; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
+    if (NC <= kRegClasses) {
+      // few outputs (binary and small multi-class forests of vector leaves, i.e. every
+      // scikit-learn style random-forest classifier): sums stay in registers until the tile ends
+#pragma unroll
+      for (int c = 0; c < kRegClasses; ++c) {
+        if (c < NC) run.v[c] += __ldg(lv + c);
+      }
+    } else {
+      for (int c = 0; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
+    }
   } else if (MODE == MODE_PERTREE) {
     if (row < p.n_rows) {
       const int orig = __ldg(f.tree_orig + tree);
@@ -428,6 +441,20 @@ __device__ __forceinline__ void take_leaf(const PredictParams& p, int tree,
     if (row < p.n_rows) {
       const int orig = __ldg(f.tree_orig + tree);
       static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = __ldg(f.leaf_ids + leaf_id_index);
+    }
+  }
+}
+
+// Add a thread's running sums to its accumulators in shared memory (end of a row tile).
+template <typename T, int MODE>
+__device__ __forceinline__ void flush_running(const ForestView& f, const Running<T>& run,
+                                              T* acc_group, int R, int r)
+{
+  if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+  if (MODE == MODE_VECTOR && f.n_outputs <= kRegClasses) {
+#pragma unroll
+    for (int c = 0; c < kRegClasses; ++c) {
+      if (c < f.n_outputs) acc_group[c * R + r] += run.v[c];
     }
   }
 }

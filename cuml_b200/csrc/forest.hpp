@@ -136,6 +136,9 @@ constexpr uint32_t Q_MAX_RANK_FIELD = 0x3FFFu;  // j of a test that every code p
 // keep the three top nodes of every tree on the host: the traversal kernel takes them as a launch
 // parameter and reads them through the constant cache instead of shared memory.
 constexpr int kQTopTrees = 2048;
+// Vector leaves of forests with at most this many outputs are stored in the tree blocks of the
+// rank-quantised image (and summed in registers): the walk then never leaves shared memory.
+constexpr int kQInlineClasses = 4;
 
 // ---- compact image of a sparse forest -----------------------------------------------------------
 // Deep, ragged forests are bound by the chain of dependent node fetches from L2 / HBM.  Sparse
@@ -233,7 +236,11 @@ struct ForestView {
   int32_t q_n_groups;
   int32_t q_has_cat;            // 1: tree blocks carry a third array of 32-bit category sets
   int32_t q_trees_in_order;     // 1: packed tree t is the caller's tree t (tree_orig is the identity)
-  int64_t q_tree_stride;        // bytes between trees: 2^D * (node bytes + element size), 16-byte multiple
+  int32_t q_leaf_bytes;         // bytes per leaf payload: the element size (scalar, or index of the
+                                // leaf's vector), or n_outputs elements when the vectors of a
+                                // forest with few outputs sit in the tree blocks themselves
+  int32_t q_pad_;
+  int64_t q_tree_stride;        // bytes between trees: 2^D * (node bytes + leaf bytes), 16-byte multiple
   const void* q_nodes;          // [n_trees] blocks of [2^D nodes][2^D leaf payloads]; a node is a
                                 // uint32, or {uint32 node, uint32 category set} when q_has_cat
   const void* q_nodes_ids;      // same blocks with the leaf id (uint32) in every leaf payload slot:

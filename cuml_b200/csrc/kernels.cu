@@ -225,7 +225,7 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
     if (__any_sync(0xffffffffu, saw_nan) && lane == 0) flags[0] = 1;
     consumer_sync(n_ct);
     const bool nans = flags[0] != 0;
-    Running<T> run{T(0), 0};
+    Running<T> run{T(0), 0, {}};
     if (ok) {
       if (CAT || nans) {
         ok = DenseWalker<T, CAT, MODE, NT>::template walk<true>(
@@ -238,7 +238,7 @@ dense_kernel(const PredictParams p, const int R, const int G, const int S, const
       }
       if (!ok) atomicExch(p.status, 2);
     }
-    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    flush_running<T, MODE>(f, run, acc_group, R, r);
     consumer_sync(n_ct);
     if (MODE <= MODE_VECTOR) {
       if (threadIdx.x < R) {
@@ -616,7 +616,7 @@ sparse_kernel(const PredictParams p, const int R, const int G, const int rows_in
     __syncthreads();
     // rows past the end of the batch read row 0 of the tile's global memory when not staged
     const T* xrow = X + (row < p.n_rows ? row : row0) * p.row_stride;
-    Running<T> run{T(0), 0};
+    Running<T> run{T(0), 0, {}};
     for (int first = g * NT; first < f.n_trees; first += per_batch) {
       const int n_act = min(NT, f.n_trees - first);
       uint32_t idx[NT];
@@ -656,7 +656,7 @@ sparse_kernel(const PredictParams p, const int R, const int G, const int rows_in
         }
       }
     }
-    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    flush_running<T, MODE>(f, run, acc_group, R, r);
     __syncthreads();
     if (MODE <= MODE_VECTOR) {
       if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
@@ -774,8 +774,8 @@ size_t dense_q_smem(size_t qstride, int precision, int F, int NC, bool reduce, i
 int q_max_trees_in_flight(const ForestView& f, int mode)
 {
   if (f.q_has_cat) return 4;
-  const bool specialised = f.format == FMT_DENSE_F && mode == MODE_SCALAR && f.dense_depth >= 4 &&
-                           f.dense_depth <= 10;
+  const bool specialised = f.format == FMT_DENSE_F && (mode == MODE_SCALAR || mode == MODE_VECTOR) &&
+                           f.dense_depth >= 4 && f.dense_depth <= 10;
   return specialised ? 6 : 4;
 }
 
@@ -899,6 +899,11 @@ int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err
   if (can_pair && (pair == 1 || (pair < 0 && walks <= kPairWalkLimit))) {
     rec.kernel = "dense_q_pair_kernel";
     return launch_q_pair(L, err);
+  }
+  if (!f64 && mode == MODE_VECTOR && f.dense_depth >= 4 && f.dense_depth <= 10 &&
+      (L.c.trees_in_flight == 6 || L.c.trees_in_flight == 4)) {
+    rec.depth = f.dense_depth;
+    return launch_q_vec(L, err);
   }
   const bool specialised = !f64 && mode == MODE_SCALAR && f.dense_depth >= 4 && f.dense_depth <= 10;
   if (specialised && L.c.trees_in_flight == 6) {

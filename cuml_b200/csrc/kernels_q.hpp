@@ -32,6 +32,8 @@ int launch_q_plain6(const QLaunch& L, std::string& err);
 int launch_q_plain4(const QLaunch& L, std::string& err);
 // fp32, scalar leaves, no categorical tests, depth 9..10, two or three trees in flight.
 int launch_q_plain23(const QLaunch& L, std::string& err);
+// fp32, vector leaves, no categorical tests, depth 4..10, six or four trees in flight.
+int launch_q_vec(const QLaunch& L, std::string& err);
 // fp32, scalar leaves, no categorical tests, any depth, 1, 2 or 4 trees in flight: the walk that
 // fetches both children of a node ahead of the test (for launch shapes with few walks in flight).
 int launch_q_pair(const QLaunch& L, std::string& err);

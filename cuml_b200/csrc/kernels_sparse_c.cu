@@ -262,7 +262,7 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
     }
     consumer_sync(n_ct);
-    Running<T> run{T(0), 0};
+    Running<T> run{T(0), 0, {}};
     for (int b = 0; b < n_batches; ++b) {
       const uint32_t s = pos.stage;
       if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
@@ -403,7 +403,7 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       }
     }
     if (!ok) atomicExch(p.status, 2);
-    if (MODE == MODE_SCALAR) acc_group[run.cls * R + r] += run.sum;
+    flush_running<T, MODE>(f, run, acc_group, R, r);
     consumer_sync(n_ct);
     if (MODE <= MODE_VECTOR) {
       if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);

@@ -569,7 +569,12 @@ struct Packer {
     const size_t es      = sizeof(T);
     const int64_t width  = int64_t(1) << D;
     const int64_t qnb    = has_cat ? 8 : 4;  // bytes per test node in the quantised image
-    int64_t qstride      = width * static_cast<int64_t>(qnb + es);
+    // vector leaves of forests with few outputs go into the tree block itself: the traversal
+    // then reads them from shared memory instead of gathering them from global memory per
+    // (row, tree), which costs a divergent load each
+    const bool inline_vec = vec && d.n_outputs <= kQInlineClasses;
+    const int64_t lbytes  = inline_vec ? static_cast<int64_t>(d.n_outputs) * es : static_cast<int64_t>(es);
+    int64_t qstride       = width * static_cast<int64_t>(qnb + lbytes);
     qstride              = (qstride + 15) / 16 * 16;
     out.q_nodes.assign(static_cast<size_t>(qstride) * nt, 0);
     for (int p = 0; p < nt; ++p) {
@@ -606,16 +611,26 @@ struct Packer {
         }
         std::memcpy(dst + i * qnb, &node, 4);
       }
-      std::memcpy(dst + width * qnb, src + width * nb, static_cast<size_t>(width) * es);
+      if (!inline_vec) {
+        std::memcpy(dst + width * qnb, src + width * nb, static_cast<size_t>(width) * es);
+      } else {
+        for (int64_t sl = 0; sl < width; ++sl) {
+          uint32_t vi;  // index of the leaf's vector (low word of the dense payload)
+          std::memcpy(&vi, src + width * nb + sl * es, 4);
+          std::memcpy(dst + width * qnb + sl * lbytes,
+                      out.leaf_vectors.data() + static_cast<size_t>(vi) * d.n_outputs * es,
+                      static_cast<size_t>(lbytes));
+        }
+      }
     }
     // the same image with the leaf id in every payload slot, for predictions that report leaves
     out.q_nodes_ids = out.q_nodes;
     for (int p = 0; p < nt; ++p) {
       uint8_t* leaves = out.q_nodes_ids.data() + static_cast<size_t>(qstride) * p + width * qnb;
-      std::memset(leaves, 0, static_cast<size_t>(width) * es);
+      std::memset(leaves, 0, static_cast<size_t>(width) * lbytes);
       for (int64_t s = 0; s < width; ++s) {
         const uint32_t id = out.leaf_ids[static_cast<size_t>(width) * p + s];
-        std::memcpy(leaves + s * es, &id, 4);
+        std::memcpy(leaves + s * lbytes, &id, 4);
       }
     }
     bool in_order = true;
@@ -632,6 +647,7 @@ struct Packer {
     out.view.q_enabled     = 1;
     out.view.q_n_groups    = static_cast<int32_t>(out.q_groups.size());
     out.view.q_tree_stride = qstride;
+    out.view.q_leaf_bytes  = static_cast<int32_t>(lbytes);
     return true;
   }
 

@@ -187,6 +187,23 @@ int64_t walk_quantised(const PackedForest& pf, const T* X, int64_t n_rows, int64
       const uint32_t slot = i - (1u << D);
       const uint32_t id   = pf.leaf_ids[(static_cast<size_t>(p) << D) + slot];
       if (id != ids[r * v.n_trees + pf.tree_orig[p]]) ++bad;
+      // the image that reports leaves holds the same id in the payload slot
+      const size_t lbytes = static_cast<size_t>(v.q_leaf_bytes);
+      uint32_t id2;
+      std::memcpy(&id2, pf.q_nodes_ids.data() + static_cast<size_t>(v.q_tree_stride) * p +
+                          (size_t(1) << D) * qnb + slot * lbytes, 4);
+      if (id2 != id) ++bad;
+      if (lbytes > sizeof(T)) {
+        // vector leaves stored in the tree block: the same values as the forest's vector table
+        const uint8_t* dense_leaf = pf.nodes.data() + static_cast<size_t>(v.tree_stride) * p +
+                                    (size_t(1) << D) * (sizeof(T) == 4 ? 8 : 16) + slot * sizeof(T);
+        uint32_t vi;
+        std::memcpy(&vi, dense_leaf, 4);
+        if (std::memcmp(t + (size_t(1) << D) * qnb + slot * lbytes,
+                        pf.leaf_vectors.data() + static_cast<size_t>(vi) * v.n_outputs * sizeof(T),
+                        lbytes) != 0)
+          ++bad;
+      }
     }
   }
   return bad;
