@@ -6,11 +6,12 @@
 // a time.  Every walk has two parts:
 //   1. the top T levels of the tree are a complete heap that a producer warp streams through a
 //      ring of shared-memory stages (bulk copies from the L2-resident heap array; one stage =
-//      the heaps of G * NT trees): T steps without a global fetch, then one exit word that names
-//      the internal node to continue at, or the leaf reached;
+//      the heaps of G * NT trees): T steps without a global fetch, then one exit {k, L} that names
+//      the internal node to continue at and the leaves before it, or the leaf reached;
 //   2. below the heap the walk follows the compact nodes in global memory: 8-byte internal
-//      nodes, left child adjacent, (k, L) bookkeeping for the leaf number.  Every step first
-//      issues the node fetches of all NT walks, then advances them without branches.
+//      nodes, first child adjacent, (k, L) bookkeeping for the leaf number, nodes fetched as
+//      aligned 16-byte pairs so that a step from an even node to its first child needs no fetch.
+//      Every step first issues the fetches of all NT walks, then advances them.
 // A stage is released as soon as the warp has left the heaps, before it starts on part 2, so the
 // next batch of heaps arrives while the warps wait for their node fetches.
 // The row tile holds floats also for fp64 forests: every value is rounded DOWN to float when the

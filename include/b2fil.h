@@ -231,8 +231,9 @@ int b2fil_last_variant(char* buf, size_t buf_bytes);
  * "compact_R", "compact_G", "compact_S"
  * force the launch shape of the kernel over the compact image of sparse forests (rows per tile,
  * tree groups, ring depth; 0 = automatic), "compact_load" picks the cache policy of its node
- * fetches (0 read-only path, 1 L2 only, 2 read-only path without L1 allocation), "compact_top"
- * caps the heap levels of compact images packed afterwards.  Unknown keys are stored and ignored.
+ * fetches (0 read-only path, 1 L2 only - the default -, 2 read-only path without L1 allocation,
+ * 3 L2 only with eviction hints: nodes evict-last, rows and leaves evict-first).  Unknown keys are
+ * stored and ignored.
  * No counterpart in the reference. */
 int b2fil_set_tuning(const char* key, int value);
 
