@@ -90,9 +90,9 @@ def _cpu_and_parity(desc, Xd, gpu_out, kind, precision, sample_rows, seconds=4.0
     cores = os.cpu_count() or 1
     n = int(Xd.shape[0])
     probe = Xd[:min(n, 2048)].cpu().numpy()
-    oracle.predict(desc, probe[:64], kind, precision, n_threads=cores)
+    oracle.predict(desc, probe[:64], kind, precision, n_threads=cores, packed=True)
     t0 = time.perf_counter()
-    oracle.predict(desc, probe, kind, precision, n_threads=cores)
+    oracle.predict(desc, probe, kind, precision, n_threads=cores, packed=True)
     rate = probe.shape[0] / max(1e-9, time.perf_counter() - t0)
     m = int(max(256, min(n, sample_rows, rate * seconds)))
     # evenly spread rows, first and last included
@@ -101,16 +101,22 @@ def _cpu_and_parity(desc, Xd, gpu_out, kind, precision, sample_rows, seconds=4.0
 
     sel = torch.as_tensor(idx, device=Xd.device)
     Xs = Xd[sel].cpu().numpy()
+    # timed: the packed walk (one record per node, eight rows side by side); checked against
+    # the plain walk, which is the one the tests pin, on the head of the sample
     t0 = time.perf_counter()
-    want = oracle.predict(desc, Xs, kind, precision, n_threads=cores)
+    want = oracle.predict(desc, Xs, kind, precision, n_threads=cores, packed=True)
     dt = time.perf_counter() - t0
+    head = min(idx.size, 2000)
+    walks_agree = bool(np.array_equal(
+        want[:head], oracle.predict(desc, Xs[:head], kind, precision, n_threads=cores)))
     got = gpu_out[sel].cpu().numpy()
     tol = dict(rtol=1e-5, atol=1e-6) if precision == "single" else dict(rtol=1e-12, atol=1e-12)
     if precision == "double":
         tol["atol"] *= max(1.0, float(np.abs(want).max()))
     ok = bool(np.allclose(got, want, **tol))
     rec = {"cpu": {"value": idx.size / dt, "unit": "rows/s", "cores": cores, "kind": "port",
-                   "sample": f"{idx.size} of {n} rows, same forest, {cores} OpenMP threads"},
+                   "sample": f"{idx.size} of {n} rows, same forest, {cores} OpenMP threads, "
+                             "packed node records", "agrees_with_plain_walk": walks_agree},
            "parity": {"rows_checked": int(idx.size), "scores_within_tolerance": ok,
                       "max_abs_diff": float(np.abs(got.astype(np.float64) - want).max())}}
     if ids_out is not None:

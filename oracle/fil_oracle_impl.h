@@ -56,6 +56,71 @@ static inline int32_t FN(find_leaf)(const b2fil_forest_desc* d, int t, const REA
   return n;
 }
 
+/* ---- packed walk --------------------------------------------------------------------------------
+ * The same traversal over a packed copy of the forest: one 24-byte (fp32) / 32-byte (fp64) record
+ * per node instead of five parallel arrays, and eight rows walked side by side through a tree so
+ * that their dependent loads overlap.  Same operators, same missing-value rule, same leaves as
+ * find_leaf above; it exists so that the CPU baseline that bench.py reports is not slowed down by
+ * the structure-of-arrays description, which is a convenient input format and a poor layout to
+ * traverse.  Forests with categorical tests keep the plain walk.  tests/test_oracle.py checks the
+ * two walks against each other. */
+typedef struct {
+  REAL thr;
+  int32_t feat;
+  int32_t left, right;
+  uint8_t leaf, default_left, op, pad;
+} FN(pnode);
+
+static FN(pnode)* FN(pack_nodes)(const b2fil_forest_desc* d)
+{
+  const int64_t total = d->tree_offsets[d->n_trees];
+  for (int64_t g = 0; g < total; ++g)
+    if (d->node_kind[g] == B2FIL_NODE_CATEGORICAL) return NULL;
+  FN(pnode)* p = (FN(pnode)*)malloc(sizeof(FN(pnode)) * (size_t)(total > 0 ? total : 1));
+  if (!p) return NULL;
+  for (int64_t g = 0; g < total; ++g) {
+    p[g].thr          = (REAL)d->threshold[g];
+    p[g].feat         = d->feature[g];
+    p[g].left         = d->left[g];
+    p[g].right        = d->right[g];
+    p[g].leaf         = d->node_kind[g] == B2FIL_NODE_LEAF;
+    p[g].default_left = d->default_left[g] != 0;
+    p[g].op           = (uint8_t)(d->op ? d->op[g] : d->op_all);
+    p[g].pad          = 0;
+  }
+  return p;
+}
+
+#define OR_LANES 8
+/* Leaves of rows r0 .. r0+n-1 (n <= OR_LANES) in tree t. */
+static inline void FN(find_leaves_packed)(const FN(pnode)* nodes, int64_t base, const REAL* X,
+                                          int64_t row_stride, int64_t r0, int n, int32_t* leaf)
+{
+  int32_t at[OR_LANES];
+  for (int j = 0; j < n; ++j) at[j] = 0;
+  for (;;) {
+    int walking = 0;
+    for (int j = 0; j < n; ++j) {
+      const FN(pnode)* nd = nodes + base + at[j];
+      if (nd->leaf) continue;
+      const REAL x = X[(r0 + j) * row_stride + nd->feat];
+      const REAL t = nd->thr;
+      int cond;
+      switch (nd->op) {
+        case B2FIL_OP_LT: cond = x < t; break;
+        case B2FIL_OP_LE: cond = x <= t; break;
+        case B2FIL_OP_GT: cond = x > t; break;
+        default: cond = x >= t; break;
+      }
+      if (x != x) cond = nd->default_left;
+      at[j]   = cond ? nd->left : nd->right;
+      walking = 1;
+    }
+    if (!walking) break;
+  }
+  for (int j = 0; j < n; ++j) leaf[j] = at[j];
+}
+
 /* Postprocessing of one row of summed outputs (Treelite postprocessor names; cuML sets
  * "identity" / "identity_multiclass": cpp/src/randomforest/randomforest.cu:263,267). */
 static void FN(postprocess)(const b2fil_forest_desc* d, double* s)
@@ -100,7 +165,7 @@ static void FN(postprocess)(const b2fil_forest_desc* d, double* s)
 
 int FN(fil_oracle_predict)(const b2fil_forest_desc* d, int infer_kind, const REAL* X,
                            int64_t n_rows, int64_t row_stride, void* out, double threshold,
-                           int n_threads)
+                           int n_threads, int packed_walk)
 {
   const int k       = d->n_outputs;
   const int vec     = d->leaf_vector_len > 1;
@@ -119,6 +184,7 @@ int FN(fil_oracle_predict)(const b2fil_forest_desc* d, int infer_kind, const REA
   }
   const int64_t n_blocks = (n_rows + OR_BLOCK - 1) / OR_BLOCK;
   int failed             = 0;
+  FN(pnode)* packed      = packed_walk ? FN(pack_nodes)(d) : NULL;
   if (n_threads < 1) n_threads = 1;
 #pragma omp parallel num_threads(n_threads)
   {
@@ -139,9 +205,14 @@ int FN(fil_oracle_predict)(const b2fil_forest_desc* d, int infer_kind, const REA
         /* scalar leaf of a multi-output forest adds to class_id[t]; implicit convention
          * tree_idx % num_class: cpp/src/explainer/tree_shap.cu:589 */
         const int cls = vec ? -1 : (d->class_id ? d->class_id[t] : t % k);
+        int32_t lanes[OR_LANES];
         for (int i = 0; i < nb; ++i) {
-          const int64_t r  = r0 + i;
-          const int32_t lf = FN(find_leaf)(d, t, X + r * row_stride);
+          const int64_t r = r0 + i;
+          if (packed && i % OR_LANES == 0) {
+            const int n = nb - i < OR_LANES ? nb - i : OR_LANES;
+            FN(find_leaves_packed)(packed, base, X, row_stride, r, n, lanes);
+          }
+          const int32_t lf = packed ? lanes[i % OR_LANES] : FN(find_leaf)(d, t, X + r * row_stride);
           if (infer_kind == B2FIL_INFER_LEAF_ID) {
             ((uint32_t*)out)[r * n_trees + t] = (uint32_t)lf;
           } else if (infer_kind == B2FIL_INFER_PER_TREE) {
@@ -195,5 +266,6 @@ int FN(fil_oracle_predict)(const b2fil_forest_desc* d, int infer_kind, const REA
     free(acc);
   }
   free(divisor);
+  free(packed);
   return failed ? -5 : 0;
 }

@@ -145,3 +145,32 @@ def test_empty_batch_and_single_leaf_tree():
     X = np.zeros((2, desc.n_features), np.float32)
     ids = oracle.predict(desc, X, INFER_LEAF_ID, "single")
     assert np.array_equal(ids, np.zeros((2, 3), np.uint32))
+
+
+def test_packed_walk_equals_plain_walk():
+    """The packed walk (one record per node, eight rows side by side) is what the benchmarks time
+    as the CPU baseline; it must give exactly what the plain walk gives, for every output kind."""
+    from cuml_b200.fil._desc import (INFER_CLASS, INFER_DEFAULT, INFER_LEAF_ID, INFER_PER_TREE,
+                                     INFER_PROBA2)
+    from tests.helpers import load_golden, random_forest_desc, random_rows
+
+    cases = [
+        (random_forest_desc(1, n_trees=15, max_depth=7, mixed_ops=True, integer_thresholds=True,
+                            postproc="sigmoid"), dict(integer=True, nan_frac=0.15)),
+        (random_forest_desc(2, n_trees=9, n_outputs=3, vector=True, average=True), dict()),
+        (random_forest_desc(3, n_trees=12, n_outputs=4, postproc="softmax", base=True), dict()),
+        (random_forest_desc(4, n_trees=8, categorical=True), dict(categories=22)),  # plain fallback
+    ]
+    for desc, kw in cases:
+        X = random_rows(7, 203, desc.n_features, np.float64, **kw)  # 203: ragged last group of rows
+        for precision in ("single", "double"):
+            kinds = [INFER_DEFAULT, INFER_LEAF_ID, INFER_PER_TREE, INFER_CLASS]
+            if desc.n_outputs == 1:
+                kinds.append(INFER_PROBA2)
+            for kind in kinds:
+                a = oracle.predict(desc, X, kind, precision)
+                b = oracle.predict(desc, X, kind, precision, packed=True)
+                assert np.array_equal(a, b, equal_nan=True)
+    desc, X, exp = load_golden("rfr_depth20")
+    assert np.array_equal(oracle.predict(desc, X, INFER_LEAF_ID, "double", packed=True).astype(np.int64),
+                          exp["leaf_ids"])
