@@ -52,7 +52,6 @@ struct CompactCfg {
   size_t smem_bytes;
   int threads;
   int grid;
-  int node_load;      // how nodes below the heap are fetched (NodeLoad in kernels_sparse_c.cu)
 };
 // Value of a named tuning knob (b2fil_set_tuning), or `fallback` when it was never set.
 int tuning_value(const char* key, int fallback);

@@ -36,118 +36,129 @@ __device__ __forceinline__ void lds_node(uint32_t a, uint32_t& value, uint32_t& 
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(value), "=r"(meta) : "r"(a));
 }
 
-// How the walk below the heap fetches its nodes from global memory.  The fetches of a warp go to
-// 32 unrelated cache lines and nothing is reused, so what matters is how many of them the SM can
-// keep in flight; the L1 allocation policy of the load decides that.
-enum NodeLoad : int { kLoadNc = 0, kLoadCg = 1, kLoadNoAllocate = 2, kLoadCgKeep = 3 };
-
-// L2 cache policies: the node array is read over and over and should stay (evict last); rows and
-// leaf payloads are read once (evict first).
-__device__ __forceinline__ uint64_t l2_policy_evict_last()
+// One aligned 16-byte fetch = nodes 2m and 2m + 1, issued only where `wanted`; the registers keep
+// their contents otherwise.  A predicated instruction rather than a branch: the walks of a warp
+// want their fetches at different steps, and a branch per fetch costs more issue slots than the
+// fetch.  L2-only (.cg): the fetches of a warp go to 32 unrelated lines and nothing is reused, so
+// the L1 should only track the misses in flight (measured 4 to 8 % faster than the read-only
+// path; L2 eviction hints measured slower).
+__device__ __forceinline__ void ld_compact_pair_if(bool wanted, const void* ptr, uint32_t& x,
+                                                   uint32_t& y, uint32_t& z, uint32_t& w)
 {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first()
-{
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint2 ld_compact_node(const uint2* ptr, int kind, uint64_t keep)
-{
-  uint2 v;
-  if (kind == kLoadCgKeep) {
-    asm volatile("ld.global.cg.L2::cache_hint.v2.u32 {%0, %1}, [%2], %3;"
-                 : "=r"(v.x), "=r"(v.y)
-                 : "l"(ptr), "l"(keep));
-  } else if (kind == kLoadCg) {
-    asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
-  } else if (kind == kLoadNoAllocate) {
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];"
-                 : "=r"(v.x), "=r"(v.y)
-                 : "l"(ptr));
-  } else {
-    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
-  }
-  return v;
-}
-// One aligned 16-byte load = nodes 2m and 2m + 1.
-__device__ __forceinline__ uint4 ld_compact_pair(const uint4* ptr, int kind, uint64_t keep)
-{
-  uint4 v;
-  if (kind == kLoadCgKeep) {
-    asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(ptr), "l"(keep));
-  } else if (kind == kLoadCg) {
-    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(ptr));
-  } else if (kind == kLoadNoAllocate) {
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(ptr));
-  } else {
-    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(ptr));
-  }
-  return v;
+  asm volatile(
+    "{\n\t"
+    ".reg .pred want;\n\t"
+    "setp.ne.u32 want, %5, 0;\n\t"
+    "@want ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];\n\t"
+    "}"
+    : "+r"(x), "+r"(y), "+r"(z), "+r"(w)
+    : "l"(ptr), "r"(static_cast<uint32_t>(wanted)));
 }
 
-// Does the row go right at a compact node?  `xl` is the row's value rounded down to float;
-// `exact_index()` yields the internal node whose exact threshold settles an fp64 test that the
-// float bound leaves open (C_NO_NODE: none, heap padding).
-template <typename T, bool CAT, typename ExactIndex>
-__device__ __forceinline__ bool compact_goes_right(uint32_t value, uint32_t meta, float xl,
-                                                   uint32_t feat, int64_t row,
-                                                   const PredictParams& p, ExactIndex exact_index)
+// A test is the float compare xl < lo, where xl is the row's value rounded down to float and lo
+// the node's float (fp64 forests: the largest float <= threshold).  It is OPEN when that compare
+// does not settle it: the value is missing, or, in an fp64 forest, xl == lo (lo <= x < next float:
+// only the doubles know).  One compare instruction (equal-or-unordered) finds both.
+template <typename T>
+__device__ __forceinline__ bool test_is_open(float xl, float lo)
 {
-  const ForestView& f = p.f;
-  if (CAT && (meta & META_CATEGORICAL)) return goes_right<float, true, true>(value, meta, xl, f);
-  const float lo = __uint_as_float(value);  // fp64 forests: largest float <= threshold
-  bool left      = xl < lo;
-  if constexpr (sizeof(T) == 8) {
-    if (xl == lo) {
-      // lo <= x < next float: only the doubles know
-      const uint32_t k = exact_index();
-      if (k != C_NO_NODE) {
-        const double x = row < p.n_rows
-                           ? __ldg(static_cast<const double*>(p.X) + row * p.row_stride + feat)
-                           : 0.0;  // rows past the end of the batch were staged as zeros
-        left = x < __ldg(f.c_exact + k);
-      }
-    }
-  }
-  if (xl != xl) left = (meta & META_DEFAULT_LEFT) != 0u;
-  return !left;
+  if constexpr (sizeof(T) == 8) return !(xl < lo || xl > lo);
+  return xl != xl;
 }
+
+// Exact form of an fp64 test that the floats left open.  `k` is the internal node whose exact
+// threshold settles it (C_NO_NODE: none, heap padding: the row goes right).
+__device__ __noinline__ bool compact_exact_left(const double* row_values, const double* exact,
+                                                uint32_t k, uint32_t feat)
+{
+  if (k == C_NO_NODE) return false;
+  // rows past the end of the batch (no values) were staged as zeros
+  const double x = row_values != nullptr ? __ldg(row_values + feat) : 0.0;
+  return x < __ldg(exact + k);
+}
+
+// Settle an open test off the common path and rewrite (xl, lo) so that the plain compare
+// xl < lo gives the answer.
+template <typename T, typename ExactIndex>
+__device__ __forceinline__ void settle_open_test(float& xl, float& lo, uint32_t meta, uint32_t feat,
+                                                 const double* row_values, const double* exact,
+                                                 ExactIndex exact_index)
+{
+  if (!test_is_open<T>(xl, lo)) return;
+  bool left = false;  // fp32 forests: xl == lo is x == threshold, which goes right
+  if (xl != xl) {
+    left = (meta & META_DEFAULT_LEFT) != 0u;
+  } else if constexpr (sizeof(T) == 8) {
+    left = compact_exact_left(row_values, exact, exact_index(), feat);
+  }
+  lo = 0.f;
+  xl = left ? -1.f : 1.f;
+}
+
+// A categorical test, also rewritten into (xl, lo).
+__device__ __forceinline__ void settle_categorical_test(float& xl, float& lo, uint32_t value,
+                                                        uint32_t meta, const ForestView& f)
+{
+  const bool right = goes_right<float, true, true>(value, meta, xl, f);
+  lo               = 0.f;
+  xl               = right ? 1.f : -1.f;
+}
+
+// One step of a walk below the heap, after its test operands (xl, lo) are known.  State: k = the
+// node the walk is on (bit 31 set once it has reached its leaf), L = leaves before the walk's
+// position, {x, y, z, w} = the aligned pair of nodes that holds node k.  The step takes the
+// branch, moves (k, L), and fetches the pair of the new node when that is a different pair: a
+// first child reached from an even node is the neighbour already held.  Predicate logic all the
+// way, no branch; written in PTX because the C++ form of the same step compiled to 2.5 times the
+// instructions (flags kept as integers and re-tested), and issue slots are what the walk is
+// short of.
+__device__ __forceinline__ void compact_step(uint32_t& k, uint32_t& L, uint32_t& x, uint32_t& y,
+                                             uint32_t& z, uint32_t& w, float xl, float lo,
+                                             uint32_t meta, int off_shift, const void* nodes)
+{
+  asm volatile(
+    "{\n\t"
+    ".reg .pred lt, sw, second, leaf, live, ls, go, want;\n\t"
+    ".reg .u32 t, off, hop, kn;\n\t"
+    ".reg .u64 a;\n\t"
+    "setp.lt.f32 lt, %6, %7;\n\t"
+    "and.b32 t, %8, 0x08000000;\n\t"  // CMETA_SWAPPED
+    "setp.ne.u32 sw, t, 0;\n\t"
+    "xor.pred second, lt, sw;\n\t"
+    "not.pred second, second;\n\t"    // second child = (left == swapped)
+    "shl.b32 off, %8, 5;\n\t"
+    "shr.u32 off, off, %9;\n\t"
+    "selp.u32 t, 0x10000000, 0x20000000, second;\n\t"  // CMETA_SECOND_LEAF, CMETA_FIRST_LEAF
+    "and.b32 t, t, %8;\n\t"
+    "setp.ne.u32 leaf, t, 0;\n\t"
+    "setp.ge.s32 live, %0, 0;\n\t"
+    "and.pred ls, live, second;\n\t"
+    "@ls add.u32 %1, %1, off;\n\t"    // the second child skips the leaves of the first
+    "selp.u32 hop, off, 1, second;\n\t"
+    "and.pred go, live, !leaf;\n\t"
+    "add.u32 kn, %0, hop;\n\t"
+    "xor.b32 t, kn, %0;\n\t"
+    "setp.gt.u32 want, t, 1;\n\t"     // another pair
+    "and.pred want, want, go;\n\t"
+    "@!go or.b32 %0, %0, 0x80000000;\n\t"
+    "@go mov.u32 %0, kn;\n\t"
+    "and.b32 t, kn, 0x7ffffffe;\n\t"
+    "mad.wide.u32 a, t, 8, %10;\n\t"
+    "@want ld.global.cg.v4.u32 {%2, %3, %4, %5}, [a];\n\t"
+    "}"
+    : "+r"(k), "+r"(L), "+r"(x), "+r"(y), "+r"(z), "+r"(w)
+    : "f"(xl), "f"(lo), "r"(meta), "r"(off_shift), "l"(nodes));
+}
+static_assert(CMETA_SWAPPED == 0x08000000u && CMETA_SECOND_LEAF == 0x10000000u &&
+                CMETA_FIRST_LEAF == 0x20000000u && C_EXIT_LEAF == 0x80000000u,
+              "compact_step spells these constants out");
 
 // Stage rows [row0, row0 + R) feature-major as floats (fp64 inputs rounded down).  A warp reads 32
 // consecutive features of one row and scatters them to 32 different banks.  Rows past the end of
 // the batch become zeros.
 template <typename T>
-__device__ __forceinline__ T ld_once(const T* ptr, uint64_t once)
-{
-  T v;
-  if constexpr (sizeof(T) == 8) {
-    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b64 %0, [%1], %2;"
-                 : "=l"(reinterpret_cast<uint64_t&>(v))
-                 : "l"(ptr), "l"(once));
-  } else {
-    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;"
-                 : "=r"(reinterpret_cast<uint32_t&>(v))
-                 : "l"(ptr), "l"(once));
-  }
-  return v;
-}
-
-template <typename T>
 __device__ __forceinline__ void stage_rows_as_float(const PredictParams& p, uint32_t tile, int R,
-                                                    int64_t row0, int warp, int lane, int n_warps,
-                                                    bool hint, uint64_t once)
+                                                    int64_t row0, int warp, int lane, int n_warps)
 {
   const int F             = p.f.n_features;
   const uint32_t stride_b = (R + 1) * 4u;
@@ -159,7 +170,7 @@ __device__ __forceinline__ void stage_rows_as_float(const PredictParams& p, uint
     for (int c = lane; c < F; c += 32) {
       float v = 0.f;
       if (live) {
-        const T raw = hint ? ld_once(src + c, once) : __ldg(src + c);
+        const T raw = __ldg(src + c);
         if constexpr (sizeof(T) == 8) {
           v = __double2float_rd(raw);
         } else {
@@ -174,8 +185,7 @@ __device__ __forceinline__ void stage_rows_as_float(const PredictParams& p, uint
 // Shared memory: [mbarriers 256 B][row tile][accumulators][16 B][S stages of G * NT heaps].
 template <typename T, bool CAT, int MODE, int NT, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1)
-sparse_compact_kernel(const PredictParams p, const int R, const int G, const int S,
-                      const int node_load)
+sparse_compact_kernel(const PredictParams p, const int R, const int G, const int S)
 {
   using TR  = Traits<T>;
   using Val = typename TR::Val;
@@ -251,26 +261,27 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
   T* acc_group            = acc + static_cast<size_t>(g) * NC * R;
   const uint32_t row_addr = tile + r * 4u;
   const CompactNode* __restrict__ nodes = f.c_nodes;
-  const uint64_t keep  = l2_policy_evict_last();
-  const uint64_t once  = l2_policy_evict_first();
   RingPos pos;
   bool ok = true;
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     const int64_t row0 = t * R;
     const int64_t row  = row0 + r;
-    stage_rows_as_float<T>(p, tile, R, row0, warp, lane, n_cw, node_load == kLoadCgKeep, once);
+    stage_rows_as_float<T>(p, tile, R, row0, warp, lane, n_cw);
     if (MODE <= MODE_VECTOR) {
       for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
     }
     consumer_sync(n_ct);
     Running<T> run{T(0), 0, {}};
+    // the row's doubles, for the tests that the float tile leaves open
+    auto row_values = [&]() -> const double* {
+      return row < p.n_rows ? static_cast<const double*>(p.X) + row * p.row_stride : nullptr;
+    };
     for (int b = 0; b < n_batches; ++b) {
       const uint32_t s = pos.stage;
       if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
       const int first = b * per_batch + g * NT;
       const int n_act = ok ? min(NT, f.n_trees - first) : 0;
-      uint32_t k[NT], L[NT];
-      bool live[NT];
+      uint32_t k[NT], L[NT];  // bit 31 of k: the walk has reached its leaf, L is its number
       if (n_act > 0) {
         // part 1: the heaps in shared memory
         uint32_t base[NT], h[NT];
@@ -283,27 +294,39 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
         }
         for (int lvl = 0; lvl < TL; ++lvl) {
           uint32_t value[NT], meta[NT];
+          float xl[NT], lo[NT];
+          bool any_open = false;
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) lds_node(base[kk] + h[kk] * 8u, value[kk], meta[kk]);
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) {
-            const uint32_t feat = meta[kk] & CMETA_LOW27;
-            const float xl      = Traits<float>::ld_real(feat * stride_b + row_addr);
-            const bool right    = compact_goes_right<T, CAT>(value[kk], meta[kk], xl, feat, row, p, [&]() {
-              const size_t tree = static_cast<size_t>(first + min(kk, n_act - 1));
-              return __ldg(f.c_top_src + tree * heap_n + h[kk]);
-            });
-            h[kk] = 2u * h[kk] + (right ? 1u : 0u);
+            xl[kk] = Traits<float>::ld_real((meta[kk] & CMETA_LOW27) * stride_b + row_addr);
+            lo[kk] = __uint_as_float(value[kk]);
+            if (CAT && (meta[kk] & META_CATEGORICAL))
+              settle_categorical_test(xl[kk], lo[kk], value[kk], meta[kk], f);
+            any_open |= test_is_open<T>(xl[kk], lo[kk]);
           }
+          if (any_open) {
+#pragma unroll
+            for (int kk = 0; kk < NT; ++kk) {
+              settle_open_test<T>(xl[kk], lo[kk], meta[kk], meta[kk] & CMETA_LOW27, row_values(),
+                                  f.c_exact, [&]() {
+                                    const size_t tree = static_cast<size_t>(first + min(kk, n_act - 1));
+                                    return __ldg(f.c_top_src + tree * heap_n + h[kk]);
+                                  });
+            }
+          }
+#pragma unroll
+          for (int kk = 0; kk < NT; ++kk) h[kk] = 2u * h[kk] + (xl[kk] < lo[kk] ? 0u : 1u);
         }
 #pragma unroll
         for (int kk = 0; kk < NT; ++kk) {
           // the exits follow the 2^T node slots: exit e sits at 8 * (2^T + e) = 8 * h
           uint32_t ek, eL;
           lds_node(base[kk] + h[kk] * 8u, ek, eL);
-          live[kk] = (ek & C_EXIT_LEAF) == 0u;
-          k[kk]    = live[kk] ? ek : 0u;  // a finished walk keeps fetching node 0: harmless
-          L[kk]    = live[kk] ? eL : (ek & ~C_EXIT_LEAF);  // leaves before k, or the leaf itself
+          const bool done = (ek & C_EXIT_LEAF) != 0u;
+          k[kk]           = ek;                              // an exit that is a leaf carries bit 31
+          L[kk]           = done ? (ek & ~C_EXIT_LEAF) : eL;  // the leaf itself, or leaves before k
         }
       }
       // the heaps of this batch are no longer needed: let the producer refill the stage
@@ -312,76 +335,62 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       pos.advance(S);
       if (n_act > 0) {
         // part 2: compact nodes in global memory
-        // Nodes come in aligned pairs {2m, 2m + 1}.  The first child of node k is node k + 1, so
-        // a walk that sits on an even node and goes to its first child already holds the next
-        // node and skips the fetch: lanes that skip touch no cache line, and the L1's line
-        // look-ups are what bounds this loop.  A walk on an even node loads the pair (16 bytes),
-        // a walk on an odd node only its own node (8 bytes): no selects afterwards.
-        uint32_t cv[NT], cm[NT], nv[NT], nm[NT];  // current node, and its neighbour when k is even
-        bool need[NT];
+        // Nodes come in aligned pairs {2m, 2m + 1} and a walk holds the pair of its node.  The
+        // first child of node k is node k + 1, so a walk that sits on an even node and goes to its
+        // first child already holds the next node and skips the fetch: lanes that skip touch no
+        // cache line.  A step is straight-line code: the operands of the NT tests, one rarely
+        // taken branch for tests that the floats leave open, then NT times compact_step, which
+        // ends in the (predicated) fetch for the next step.
+        uint32_t pair[NT][4];
+        const uint2* node_ptr = reinterpret_cast<const uint2*>(nodes);
 #pragma unroll
         for (int kk = 0; kk < NT; ++kk) {
-          need[kk] = live[kk];
-          cv[kk] = cm[kk] = nv[kk] = nm[kk] = 0u;
+          // a walk that ended in the heap keeps a node that no value ties with
+          pair[kk][0] = pair[kk][2] = 0x00800001u;
+          pair[kk][1] = pair[kk][3] = 0u;
+          ld_compact_pair_if(static_cast<int32_t>(k[kk]) >= 0, node_ptr + (k[kk] & 0x7ffffffeu),
+                             pair[kk][0], pair[kk][1], pair[kk][2], pair[kk][3]);
         }
-        const uint2* node_ptr = reinterpret_cast<const uint2*>(nodes);
-        const int off_shift   = 5 + fb;  // the offset sits between the five flag bits and the feature
+        const int off_shift = 5 + fb;  // the offset sits between the five flag bits and the feature
         for (int step = 0; step < f.c_bottom_steps; ++step) {
+          uint32_t value[NT], meta[NT];
+          float xl[NT], lo[NT];
+          bool any_open = false;
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) {
-            if (need[kk]) {
-              if (k[kk] & 1u) {
-                const uint2 one = ld_compact_node(node_ptr + k[kk], node_load, keep);
-                cv[kk]          = one.x;
-                cm[kk]          = one.y;
-              } else {
-                const uint4 two = ld_compact_pair(reinterpret_cast<const uint4*>(node_ptr + k[kk]), node_load, keep);
-                cv[kk]          = two.x;
-                cm[kk]          = two.y;
-                nv[kk]          = two.z;
-                nm[kk]          = two.w;
-              }
-            }
+            const bool odd = (k[kk] & 1u) != 0u;
+            value[kk]      = odd ? pair[kk][2] : pair[kk][0];
+            meta[kk]       = odd ? pair[kk][3] : pair[kk][1];
+            xl[kk]         = Traits<float>::ld_real((meta[kk] & feat_mask) * stride_b + row_addr);
+            lo[kk]         = __uint_as_float(value[kk]);
+            if (CAT && (meta[kk] & META_CATEGORICAL))
+              settle_categorical_test(xl[kk], lo[kk], value[kk], meta[kk], f);
+            any_open |= test_is_open<T>(xl[kk], lo[kk]);
           }
-          bool walking = false;
+          if (any_open) {
 #pragma unroll
-          for (int kk = 0; kk < NT; ++kk) {
-            const uint32_t meta = cm[kk];
-            const uint32_t feat = meta & feat_mask;
-            const float xl      = Traits<float>::ld_real(feat * stride_b + row_addr);
-            const uint32_t kx   = k[kk];
-            const bool right    = compact_goes_right<T, CAT>(cv[kk], meta, xl, feat, row, p,
-                                                             [&]() { return kx; });
-            const bool second   = right != ((meta & CMETA_SWAPPED) != 0u);
-            const uint32_t off  = (meta << 5) >> off_shift;
-            const bool at_leaf  = (meta & (second ? CMETA_SECOND_LEAF : CMETA_FIRST_LEAF)) != 0u;
-            if (live[kk]) {
-              const uint32_t hop = second ? off : 0u;
-              L[kk] += hop;
-              live[kk] = !at_leaf;
-              if (live[kk]) {
-                // a first child reached from an even node is the neighbour already held
-                const bool reuse = !second && (kx & 1u) == 0u;
-                k[kk]            = kx + (second ? off : 1u);
-                need[kk]         = !reuse;
-                if (reuse) {
-                  cv[kk] = nv[kk];
-                  cm[kk] = nm[kk];
-                }
-              } else {
-                need[kk] = false;
-              }
+            for (int kk = 0; kk < NT; ++kk) {
+              // (a finished walk repeats its last test: nothing to settle)
+              if (static_cast<int32_t>(k[kk]) >= 0)
+                settle_open_test<T>(xl[kk], lo[kk], meta[kk], meta[kk] & feat_mask, row_values(),
+                                    f.c_exact, [&]() { return k[kk]; });
             }
-            walking |= live[kk];
           }
-          if (!__any_sync(0xffffffffu, walking)) break;
+#pragma unroll
+          for (int kk = 0; kk < NT; ++kk)
+            compact_step(k[kk], L[kk], pair[kk][0], pair[kk][1], pair[kk][2], pair[kk][3], xl[kk],
+                         lo[kk], meta[kk], off_shift, node_ptr);
+          uint32_t all = k[0];
+#pragma unroll
+          for (int kk = 1; kk < NT; ++kk) all &= k[kk];
+          if (!__any_sync(0xffffffffu, static_cast<int32_t>(all) >= 0)) break;
         }
         // the leaves: payload (or id) from the leaf arrays
         if (MODE == MODE_LEAFID) {
           uint32_t id[NT];
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk)
-            id[kk] = node_load == kLoadCgKeep ? ld_once(f.c_leaf_ids + L[kk], once) : __ldg(f.c_leaf_ids + L[kk]);
+            id[kk] = __ldg(f.c_leaf_ids + L[kk]);
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) {
             if (kk < n_act && row < p.n_rows) {
@@ -393,8 +402,7 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
           Val pay[NT];
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) {
-            const Val* lp = static_cast<const Val*>(f.c_leaf_payload) + L[kk];
-            pay[kk]       = node_load == kLoadCgKeep ? ld_once(lp, once) : __ldg(lp);
+            pay[kk] = __ldg(static_cast<const Val*>(f.c_leaf_payload) + L[kk]);
           }
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk) {
@@ -430,15 +438,13 @@ int launch_mode(const PredictParams& p, const CompactCfg& c, cudaStream_t stream
     auto k       = sparse_compact_kernel<T, CAT, MODE, kCompactTreesInFlight, kCompactThreadsBig>;
     const int rc = set_smem_bytes(reinterpret_cast<const void*>(k), c.smem_bytes, err);
     if (rc != B2FIL_OK) return rc;
-    k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
-                                                   c.node_load);
+    k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
     return B2FIL_OK;
   }
   auto k       = sparse_compact_kernel<T, CAT, MODE, kCompactTreesInFlight, kCompactThreads>;
   const int rc = set_smem_bytes(reinterpret_cast<const void*>(k), c.smem_bytes, err);
   if (rc != B2FIL_OK) return rc;
-  k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
-                                                 c.node_load);
+  k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
   return B2FIL_OK;
 }
 
@@ -461,8 +467,6 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
 {
   if (!f.c_enabled) return false;
   const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
-  // L2-only loads measured 4 to 8 % faster than the read-only path: the lines are never reused
-  const int load  = tuning_value("compact_load", kLoadCg);
   if (const int R = tuning_value("compact_R", 0), G = tuning_value("compact_G", 0),
       S = tuning_value("compact_S", 0);
       R >= 32 && (R & (R - 1)) == 0 && R <= 128 && G >= 1 && (R / 32) * G <= 31 && S >= 1 &&
@@ -471,7 +475,7 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
     if (b <= kMaxSmemBytes) {
       const int64_t n_tiles = (n_rows + R - 1) / R;
       cfg = CompactCfg{R, G, S, b, ((R / 32) * G + 1) * 32,
-                       static_cast<int>(std::min<int64_t>(n_tiles, sm_count)), load};
+                       static_cast<int>(std::min<int64_t>(n_tiles, sm_count))};
       return true;
     }
   }
@@ -490,7 +494,7 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
           if (b <= limit) {
             const int64_t n_tiles = (n_rows + R - 1) / R;
             cfg = CompactCfg{R, G, S, b, (rw * G + 1) * 32,
-                             static_cast<int>(std::min<int64_t>(n_tiles, sm_count)), load};
+                             static_cast<int>(std::min<int64_t>(n_tiles, sm_count))};
             return true;
           }
         }
