@@ -15,7 +15,8 @@ SRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libb2fil.so")
 SOURCES = ["api.cu", "kernels.cu", "kernels_q_top6.cu", "kernels_q_plain6.cu", "kernels_q_plain4.cu",
-           "kernels_q_cat.cu", "kernels_q_generic.cu", "kernels_q_pair.cu", "kernels_q_vec.cu",
+           "kernels_q_cat.cu", "kernels_q_generic.cu", "kernels_q_pair.cu", "kernels_q_leafg.cu",
+           "kernels_q_vec.cu",
            "kernels_sparse_c.cu",
            "pack.cpp"]
 HEADERS = ["forest.hpp", "kernels.hpp", "kernels_q.hpp", "device_common.cuh", "dense_q.cuh",

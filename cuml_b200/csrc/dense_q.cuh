@@ -51,7 +51,13 @@ __device__ __forceinline__ uint2 lds_u32x2(uint32_t a)
 // of the current node (heap words 2i and 2i + 1, one aligned 8-byte load) are requested together
 // with the row's rank, before the test is decided, so the next node is already there when the
 // test is known; a step costs one shared-memory latency instead of two, and one more wavefront.
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false>
+// LEAFG: the stages hold only the test nodes of the trees and a walk fetches its leaf payload from
+// the forest image in global memory (L2).  Deep trees are half payloads (4 KB of 8 KB at depth
+// 10); where shared memory next to the row tile holds only a dozen whole trees, leaving the
+// payloads out doubles the walks in flight, which is what such shapes are bound by.  The payload
+// fetch of a sub-batch is consumed one sub-batch later, behind the next walk.
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false,
+          bool LEAFG = false>
 struct DenseQWalker {
   using TR = Traits<T>;
   // Walk the warp's 32 rows through all trees.  A stage of the ring holds K sub-batches of G * NT
@@ -67,11 +73,14 @@ struct DenseQWalker {
     static_assert(!TOPC || (DEPTH >= 2 && !CAT), "top nodes need two plain levels");
     static_assert(!PAIR || (!CAT && !TOPC && MODE == MODE_SCALAR && sizeof(T) == 4),
                   "the child-pair walk exists for fp32 scalar leaves without categorical tests");
+    static_assert(!LEAFG || (!CAT && !PAIR && MODE == MODE_SCALAR && sizeof(T) == 4),
+                  "payloads outside the stages exist for fp32 scalar leaves without categorical tests");
     const ForestView& f    = p.f;
     const int D            = DEPTH > 0 ? DEPTH : f.dense_depth;
-    const uint32_t tstride = static_cast<uint32_t>(f.q_tree_stride);
     constexpr uint32_t QNB = CAT ? 8u : 4u;  // bytes per test node: {node, category set} or node
     const uint32_t width_b = (1u << D) * QNB;
+    // bytes between two trees of a stage
+    const uint32_t tstride = LEAFG ? width_b : static_cast<uint32_t>(f.q_tree_stride);
     // bytes per leaf payload: the element size, except where vector leaves sit in the tree block
     const uint32_t lbytes  = MODE == MODE_SCALAR ? TR::ES : static_cast<uint32_t>(f.q_leaf_bytes);
     const bool inline_vec  = MODE != MODE_SCALAR && lbytes > TR::ES;
@@ -83,6 +92,16 @@ struct DenseQWalker {
     const uint32_t sub_b   = static_cast<uint32_t>(per_sub) * tstride;
     bool ok                = true;
 
+    // LEAFG: payloads requested by the previous sub-batch, not yet added
+    uint32_t pend[NT] = {};
+    int pend_first = 0, pend_n = 0;
+    auto take_pending = [&]() {
+#pragma unroll
+      for (int k = 0; k < NT; ++k) {
+        if (k < pend_n) take_leaf<T, MODE>(p, pend_first + k, pend[k], 0u, acc_group, R, r, row, run);
+      }
+      pend_n = 0;
+    };
     // One sub-batch: NT trees side by side.  FULL means all NT slots hold live trees, which lets
     // the compiler drop every per-slot guard.
     auto sub_batch = [&](auto full_tag, uint32_t base0, int first, int n_act) {
@@ -207,6 +226,22 @@ struct DenseQWalker {
 #pragma unroll 4
         for (int lvl = 0; lvl < D; ++lvl) level();
       }
+      if constexpr (LEAFG) {
+        // add the payloads that the previous sub-batch requested (they arrived during this
+        // walk), then request this sub-batch's; nothing touches them until the next one is done
+        take_pending();
+        const unsigned char* image = static_cast<const unsigned char*>(f.q_nodes) + width_b;
+#pragma unroll
+        for (int k = 0; k < NT; ++k) {
+          const uint32_t slot = idx[k] - (1u << D);
+          const int tree      = first + (FULL ? k : min(k, n_act - 1));
+          pend[k] = __ldg(reinterpret_cast<const uint32_t*>(
+            image + static_cast<size_t>(tree) * static_cast<size_t>(f.q_tree_stride) + slot * 4u));
+        }
+        pend_first = first;
+        pend_n     = FULL ? NT : n_act;
+        return;
+      }
       // scalar leaves of a multi-class forest: trees are stored class by class, so when the
       // first and the last tree of the sub-batch feed the class of the running sum, all do
       bool same_class = false;
@@ -320,11 +355,13 @@ struct DenseQWalker {
       if (lane == 0) mbar_arrive(bars + 8u * (kMaxStages + s));
       pos.advance(S);
     }
+    if constexpr (LEAFG) take_pending();
     return ok;
   }
 };
 
-template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false>
+template <typename T, int MODE, int NT, int DEPTH, bool CAT, bool TOPC, bool PAIR = false,
+          bool LEAFG = false>
 __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint16_t* __restrict__ Q,
                                              const int32_t* __restrict__ tile_flags, const int R,
                                              const int G, const int S, const int K,
@@ -350,7 +387,9 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
   const uint32_t bars        = smem_addr(smem);
   const uint32_t tile        = smem_addr(tile_ptr);
   const uint32_t stages      = smem_addr(stage_ptr);
-  const uint32_t tstride     = static_cast<uint32_t>(f.q_tree_stride);
+  const uint32_t gstride     = static_cast<uint32_t>(f.q_tree_stride);  // trees in the forest image
+  // trees in a stage: whole, or (LEAFG) only their 2^depth test nodes
+  const uint32_t tstride     = LEAFG ? (4u << (DEPTH > 0 ? DEPTH : f.dense_depth)) : gstride;
   const int per_batch        = G * NT * K;
   const uint32_t stage_bytes = per_batch * tstride;
   const int n_batches        = (f.n_trees + per_batch - 1) / per_batch;
@@ -397,8 +436,15 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
           const int count      = min(per_batch, f.n_trees - first);
           const uint32_t bytes = count * tstride;
           mbar_expect_tx(bars + 8u * s, bytes);
-          bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * tstride,
-                        bytes, bars + 8u * s);
+          if (LEAFG) {
+            // one copy per tree: the node half of its block
+            for (int i = 0; i < count; ++i)
+              bulk_copy_g2s(stages + s * stage_bytes + i * tstride,
+                            src + static_cast<size_t>(first + i) * gstride, tstride, bars + 8u * s);
+          } else {
+            bulk_copy_g2s(stages + s * stage_bytes, src + static_cast<size_t>(first) * gstride,
+                          bytes, bars + 8u * s);
+          }
           pos.advance(S);
           if (pos.stage == 0) primed = true;
         }
@@ -426,11 +472,11 @@ __device__ __forceinline__ void dense_q_body(const PredictParams& p, const uint1
     Running<T> run{T(0), 0, {}};
     if (ok) {
       if (nans) {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR>::template walk<true>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR, LEAFG>::template walk<true>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, pos, run, top);
       } else {
-        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR>::template walk<false>(
+        ok = DenseQWalker<T, MODE, NT, DEPTH, CAT, TOPC, PAIR, LEAFG>::template walk<false>(
           p, G, S, K, g, r, row0 + r, lane, bars, stages, stage_bytes, row_addr, stride_b,
           acc_group, R, pos, run, top);
       }
@@ -465,6 +511,17 @@ dense_q_pair_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
                     const int K)
 {
   dense_q_body<float, MODE_SCALAR, NT, 0, false, false, true>(p, Q, tile_flags, R, G, S, K, nullptr);
+}
+
+// Same kernel with the leaf payloads left in global memory (see DenseQWalker).
+template <int NT, int DEPTH>
+__global__ void __launch_bounds__(1024, 1)
+dense_q_leafg_kernel(const PredictParams p, const uint16_t* __restrict__ Q,
+                     const int32_t* __restrict__ tile_flags, const int R, const int G, const int S,
+                     const int K)
+{
+  dense_q_body<float, MODE_SCALAR, NT, DEPTH, false, false, false, true>(p, Q, tile_flags, R, G, S,
+                                                                         K, nullptr);
 }
 
 // Same kernel with the top nodes of every tree in the parameter block.

@@ -770,6 +770,15 @@ size_t dense_q_smem(size_t qstride, int precision, int F, int NC, bool reduce, i
   return b;
 }
 
+// Bytes of a tree's test nodes when kernels exist that keep only those in the stages
+// (dense_q_leafg_kernel: fp32 scalar leaves, no categorical tests, depth 9 or 10), else 0.
+size_t q_node_only_stride(const ForestView& f, int mode)
+{
+  const bool ok = f.format == FMT_DENSE_F && mode == MODE_SCALAR && !f.q_has_cat &&
+                  (f.dense_depth == 9 || f.dense_depth == 10);
+  return ok ? (size_t(4) << f.dense_depth) : 0;
+}
+
 // Most trees a warp of the quantised kernel may walk side by side: the kernels that exist.
 int q_max_trees_in_flight(const ForestView& f, int mode)
 {
@@ -782,9 +791,12 @@ int q_max_trees_in_flight(const ForestView& f, int mode)
 // Launch shape of the quantised dense kernel: the largest row tile that fits, then as many warps
 // as fit (31 consumer warps at most), then as many trees in flight per warp as there is a kernel
 // for, then the deepest tree ring that still fits.
+// `node_stride` > 0 says that kernels exist which keep only a tree's test nodes (that many bytes)
+// in the stages and fetch leaf payloads from global memory; the shape with them is taken when it
+// puts at least a third more walks in flight.
 bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bool reduce,
                     int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg,
-                    int depth_hint = 0)
+                    int depth_hint = 0, size_t node_stride = 0)
 {
   int want = 256;
   if (chunk_size > 0) {
@@ -819,13 +831,15 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
         (NT == 1 || NT == 2 || NT == 4 || (NT == 6 && (R / 32) * G <= 24) ||
          (NT == 3 && max_nt == 6 && depth_hint >= 9)) && S >= 2 &&
         S <= kMaxStages && K >= 1 && NT <= max_nt) {
-      const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, G, NT, S, K);
+      const bool leafg = node_stride > 0 && tuning_value("q_leafg", 0) == 1 && NT >= 2 && NT <= 4;
+      const size_t b = dense_q_smem(leafg ? node_stride : qstride, precision, F, NC, reduce, R, G, NT, S, K);
       if (b <= kMaxSmemBytes) {
-        cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32, K};
+        cfg = DenseCfg{R, G, NT, S, b, ((R / 32) * G + 1) * 32, K, leafg ? 1 : 0};
         return true;
       }
     }
   }
+  const int leafg_knob = tuning_value("q_leafg", -1);  // -1 automatic, 0 never, 1 whenever possible
   for (int R = want; R >= 32; R /= 2) {
     const int rw = R / 32;
     // Among the (tree groups, trees in flight) pairs that fit with a two-stage ring, take the one
@@ -847,14 +861,36 @@ bool dense_q_config(size_t qstride, int max_nt, int precision, int F, int NC, bo
         break;  // smaller NT with the same G only has fewer walks
       }
     }
+    size_t stride = qstride;
+    int leafg     = 0;
+    if (node_stride > 0 && leafg_knob != 0) {
+      // the same search with node-only trees (kernels for two to four trees in flight)
+      int lg = 0, lnt = 0;
+      for (int G = std::min(8, 31 / rw); G >= 1; --G) {
+        for (int NT = 4; NT >= 2; --NT) {
+          if (dense_q_smem(node_stride, precision, F, NC, reduce, R, G, NT, 2, 1) > kMaxSmemBytes) continue;
+          if (G * NT > lg * lnt) {
+            lg  = G;
+            lnt = NT;
+          }
+          break;
+        }
+      }
+      if (lg > 0 && (leafg_knob == 1 || lg * lnt * 3 >= best_g * best_nt * 4)) {
+        best_g  = lg;
+        best_nt = lnt;
+        stride  = node_stride;
+        leafg   = 1;
+      }
+    }
     if (best_g == 0) continue;
     // a stage holds K sub-batches so that a warp waits and signals once per K * NT trees.
     // Two stages already hide the bulk copies (measured: S = 2 and S = 3 run alike).
     for (int K = 2; K >= 1; K /= 2) {
       for (int S = 3; S >= 2; --S) {
-        const size_t b = dense_q_smem(qstride, precision, F, NC, reduce, R, best_g, best_nt, S, K);
+        const size_t b = dense_q_smem(stride, precision, F, NC, reduce, R, best_g, best_nt, S, K);
         if (b <= kMaxSmemBytes) {
-          cfg = DenseCfg{R, best_g, best_nt, S, b, (rw * best_g + 1) * 32, K};
+          cfg = DenseCfg{R, best_g, best_nt, S, b, (rw * best_g + 1) * 32, K, leafg};
           return true;
         }
       }
@@ -900,6 +936,11 @@ int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err
     rec.kernel = "dense_q_pair_kernel";
     return launch_q_pair(L, err);
   }
+  if (L.c.leaves_global) {
+    rec.kernel = "dense_q_leafg_kernel";
+    rec.depth  = f.dense_depth;
+    return launch_q_leafg(L, err);
+  }
   if (!f64 && mode == MODE_VECTOR && f.dense_depth >= 4 && f.dense_depth <= 10 &&
       (L.c.trees_in_flight == 6 || L.c.trees_in_flight == 4)) {
     rec.depth = f.dense_depth;
@@ -939,7 +980,7 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
   DenseCfg c;
   if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
                       f.n_features, f.n_outputs, reduce, p.n_rows, chunk_size, sm_count, c,
-                      f.dense_depth)) {
+                      f.dense_depth, q_node_only_stride(f, mode))) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }
@@ -1121,7 +1162,7 @@ bool dense_config(int depth, int precision, int n_features, int n_outputs, bool 
           const size_t b =
             dense_smem(depth, precision, n_features, n_outputs, reduce_kind, R, G, NT, S);
           if (b <= kMaxSmemBytes) {
-            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, 1};
+            cfg = DenseCfg{R, G, NT, S, b, (rw * G + 1) * 32, 1, 0};
             return true;
           }
         }
@@ -1340,7 +1381,7 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
   DenseCfg c;
   if (!dense_q_config(static_cast<size_t>(f.q_tree_stride), q_max_trees_in_flight(f, mode), precision,
                       f.n_features, f.n_outputs, mode <= MODE_VECTOR, p.n_rows, chunk_size,
-                      sm_count, c, f.dense_depth)) {
+                      sm_count, c, f.dense_depth, q_node_only_stride(f, mode))) {
     err = "no quantised launch shape fits shared memory";
     return B2FIL_ERR_UNSUPPORTED;
   }

@@ -33,6 +33,7 @@ struct DenseCfg {
   size_t smem_bytes;
   int threads;
   int sub_batches;     // K: sub-batches of G * NT trees per stage (quantised kernel)
+  int leaves_global;   // quantised kernel: the stages hold test nodes only, payloads stay in global memory
 };
 
 // Largest dynamic shared memory a CTA may use on sm_100 (227 KiB).

@@ -37,6 +37,8 @@ int launch_q_vec(const QLaunch& L, std::string& err);
 // fp32, scalar leaves, no categorical tests, any depth, 1, 2 or 4 trees in flight: the walk that
 // fetches both children of a node ahead of the test (for launch shapes with few walks in flight).
 int launch_q_pair(const QLaunch& L, std::string& err);
+// fp32 scalar leaves of depth 9 and 10, two to four trees in flight, payloads left in global memory.
+int launch_q_leafg(const QLaunch& L, std::string& err);
 // Forests with categorical tests: every precision, output mode and depth; 1, 2 or 4 trees in
 // flight (depth-specialised bodies for fp32 scalar leaves of depth 4..8 with four trees).
 int launch_q_cat(const QLaunch& L, int mode, bool f64, std::string& err);

@@ -227,13 +227,12 @@ int b2fil_last_variant(char* buf, size_t buf_bytes);
  * set a named integer knob for the whole process.  Knobs: "q_R", "q_G", "q_NT", "q_S", "q_K" force
  * the launch shape of the traversal over rank-quantised rows (rows per tile, tree groups, trees
  * in flight per warp, ring depth, sub-batches per stage; q_R = 0: automatic), "q_pair" = 1 / 0
- * forces / forbids its variant that fetches both children of a node ahead of the test (-1: automatic);
- * "compact_R", "compact_G", "compact_S"
- * force the launch shape of the kernel over the compact image of sparse forests (rows per tile,
- * tree groups, ring depth; 0 = automatic), "compact_load" picks the cache policy of its node
- * fetches (0 read-only path, 1 L2 only - the default -, 2 read-only path without L1 allocation,
- * 3 L2 only with eviction hints: nodes evict-last, rows and leaves evict-first).  Unknown keys are
- * stored and ignored.
+ * forces / forbids its variant that fetches both children of a node ahead of the test (-1:
+ * automatic), "q_leafg" = 1 / 0 forces / forbids its variant that keeps only the test nodes of
+ * depth-9 and depth-10 trees in shared memory and fetches leaf payloads from global memory (-1:
+ * automatic, taken when it puts a third more walks in flight); "compact_R", "compact_G",
+ * "compact_S" force the launch shape of the kernel over the compact image of sparse forests (rows
+ * per tile, tree groups, ring depth; 0 = automatic).  Unknown keys are stored and ignored.
  * No counterpart in the reference. */
 int b2fil_set_tuning(const char* key, int value);
 

@@ -915,6 +915,52 @@ def test_quantised_traversal_kernel_variants(n_trees, depth, n_classes):
         lib.b2fil_set_tuning(b"q_R", 0)
 
 
+@pytest.mark.parametrize("n_trees,depth,n_classes,n_features",
+                         [(37, 10, 1, 24), (50, 9, 1, 600), (45, 10, 3, 24), (7, 9, 1, 24)])
+def test_quantised_walk_with_leaf_payloads_in_global_memory(n_trees, depth, n_classes, n_features):
+    """Depth 9 and 10, fp32 scalar leaves: the variant whose stages hold only the test nodes and
+    whose walks fetch the leaf payload from the forest image, consumed one sub-batch later.
+    Forced on (q_leafg = 1) with two, three and four trees in flight, partial last sub-batches,
+    several classes, tiles with and without NaN; and chosen automatically where it puts more
+    walks in flight (600 features: the row tile leaves room for few whole trees)."""
+    kw = dict(n_classes=n_classes) if n_classes > 1 else {}
+    desc = synthetic_complete_forest(n_trees, depth, n_features, seed=60 + depth, **kw)
+    rng = np.random.default_rng(61)
+    n = 5000
+    X = rng.standard_normal((n, n_features)).astype(np.float32)
+    X[:2500][rng.random((2500, n_features)) < 0.05] = np.nan
+    fi = ForestInference.load_from_treelite_model(desc)
+    assert fi.describe()["row_quantization"] == 1
+    Xd = _dev(X, "single")
+    want = oracle.predict(desc, X, INFER_DEFAULT, "single")
+    from cuml_b200.fil import _lib
+
+    lib = _lib.load()
+    try:
+        if n_features == 600:
+            raw = fi._run(Xd, INFER_DEFAULT, 4).cpu().numpy()
+            assert "dense_q_leafg_kernel" in _lib.last_variant()
+            np.testing.assert_allclose(raw, want, **_tol(desc, "single"))
+        lib.b2fil_set_tuning(b"q_leafg", 1)
+        for shape in (None, (128, 2, 2, 2, 1), (64, 3, 3, 2, 1), (32, 2, 4, 2, 2), (128, 1, 2, 3, 1)):
+            if shape and n_features == 600 and shape[0] > 64:
+                continue  # a 128-row tile of 600 features leaves no room for these stages
+            for key, v in zip((b"q_R", b"q_G", b"q_NT", b"q_S", b"q_K"), shape or (0, 0, 0, 0, 0)):
+                lib.b2fil_set_tuning(key, v)
+            raw = fi._run(Xd, INFER_DEFAULT, 4).cpu().numpy()
+            assert "dense_q_leafg_kernel" in _lib.last_variant(), _lib.last_variant()
+            np.testing.assert_allclose(raw, want, **_tol(desc, "single"))
+        lib.b2fil_set_tuning(b"q_leafg", 0)
+        lib.b2fil_set_tuning(b"q_R", 0)
+        raw = fi._run(Xd, INFER_DEFAULT, 4).cpu().numpy()
+        assert "dense_q_leafg_kernel" not in _lib.last_variant()
+        np.testing.assert_allclose(raw, want, **_tol(desc, "single"))
+        fi.check_status()
+    finally:
+        lib.b2fil_set_tuning(b"q_leafg", -1)
+        lib.b2fil_set_tuning(b"q_R", 0)
+
+
 @pytest.mark.parametrize("precision", ["single", "double"])
 def test_per_tree_outputs_wide_and_narrow_stores(precision):
     """Leaf ids and per-tree values leave the quantised traversal as 16-byte stores when a row's
