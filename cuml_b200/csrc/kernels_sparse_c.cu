@@ -271,6 +271,20 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       for (int i = threadIdx.x; i < G * NC * R; i += n_ct) acc[i] = T(0);
     }
     consumer_sync(n_ct);
+    {
+      // ask the L2 for the rows of this CTA's next tile, so that staging them does not wait on HBM
+      const int64_t next0 = row0 + static_cast<int64_t>(gridDim.x) * R;
+      const int row_bytes = F * static_cast<int>(sizeof(T));
+      const int lines     = (row_bytes + 127) >> 7;
+      for (int i = threadIdx.x; i < R * lines; i += n_ct) {
+        const int64_t nrow = next0 + i / lines;
+        if (nrow < p.n_rows) {
+          const char* at = reinterpret_cast<const char*>(static_cast<const T*>(p.X) + nrow * p.row_stride) +
+                           min((i % lines) << 7, row_bytes - 1);
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(at));
+        }
+      }
+    }
     Running<T> run{T(0), 0, {}};
     // the row's doubles, for the tests that the float tile leaves open
     auto row_values = [&]() -> const double* {
@@ -391,11 +405,27 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
 #pragma unroll
           for (int kk = 0; kk < NT; ++kk)
             id[kk] = __ldg(f.c_leaf_ids + L[kk]);
+          // four live trees that are also the caller's trees o, o + 1, o + 2, o + 3 with o a
+          // multiple of four: the row's four ids are contiguous and leave as one 16-byte store
+          // (scalar 4-byte stores at a stride of a whole output row cost a sector request each)
+          int orig[NT];
 #pragma unroll
-          for (int kk = 0; kk < NT; ++kk) {
-            if (kk < n_act && row < p.n_rows) {
-              const int orig = __ldg(f.tree_orig + first + kk);
-              static_cast<uint32_t*>(p.out)[row * f.n_trees + orig] = id[kk];
+          for (int kk = 0; kk < NT; ++kk) orig[kk] = __ldg(f.tree_orig + first + min(kk, n_act - 1));
+          bool wide = NT == 4 && n_act == NT && (orig[0] & 3) == 0 && (f.n_trees & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+#pragma unroll
+          for (int kk = 1; kk < NT; ++kk) wide = wide && orig[kk] == orig[0] + kk;
+          if (wide) {
+            if (row < p.n_rows) {
+              uint32_t* dst = static_cast<uint32_t*>(p.out) + row * f.n_trees + orig[0];
+              *reinterpret_cast<uint4*>(dst) =
+                make_uint4(id[0], id[NT > 1 ? 1 : 0], id[NT > 2 ? 2 : 0], id[NT > 3 ? 3 : 0]);
+            }
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < NT; ++kk) {
+              if (kk < n_act && row < p.n_rows)
+                static_cast<uint32_t*>(p.out)[row * f.n_trees + orig[kk]] = id[kk];
             }
           }
         } else {
