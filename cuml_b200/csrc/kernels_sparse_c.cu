@@ -434,9 +434,34 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
           for (int kk = 0; kk < NT; ++kk) {
             pay[kk] = __ldg(static_cast<const Val*>(f.c_leaf_payload) + L[kk]);
           }
+          bool wide = false;
+          int first_orig = 0;
+          if (MODE == MODE_PERTREE) {
+            // per-tree scalar outputs: the same 16-byte stores as for leaf ids
+            first_orig = __ldg(f.tree_orig + first);
+            wide = NT == 4 && n_act == NT && f.leaf_vector_len <= 1 && (first_orig & 3) == 0 &&
+                   (f.n_trees & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
 #pragma unroll
-          for (int kk = 0; kk < NT; ++kk) {
-            if (kk < n_act) take_leaf<T, MODE>(p, first + kk, pay[kk], 0u, acc_group, R, r, row, run);
+            for (int kk = 1; kk < NT; ++kk)
+              wide = wide && __ldg(f.tree_orig + first + min(kk, n_act - 1)) == first_orig + kk;
+          }
+          if (MODE == MODE_PERTREE && wide) {
+            if (row < p.n_rows) {
+              Val* dst = static_cast<Val*>(p.out) + row * f.n_trees + first_orig;
+              if constexpr (sizeof(Val) == 4) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pay[0], pay[NT > 1 ? 1 : 0],
+                                                            pay[NT > 2 ? 2 : 0], pay[NT > 3 ? 3 : 0]);
+              } else {
+                *reinterpret_cast<ulonglong2*>(dst)     = make_ulonglong2(pay[0], pay[NT > 1 ? 1 : 0]);
+                *reinterpret_cast<ulonglong2*>(dst + 2) = make_ulonglong2(pay[NT > 2 ? 2 : 0],
+                                                                          pay[NT > 3 ? 3 : 0]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < NT; ++kk) {
+              if (kk < n_act) take_leaf<T, MODE>(p, first + kk, pay[kk], 0u, acc_group, R, r, row, run);
+            }
           }
         }
       }

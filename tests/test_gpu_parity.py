@@ -989,3 +989,27 @@ def test_per_tree_outputs_wide_and_narrow_stores(precision):
         fi.apply(Xd, preds=view, chunk_size=8)
         assert np.array_equal(view.cpu().numpy().astype(np.uint32), want_ids)
         assert int(buf[0]) == 0
+    # the walk over the compact image of a sparse forest stores the same way
+    from cuml_b200.fil import _lib
+
+    for n_trees in (24, 23):
+        desc = random_forest_desc(70 + n_trees, n_trees=n_trees, n_features=16, max_depth=12,
+                                  p_leaf=0.15)
+        fi = ForestInference.load_from_treelite_model(desc, precision=precision, storage="sparse")
+        Xd = _dev(X, precision)
+        want_ids = oracle.predict(desc, X, INFER_LEAF_ID, precision)
+        want_pt = oracle.predict(desc, X, INFER_PER_TREE, precision)
+        assert np.array_equal(fi.apply(Xd).cpu().numpy().astype(np.uint32), want_ids)
+        assert "sparse_compact_kernel" in _lib.last_variant()
+        assert np.array_equal(fi.predict_per_tree(Xd).cpu().numpy(), want_pt)
+        buf = torch.zeros(n * n_trees + 1, device="cuda:0", dtype=torch.int32)
+        view = buf[1:].view(n, n_trees)
+        fi.apply(Xd, preds=view)
+        assert np.array_equal(view.cpu().numpy().astype(np.uint32), want_ids)
+        assert int(buf[0]) == 0
+        real = torch.float32 if precision == "single" else torch.float64
+        buf = torch.zeros(n * n_trees + 1, device="cuda:0", dtype=real)
+        view = buf[1:].view(n, n_trees)
+        fi.predict_per_tree(Xd, preds=view)
+        assert np.array_equal(view.cpu().numpy(), want_pt)
+        assert float(buf[0]) == 0.0
