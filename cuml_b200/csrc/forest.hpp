@@ -314,9 +314,11 @@ constexpr uint32_t kQMaxGroupFeatures = 32;
 
 // Validate `desc`, normalise its tests and lay its nodes out.  Returns B2FIL_OK or an error code
 // with `err` set.  `dense_ok(depth, precision, n_features, n_outputs)` tells whether the dense
-// kernel can run a forest of that shape (shared-memory fit); AUTO storage asks it.
+// kernels can run a forest of that shape (shared-memory fit): 0 no, 1 yes, 2 only the traversal
+// over rank-quantised rows (its 2-byte row tile fits where a tile of reals does not: forests with
+// a thousand features and more); AUTO storage asks it.
 int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
-                bool (*dense_ok)(int depth, int precision, int n_features, int n_outputs),
+                int (*dense_ok)(int depth, int precision, int n_features, int n_outputs),
                 PackedForest& out,
                 std::string& err);
 

@@ -1200,10 +1200,18 @@ bool dense_config(int depth, int precision, int n_features, int n_outputs, bool 
   return false;
 }
 
-bool dense_ok(int depth, int precision, int n_features, int n_outputs)
+int dense_ok(int depth, int precision, int n_features, int n_outputs)
 {
   // usable when at least 64 rows and two tree groups fit next to a two-stage ring
-  return dense_smem(depth, precision, n_features, n_outputs, true, 64, 2, 1, 2) <= kMaxSmemBytes;
+  if (dense_smem(depth, precision, n_features, n_outputs, true, 64, 2, 1, 2) <= kMaxSmemBytes) return 1;
+  // else the traversal over rank-quantised rows alone, if a 32-row tile of ranks and two stages
+  // of one tree fit (a tree counted at its largest: 8-byte test nodes, four inline outputs)
+  const size_t es      = precision == B2FIL_F32 ? 4 : 8;
+  const size_t qstride = (size_t(8) + 4 * es) << depth;
+  if (dense_q_smem(qstride, precision, n_features, n_outputs, true, 32, 1, 1, 2, 1) <= kMaxSmemBytes &&
+      n_features < (1 << 14))
+    return 2;
+  return 0;
 }
 
 int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStream_t stream,
@@ -1231,9 +1239,14 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
   // the pre-pass indexes a row tile with 32-bit element offsets
   // (small batches skip the pre-pass: with fewer 128-row tiles than half the SMs the forest is
   // split across CTAs of the plain dense kernel instead, which is what bounds their latency)
-  if ((f.format == FMT_DENSE_F || f.format == FMT_DENSE_D) && f.q_enabled &&
-      p.row_stride < (int64_t(1) << 22) &&
-      pool != nullptr && (chunk_size > 0 || (p.n_rows + 127) / 128 * 2 > sm_count)) {
+  // (forests whose row tile only fits as ranks - a thousand features and more - have no other
+  // dense kernel and take this path at every batch size)
+  const bool dense_fmt = f.format == FMT_DENSE_F || f.format == FMT_DENSE_D;
+  const bool ranks_only =
+    dense_fmt && dense_ok(f.dense_depth, f.format == FMT_DENSE_F ? B2FIL_F32 : B2FIL_F64,
+                          f.n_features, f.n_outputs) != 1;
+  if (dense_fmt && f.q_enabled && p.row_stride < (int64_t(1) << 22) && pool != nullptr &&
+      (chunk_size > 0 || ranks_only || (p.n_rows + 127) / 128 * 2 > sm_count)) {
     rc = launch_dense_q(p, mode, chunk_size, sm_count, stream, pool, err, launches);
     if (rc != B2FIL_OK) return rc;
     const cudaError_t e = cudaGetLastError();

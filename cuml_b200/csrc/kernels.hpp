@@ -43,8 +43,9 @@ constexpr size_t kMaxSmemBytes = 227 * 1024;
 bool dense_config(int depth, int precision, int n_features, int n_outputs, bool reduce_kind,
                   int64_t n_rows, int chunk_size, int sm_count, DenseCfg& cfg);
 
-// True when the dense kernels can run forests of this shape at all.
-bool dense_ok(int depth, int precision, int n_features, int n_outputs);
+// Can the dense kernels run forests of this shape?  0 no, 1 yes, 2 only the traversal over
+// rank-quantised rows.
+int dense_ok(int depth, int precision, int n_features, int n_outputs);
 
 // Enqueue a prediction on `stream`.  Returns B2FIL_OK or an error code with `err` set.
 // `launches` (optional) is incremented by the number of kernels enqueued.

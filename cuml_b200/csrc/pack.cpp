@@ -1017,7 +1017,7 @@ struct Packer {
 }  // namespace
 
 int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
-                bool (*dense_ok)(int, int, int, int), PackedForest& out, std::string& err)
+                int (*dense_ok)(int, int, int, int), PackedForest& out, std::string& err)
 {
   if (opts.precision != B2FIL_F32 && opts.precision != B2FIL_F64) {
     err = "precision must be B2FIL_F32 or B2FIL_F64";
@@ -1060,8 +1060,24 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
   v.ratio_c         = desc.ratio_c;
 
   bool dense = false;
+  // 2: only the traversal over rank-quantised rows fits, so dense storage stands or falls with
+  // the rank tables
+  int fit = 0;
   if (opts.storage != B2FIL_STORAGE_SPARSE) {
-    const bool fits = max_depth <= 16 && dense_ok(max_depth, opts.precision, desc.n_features, desc.n_outputs);
+    fit = max_depth <= 16 ? dense_ok(max_depth, opts.precision, desc.n_features, desc.n_outputs) : 0;
+    bool fits = fit == 1 || (fit == 2 && opts.row_quantization == 0);
+    if (fit == 2 && opts.storage == B2FIL_STORAGE_AUTO) {
+      // The rank pre-pass costs time in proportion to the features of a row, the walks in
+      // proportion to the nodes a row visits.  With few visits per feature the sparse kernels,
+      // which rank nothing, are faster.  Measured break-even (complete trees of depth 4 to 10,
+      // 100 to 1000 trees): about half a visit per feature at 1024 and 1536 features, about
+      // 1.1 at 2048 and 3000, where the pre-pass has more feature groups than half the SMs and
+      // reads every row in 128-byte pieces.
+      const double nodes_per_tree = static_cast<double>(out.n_nodes_in) / std::max(1, desc.n_trees);
+      const double visits = desc.n_trees * std::min<double>(max_depth, std::log2(nodes_per_tree + 1.0));
+      const double per_feature = desc.n_features <= 1536 ? 0.5 : 1.1;
+      if (visits < per_feature * desc.n_features) fits = false;
+    }
     if (opts.storage == B2FIL_STORAGE_DENSE) {
       if (!fits) {
         err = "dense storage cannot hold this forest: depth " + std::to_string(max_depth) +
@@ -1096,6 +1112,21 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
       out.view.q_enabled        = 0;
       out.view.q_max_blob_bytes = 0;
     }
+  }
+  if (fit == 2 && !out.view.q_enabled) {
+    // no rank tables for this forest (category sets too large, a feature used both ways, ...)
+    // and no other dense kernel that fits: sparse storage after all
+    if (opts.storage == B2FIL_STORAGE_DENSE) {
+      err = "dense storage cannot hold this forest: its row tile only fits as ranks and the "
+            "forest cannot be rank-quantised";
+      return B2FIL_ERR_UNSUPPORTED;
+    }
+    b2fil_create_opts sparse_opts = opts;
+    sparse_opts.storage           = B2FIL_STORAGE_SPARSE;
+    PackedForest fresh;
+    rc = pack_forest(desc, sparse_opts, dense_ok, fresh, err);
+    if (rc == B2FIL_OK) out = std::move(fresh);
+    return rc;
   }
   return B2FIL_OK;
 }

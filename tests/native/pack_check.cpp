@@ -15,7 +15,7 @@
 using namespace b2fil;
 
 namespace {
-bool always_dense(int depth, int, int, int) { return depth <= 16; }
+int always_dense(int depth, int, int, int) { return depth <= 16 ? 1 : 0; }
 std::string g_err;
 
 template <typename T, typename V>

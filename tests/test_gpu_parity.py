@@ -93,6 +93,38 @@ def test_random_forests_operators_nan(layout, storage, precision):
 
 
 @pytest.mark.parametrize("precision", ["single", "double"])
+def test_forests_over_a_thousand_features_and_more(precision):
+    """A row tile of reals no longer fits shared memory, a tile of 16-bit ranks does: such forests
+    keep dense storage and run the traversal over rank-quantised rows at every batch size (one
+    row included) when a row visits enough nodes per feature to pay for ranking it; small
+    forests stay sparse unless dense storage is asked for.  Without rank tables
+    (quantize_rows=False) there is no dense kernel for them: sparse storage, and dense storage on
+    request is refused."""
+    from cuml_b200.fil import _lib
+
+    for n_features, n_trees, n_rows in ((1100, 140, 3000), (2500, 620, 700)):
+        desc = random_forest_desc(80 + n_features, n_trees=n_trees, n_features=n_features,
+                                  max_depth=6, mixed_ops=True, postproc="sigmoid", p_leaf=0.05)
+        X = random_rows(81, n_rows, n_features, np.float64, nan_frac=0.02)
+        fi = _all_kinds(desc, X, precision, "depth_first", "auto")
+        d = fi.describe()
+        assert d["storage"] == 1 and d["row_quantization"] == 1, d
+        assert "dense_q" in _lib.last_variant(), _lib.last_variant()
+        _all_kinds(desc, X[:1], precision, "depth_first", "auto")
+        sp = _all_kinds(desc, X[:300], precision, "depth_first", "auto", quantize_rows=False)
+        assert sp.describe()["storage"] == 2
+        with pytest.raises(Exception):
+            ForestInference.load_from_treelite_model(desc, precision=precision, storage="dense",
+                                                     quantize_rows=False)
+        # few trees: ranking 1100 or 2500 features per row costs more than the walks save
+        small = random_forest_desc(82, n_trees=12, n_features=n_features, max_depth=6)
+        fi = _all_kinds(small, X[:300], precision, "depth_first", "auto")
+        assert fi.describe()["storage"] == 2
+        fi = _all_kinds(small, X[:33], precision, "depth_first", "dense")
+        assert fi.describe()["storage"] == 1 and "dense_q" in _lib.last_variant()
+
+
+@pytest.mark.parametrize("precision", ["single", "double"])
 @pytest.mark.parametrize("quantize_rows", [True, False])
 def test_dense_with_and_without_row_quantisation(precision, quantize_rows):
     # scalar leaves, multi-class scalar leaves and vector leaves through both dense kernels
