@@ -184,17 +184,26 @@ struct CompactNode {  // 8 bytes
 // levels (4 KB per tree) with 28 warps on 128-row tiles were the best trade (9.5e7 rows/s; six
 // levels 8.9e7, nine levels - room for 12 warps only - 5.8e7).
 constexpr int kCDefaultTopLevels = 8;
+// With many features the row tile leaves little room: the heaps then get fewer levels, so that
+// 24 warps still fit under the 160 KiB that the launch code prefers (one warp per CTA next to
+// eight-level heaps ran a 1024-feature forest at 3.7e7 rows/s).
 inline int compact_pick_top_levels(int elem_bytes, int n_features, int n_outputs, int max_depth)
 {
-  const size_t budget = 218 * 1024;
-  bool fits           = false;
-  for (int R = 128; R >= 32 && !fits; R /= 2) {
-    const size_t tile = static_cast<size_t>(n_features) * (R + 1) * 4;  // rows are staged as floats
-    const size_t acc  = static_cast<size_t>(8) * n_outputs * R * elem_bytes;
-    fits = tile + acc + (static_cast<size_t>(16) << kCDefaultTopLevels) * 8 <= budget;
+  const size_t hard = 218 * 1024, soft = 160 * 1024;
+  constexpr int kWalks = 4;  // trees a warp walks at once (kCompactTreesInFlight)
+  int fallback = 0;
+  for (int T = kCDefaultTopLevels; T >= 1; --T) {
+    const size_t heap = static_cast<size_t>(16) << T;
+    for (int R = 128; R >= 32; R /= 2) {
+      const size_t tile = static_cast<size_t>(n_features) * (R + 1) * 4;  // rows are staged as floats
+      const int G       = (24 + R / 32 - 1) / (R / 32);
+      const size_t acc  = static_cast<size_t>(G) * n_outputs * R * elem_bytes;
+      if (tile + acc + heap * G * kWalks <= soft) return std::max(1, std::min(T, max_depth));
+      if (fallback == 0 && tile + static_cast<size_t>(8) * n_outputs * R * elem_bytes + heap * 8 <= hard)
+        fallback = T;
+    }
   }
-  if (!fits) return 0;
-  return std::max(1, std::min(kCDefaultTopLevels, max_depth));
+  return fallback == 0 ? 0 : std::max(1, std::min(fallback, max_depth));
 }
 
 enum NodeFormat : int32_t {

@@ -1069,13 +1069,15 @@ int pack_forest(const b2fil_forest_desc& desc, const b2fil_create_opts& opts,
     if (fit == 2 && opts.storage == B2FIL_STORAGE_AUTO) {
       // The rank pre-pass costs time in proportion to the features of a row, the walks in
       // proportion to the nodes a row visits.  With few visits per feature the sparse kernels,
-      // which rank nothing, are faster.  Measured break-even (complete trees of depth 4 to 10,
-      // 100 to 1000 trees): about half a visit per feature at 1024 and 1536 features, about
-      // 1.1 at 2048 and 3000, where the pre-pass has more feature groups than half the SMs and
-      // reads every row in 128-byte pieces.
+      // which rank nothing, are faster.  Measured break-even in node visits per feature and row
+      // (complete trees of depth 4 to 10, 100 to 1000 trees): about 2 at 1024 features, where
+      // the sparse forest still gets a compact image with 24 warps per CTA; about 0.33 at 1536,
+      // where that image runs with few warps; about 1.1 at 2048 and 3000, where there is no
+      // compact image but the pre-pass has more feature groups than half the SMs and reads
+      // every row in 128-byte pieces.
       const double nodes_per_tree = static_cast<double>(out.n_nodes_in) / std::max(1, desc.n_trees);
       const double visits = desc.n_trees * std::min<double>(max_depth, std::log2(nodes_per_tree + 1.0));
-      const double per_feature = desc.n_features <= 1536 ? 0.5 : 1.1;
+      const double per_feature = desc.n_features < 1280 ? 2.0 : (desc.n_features <= 1792 ? 0.33 : 1.1);
       if (visits < per_feature * desc.n_features) fits = false;
     }
     if (opts.storage == B2FIL_STORAGE_DENSE) {

@@ -102,7 +102,7 @@ def test_forests_over_a_thousand_features_and_more(precision):
     request is refused."""
     from cuml_b200.fil import _lib
 
-    for n_features, n_trees, n_rows in ((1100, 140, 3000), (2500, 620, 700)):
+    for n_features, n_trees, n_rows in ((1100, 400, 1500), (2500, 620, 700)):
         desc = random_forest_desc(80 + n_features, n_trees=n_trees, n_features=n_features,
                                   max_depth=6, mixed_ops=True, postproc="sigmoid", p_leaf=0.05)
         X = random_rows(81, n_rows, n_features, np.float64, nan_frac=0.02)
