@@ -69,7 +69,10 @@ extern "C" {
  * DENSE pads every tree to a complete binary tree of the forest's maximum depth and indexes
  * children implicitly (heap order), which removes the offset arithmetic from the hot loop and
  * lets whole trees be staged in shared memory.  AUTO picks DENSE when the padded forest is small
- * enough. */
+ * enough and a row tile fits shared memory next to it.  Forests with so many features (from
+ * about 800 on) that only a tile of 16-bit ranks fits are dense only together with
+ * row_quantization = 0: AUTO then weighs the cost of ranking a row against the nodes it visits,
+ * and DENSE is refused with B2FIL_ERR_UNSUPPORTED when the forest cannot be rank-quantised. */
 #define B2FIL_STORAGE_AUTO 0
 #define B2FIL_STORAGE_DENSE 1
 #define B2FIL_STORAGE_SPARSE 2
