@@ -736,13 +736,7 @@ int launch_dense_mode(const PredictParams& p, const DenseCfg& c, dim3 grid, int 
                                                  n_splits, part);
   }
   if (n_splits > 1 && MODE <= MODE_VECTOR) {
-    if (n_splits > 4) {
-      const int blocks = static_cast<int>((p.n_rows + 7) / 8);  // a warp per row
-      finish_kernel<T><<<blocks, 256, 0, stream>>>(p, part, n_splits);
-    } else {
-      const int blocks = static_cast<int>((p.n_rows + 255) / 256);
-      finish_few_splits_kernel<T><<<blocks, 256, 0, stream>>>(p, part, n_splits);
-    }
+    launch_finish_rows(p, part, n_splits, sizeof(T) == 8, stream);
   }
   return B2FIL_OK;
 }
@@ -1139,6 +1133,30 @@ std::mutex g_tuning_mu;
 std::map<std::string, int> g_tuning;
 }  // namespace
 
+namespace {
+template <typename T>
+void finish_rows(const PredictParams& p, T* part, int n_splits, cudaStream_t stream)
+{
+  if (n_splits > 4) {
+    const int blocks = static_cast<int>((p.n_rows + 7) / 8);  // a warp per row
+    finish_kernel<T><<<blocks, 256, 0, stream>>>(p, part, n_splits);
+  } else {
+    const int blocks = static_cast<int>((p.n_rows + 255) / 256);
+    finish_few_splits_kernel<T><<<blocks, 256, 0, stream>>>(p, part, n_splits);
+  }
+}
+}  // namespace
+
+void launch_finish_rows(const PredictParams& p, void* partial, int n_splits, bool f64,
+                        cudaStream_t stream)
+{
+  if (f64) {
+    finish_rows<double>(p, static_cast<double*>(partial), n_splits, stream);
+  } else {
+    finish_rows<float>(p, static_cast<float*>(partial), n_splits, stream);
+  }
+}
+
 int tuning_value(const char* key, int fallback)
 {
   std::lock_guard<std::mutex> lock(g_tuning_mu);
@@ -1313,7 +1331,8 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
     if (partial) cudaFreeAsync(partial, stream);
     if (launches && n_splits > 1 && reduce) ++*launches;
   } else if (CompactCfg cc; compact_config(f, reduce, pick_rows_per_tile(p.n_rows, chunk_size, sm_count),
-                                          p.n_rows, sm_count, cc)) {
+                                          p.n_rows, sm_count,
+                                          chunk_size <= 0 && (pool != nullptr || !reduce), cc)) {
     // deep / ragged forests with a compact image: heaps of the top levels through shared memory,
     // 8-byte internal nodes below
     LaunchRecord& rec = g_last_launch;
@@ -1327,7 +1346,8 @@ int launch_predict(const PredictParams& p, int chunk_size, int sm_count, cudaStr
     rec.R             = cc.rows_per_tile;
     rec.G             = cc.tree_groups;
     rec.S             = cc.stages;
-    rc = launch_sparse_compact(p, mode, cc, stream, err);
+    rec.splits        = cc.splits;
+    rc = launch_sparse_compact(p, mode, cc, stream, pool, err, launches);
   } else {
     const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
     int R           = pick_rows_per_tile(p.n_rows, chunk_size, sm_count);

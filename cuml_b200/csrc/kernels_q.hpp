@@ -54,15 +54,22 @@ struct CompactCfg {
   size_t smem_bytes;
   int threads;
   int grid;
+  int splits;         // CTAs that share the tree batches of a row tile (small batches), else 1
 };
 // Value of a named tuning knob (b2fil_set_tuning), or `fallback` when it was never set.
 int tuning_value(const char* key, int fallback);
 void set_tuning_value(const char* key, int value);
 // Launch shape for `n_rows` rows starting from tiles of `rows_per_tile`; false when the forest has
 // no compact image or no shape fits shared memory (the plain sparse kernel runs then).
+// `may_split`: small batches may split the forest over CTAs (needs scratch for reduced outputs).
 bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t n_rows,
-                    int sm_count, CompactCfg& cfg);
+                    int sm_count, bool may_split, CompactCfg& cfg);
 int launch_sparse_compact(const PredictParams& p, int mode, const CompactCfg& c,
-                          cudaStream_t stream, std::string& err);
+                          cudaStream_t stream, cudaMemPool_t pool, std::string& err,
+                          int64_t* launches);
+// Second step of a split prediction: add the raw sums `partial` [split][output][row] and finish
+// the rows (kernels.cu).
+void launch_finish_rows(const PredictParams& p, void* partial, int n_splits, bool f64,
+                        cudaStream_t stream);
 
 }  // namespace b2fil

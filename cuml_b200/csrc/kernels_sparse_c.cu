@@ -185,7 +185,8 @@ __device__ __forceinline__ void stage_rows_as_float(const PredictParams& p, uint
 // Shared memory: [mbarriers 256 B][row tile][accumulators][16 B][S stages of G * NT heaps].
 template <typename T, bool CAT, int MODE, int NT, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1)
-sparse_compact_kernel(const PredictParams p, const int R, const int G, const int S)
+sparse_compact_kernel(const PredictParams p, const int R, const int G, const int S,
+                      const int n_splits, T* __restrict__ partial)
 {
   using TR  = Traits<T>;
   using Val = typename TR::Val;
@@ -216,6 +217,10 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
   const int per_batch        = G * NT;
   const uint32_t stage_bytes = per_batch * top_stride;
   const int n_batches        = (f.n_trees + per_batch - 1) / per_batch;
+  // small batches: blockIdx.y splits the tree batches over CTAs (n_splits = gridDim.y); a CTA
+  // then streams and walks only its share and leaves raw sums for finish_kernel
+  const int b_begin = static_cast<int>(static_cast<int64_t>(n_batches) * blockIdx.y / n_splits);
+  const int b_end   = static_cast<int>(static_cast<int64_t>(n_batches) * (blockIdx.y + 1) / n_splits);
   const int64_t n_tiles      = (p.n_rows + R - 1) / R;
 
   if (threadIdx.x == 0) {
@@ -234,7 +239,7 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
       RingPos pos;
       bool primed = false;  // every stage has been filled once
       for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-        for (int b = 0; b < n_batches; ++b) {
+        for (int b = b_begin; b < b_end; ++b) {
           const uint32_t s = pos.stage;
           if (primed && !mbar_wait(bars + 8u * (kMaxStages + s), pos.phase ^ 1u)) {
             atomicExch(p.status, 1);
@@ -290,7 +295,7 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
     auto row_values = [&]() -> const double* {
       return row < p.n_rows ? static_cast<const double*>(p.X) + row * p.row_stride : nullptr;
     };
-    for (int b = 0; b < n_batches; ++b) {
+    for (int b = b_begin; b < b_end; ++b) {
       const uint32_t s = pos.stage;
       if (ok) ok = mbar_wait(bars + 8u * s, pos.phase);
       const int first = b * per_batch + g * NT;
@@ -470,7 +475,18 @@ sparse_compact_kernel(const PredictParams p, const int R, const int G, const int
     flush_running<T, MODE>(f, run, acc_group, R, r);
     consumer_sync(n_ct);
     if (MODE <= MODE_VECTOR) {
-      if (threadIdx.x < R) finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+      if (threadIdx.x < R) {
+        if (n_splits == 1) {
+          finish_row<T>(p, acc, R, G, threadIdx.x, row0 + threadIdx.x);
+        } else if (row0 + threadIdx.x < p.n_rows) {
+          // raw sums of this CTA's trees, laid out [split][output][row]
+          for (int c = 0; c < NC; ++c) {
+            T sum = acc[c * R + threadIdx.x];
+            for (int gg = 1; gg < G; ++gg) sum += acc[(gg * NC + c) * R + threadIdx.x];
+            partial[(static_cast<int64_t>(blockIdx.y) * NC + c) * p.n_rows + row0 + threadIdx.x] = sum;
+          }
+        }
+      }
     }
     consumer_sync(n_ct);
   }
@@ -487,41 +503,65 @@ size_t compact_smem(const ForestView& f, size_t es, bool reduce, int R, int G, i
 }
 
 template <typename T, bool CAT, int MODE>
-int launch_mode(const PredictParams& p, const CompactCfg& c, cudaStream_t stream, std::string& err)
+int launch_mode(const PredictParams& p, const CompactCfg& c, void* partial, cudaStream_t stream,
+                std::string& err)
 {
+  const dim3 grid(c.grid, c.splits);
+  T* part = static_cast<T*>(partial);
   if (c.threads > kCompactThreads) {
     auto k       = sparse_compact_kernel<T, CAT, MODE, kCompactTreesInFlight, kCompactThreadsBig>;
     const int rc = set_smem_bytes(reinterpret_cast<const void*>(k), c.smem_bytes, err);
     if (rc != B2FIL_OK) return rc;
-    k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+    k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
+                                                 c.splits, part);
     return B2FIL_OK;
   }
   auto k       = sparse_compact_kernel<T, CAT, MODE, kCompactTreesInFlight, kCompactThreads>;
   const int rc = set_smem_bytes(reinterpret_cast<const void*>(k), c.smem_bytes, err);
   if (rc != B2FIL_OK) return rc;
-  k<<<c.grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages);
+  k<<<grid, c.threads, c.smem_bytes, stream>>>(p, c.rows_per_tile, c.tree_groups, c.stages,
+                                               c.splits, part);
   return B2FIL_OK;
 }
 
 template <typename T, bool CAT>
-int launch_cat(const PredictParams& p, int mode, const CompactCfg& c, cudaStream_t stream,
-               std::string& err)
+int launch_cat(const PredictParams& p, int mode, const CompactCfg& c, void* partial,
+               cudaStream_t stream, std::string& err)
 {
   switch (mode) {
-    case MODE_SCALAR: return launch_mode<T, CAT, MODE_SCALAR>(p, c, stream, err);
-    case MODE_VECTOR: return launch_mode<T, CAT, MODE_VECTOR>(p, c, stream, err);
-    case MODE_PERTREE: return launch_mode<T, CAT, MODE_PERTREE>(p, c, stream, err);
-    default: return launch_mode<T, CAT, MODE_LEAFID>(p, c, stream, err);
+    case MODE_SCALAR: return launch_mode<T, CAT, MODE_SCALAR>(p, c, partial, stream, err);
+    case MODE_VECTOR: return launch_mode<T, CAT, MODE_VECTOR>(p, c, partial, stream, err);
+    case MODE_PERTREE: return launch_mode<T, CAT, MODE_PERTREE>(p, c, partial, stream, err);
+    default: return launch_mode<T, CAT, MODE_LEAFID>(p, c, partial, stream, err);
   }
 }
 
 }  // namespace
 
 bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t n_rows,
-                    int sm_count, CompactCfg& cfg)
+                    int sm_count, bool may_split, CompactCfg& cfg)
 {
   if (!f.c_enabled) return false;
   const size_t es = f.format == FMT_SPARSE_16D ? 8 : 4;
+  // Small batches (fewer row tiles than half the SMs): one CTA per tile would walk the whole
+  // forest batch after batch, which is what bounds their latency.  The tree batches are split
+  // over CTAs instead (tiles x splits fills the SMs once) with few tree groups per CTA, so that
+  // there are enough batches to split.
+  const int64_t small_tiles = (n_rows + 31) / 32;
+  if (may_split && small_tiles * 2 <= sm_count && tuning_value("compact_R", 0) == 0) {
+    const int want_splits = static_cast<int>(sm_count / small_tiles);
+    const int n_quads     = (f.n_trees + kCompactTreesInFlight - 1) / kCompactTreesInFlight;
+    int G                 = std::max(1, std::min(31, (n_quads + want_splits - 1) / want_splits));
+    for (; G >= 1; --G) {
+      const size_t b = compact_smem(f, es, reduce, 32, G, kCompactTreesInFlight, 1);
+      if (b > kMaxSmemBytes) continue;
+      const int per_batch = G * kCompactTreesInFlight;
+      const int n_batches = (f.n_trees + per_batch - 1) / per_batch;
+      const int splits    = std::max(1, std::min(n_batches, want_splits));
+      cfg = CompactCfg{32, G, 1, b, (G + 1) * 32, static_cast<int>(small_tiles), splits};
+      return true;
+    }
+  }
   if (const int R = tuning_value("compact_R", 0), G = tuning_value("compact_G", 0),
       S = tuning_value("compact_S", 0);
       R >= 32 && (R & (R - 1)) == 0 && R <= 128 && G >= 1 && (R / 32) * G <= 31 && S >= 1 &&
@@ -530,7 +570,7 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
     if (b <= kMaxSmemBytes) {
       const int64_t n_tiles = (n_rows + R - 1) / R;
       cfg = CompactCfg{R, G, S, b, ((R / 32) * G + 1) * 32,
-                       static_cast<int>(std::min<int64_t>(n_tiles, sm_count))};
+                       static_cast<int>(std::min<int64_t>(n_tiles, sm_count)), 1};
       return true;
     }
   }
@@ -549,7 +589,7 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
           if (b <= limit) {
             const int64_t n_tiles = (n_rows + R - 1) / R;
             cfg = CompactCfg{R, G, S, b, (rw * G + 1) * 32,
-                             static_cast<int>(std::min<int64_t>(n_tiles, sm_count))};
+                             static_cast<int>(std::min<int64_t>(n_tiles, sm_count)), 1};
             return true;
           }
         }
@@ -560,15 +600,37 @@ bool compact_config(const ForestView& f, bool reduce, int rows_per_tile, int64_t
 }
 
 int launch_sparse_compact(const PredictParams& p, int mode, const CompactCfg& c,
-                          cudaStream_t stream, std::string& err)
+                          cudaStream_t stream, cudaMemPool_t pool, std::string& err,
+                          int64_t* launches)
 {
   const ForestView& f = p.f;
-  if (f.format == FMT_SPARSE_16D) {
-    return f.has_categorical ? launch_cat<double, true>(p, mode, c, stream, err)
-                             : launch_cat<double, false>(p, mode, c, stream, err);
+  const bool f64      = f.format == FMT_SPARSE_16D;
+  void* partial       = nullptr;
+  if (c.splits > 1 && mode <= MODE_VECTOR) {
+    const size_t bytes  = static_cast<size_t>(c.splits) * f.n_outputs * p.n_rows * (f64 ? 8 : 4);
+    const cudaError_t e = cudaMallocFromPoolAsync(&partial, bytes, pool, stream);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      err = std::string("scratch allocation for split prediction failed: ") + cudaGetErrorString(e);
+      return e == cudaErrorMemoryAllocation ? B2FIL_ERR_NO_MEMORY : B2FIL_ERR_CUDA;
+    }
   }
-  return f.has_categorical ? launch_cat<float, true>(p, mode, c, stream, err)
-                           : launch_cat<float, false>(p, mode, c, stream, err);
+  int rc;
+  if (f64) {
+    rc = f.has_categorical ? launch_cat<double, true>(p, mode, c, partial, stream, err)
+                           : launch_cat<double, false>(p, mode, c, partial, stream, err);
+  } else {
+    rc = f.has_categorical ? launch_cat<float, true>(p, mode, c, partial, stream, err)
+                           : launch_cat<float, false>(p, mode, c, partial, stream, err);
+  }
+  if (partial) {
+    if (rc == B2FIL_OK) {
+      launch_finish_rows(p, partial, c.splits, f64, stream);
+      if (launches) ++*launches;
+    }
+    cudaFreeAsync(partial, stream);
+  }
+  return rc;
 }
 
 }  // namespace b2fil
