@@ -11,7 +11,9 @@
 //   2. below the heap the walk follows the compact nodes in global memory: 8-byte internal
 //      nodes, first child adjacent, (k, L) bookkeeping for the leaf number, nodes fetched as
 //      aligned 16-byte pairs so that a step from an even node to its first child needs no fetch.
-//      Every step first issues the fetches of all NT walks, then advances them.
+//      A step is straight-line code: the NT tests, then per walk compact_step, which moves
+//      (k, L) and ends in the predicated fetch for the next step; only a test that the float
+//      compare leaves open (missing value, fp64 tie) takes a branch.
 // A stage is released as soon as the warp has left the heaps, before it starts on part 2, so the
 // next batch of heaps arrives while the warps wait for their node fetches.
 // The row tile holds floats also for fp64 forests: every value is rounded DOWN to float when the
@@ -20,8 +22,10 @@
 // x > threshold, and only xl == lo leaves the answer open; then, and only then (once in 2^24
 // visits on continuous data), the walk reads the row's double from global memory and the exact
 // threshold from a side array.  So fp64 forests run on 4-byte tiles and float compares and still
-// decide every test exactly.  (fp32 forests: xl = x, lo = threshold, nothing is ever open.)
+// decide every test exactly.  (fp32 forests: xl = x, lo = threshold, only a missing value is open.)
 // Categories survive the rounding too: integers below 2^24 are floats, so trunc(xl) = trunc(x).
+// Small batches split the tree batches of a row tile over CTAs (blockIdx.y) and leave raw sums
+// for finish_kernel, like the dense kernel does.
 #include "device_common.cuh"
 #include "kernels_q.hpp"
 
