@@ -423,7 +423,29 @@ __device__ __forceinline__ void take_leaf(const PredictParams& p, int tree,
         if (c < NC) run.v[c] += __ldg(lv + c);
       }
     } else {
-      for (int c = 0; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
+      // four outputs at a time: the loads of a chunk are in flight together (one after the other
+      // they cost a load latency per output)
+      int c = 0;
+      // (vectors of a multiple of four floats start on 16-byte boundaries: one load per chunk)
+      const bool wide = sizeof(T) == 4 && (NC & 3) == 0;
+      for (; c + 4 <= NC; c += 4) {
+        T v[4], a[4];
+        if (wide) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(lv + c));
+          v[0] = static_cast<T>(q.x);
+          v[1] = static_cast<T>(q.y);
+          v[2] = static_cast<T>(q.z);
+          v[3] = static_cast<T>(q.w);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = __ldg(lv + c + u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = acc_group[(c + u) * R + r];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc_group[(c + u) * R + r] = a[u] + v[u];
+      }
+      for (; c < NC; ++c) acc_group[c * R + r] += __ldg(lv + c);
     }
   } else if (MODE == MODE_PERTREE) {
     if (row < p.n_rows) {

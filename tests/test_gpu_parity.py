@@ -221,11 +221,14 @@ def test_categorical(layout, storage, big):
 @pytest.mark.parametrize("layout,storage", CONFIGS)
 @pytest.mark.parametrize("precision", ["single", "double"])
 def test_vector_leaves(layout, storage, precision):
-    desc = random_forest_desc(5, n_trees=13, n_outputs=5, vector=True, average=True)
-    X = random_rows(6, 300, desc.n_features, np.float32)
-    _all_kinds(desc, X, precision, layout, storage)
-    if storage == "sparse":
-        _all_kinds(desc, X, precision, layout, storage, compact_nodes=False)
+    # five and eleven outputs: more than the sums a thread keeps in registers, added to shared
+    # memory four at a time with a remainder of one and of three
+    for n_outputs in (5, 8, 11):  # (eight: vectors that load 16 bytes at a time)
+        desc = random_forest_desc(5, n_trees=13, n_outputs=n_outputs, vector=True, average=True)
+        X = random_rows(6, 300, desc.n_features, np.float32)
+        _all_kinds(desc, X, precision, layout, storage)
+        if storage == "sparse":
+            _all_kinds(desc, X, precision, layout, storage, compact_nodes=False)
 
 
 @pytest.mark.parametrize("post", ["identity", "sigmoid", "exponential", "logarithm_one_plus_exp",
