@@ -276,3 +276,18 @@ def test_compact_image_of_sparse_forests(pack_check, layout):
     Xc = random_rows(3, 300, cat.n_features, np.float64, categories=75)
     _check(pack_check, cat, Xc, "double", layout, "sparse")
     _check(pack_check, cat, Xc, "single", layout, "sparse")
+
+
+def test_heap_levels_of_the_compact_image_follow_the_row_tile(pack_check):
+    """Few features: eight heap levels.  A thousand features: the row tile takes most of shared
+    memory and the heaps get fewer levels, so that a CTA still holds two dozen warps.  The walk
+    over the image gives the same leaves either way."""
+    levels = {}
+    for n_features in (24, 1000):
+        desc = random_forest_desc(90, n_trees=5, n_features=n_features, max_depth=12, p_leaf=0.1)
+        X = random_rows(4, 64, n_features, np.float32)
+        info = _check(pack_check, desc, X, "single", "depth_first", "sparse")
+        assert info[12] == 1
+        levels[n_features] = int(info[14])
+    assert levels[24] == 8
+    assert 1 <= levels[1000] < 8
