@@ -990,6 +990,28 @@ int launch_dense_q_kernel(const QLaunch& L, int mode, bool f64, std::string& err
   return launch_q_generic(L, mode, f64, err);
 }
 
+// CTAs per feature group of the rank pre-pass.  Every CTA holds the tables of one group, so the
+// grid is (CTAs per group) x (groups) and the SMs take it in waves of one CTA each.  With g
+// groups on s SMs, s / g CTAs per group fill one wave but leave s mod g SMs idle (64 groups on
+// 148 SMs: 20 idle); more, shorter CTAs per group waste less: the count that minimises
+// waves / (CTAs per group) is taken, among up to 48 or one wave's worth (a CTA loads its group's
+// tables once, about 200 KB from L2).
+int quantise_ctas_per_group(int n_groups, int sm_count, int64_t n_tiles)
+{
+  int best = 1;
+  double best_cost = 1e30;
+  const int most = std::max(48, sm_count / std::max(1, n_groups));
+  for (int gx = 1; gx <= most; ++gx) {
+    const int waves   = (gx * n_groups + sm_count - 1) / sm_count;
+    const double cost = static_cast<double>(waves) / gx;
+    if (cost < best_cost * 0.99) {  // ties and near ties: fewer CTAs
+      best_cost = cost;
+      best      = gx;
+    }
+  }
+  return static_cast<int>(std::min<int64_t>(n_tiles, best));
+}
+
 // Rank-quantised prediction: rows are processed in chunks of whole waves of tiles; for each
 // chunk the pre-pass writes the ranks into stream-ordered scratch and the traversal kernel reads
 // them back.
@@ -1059,9 +1081,7 @@ int launch_dense_q(const PredictParams& p, int mode, int chunk_size, int sm_coun
       rc  = B2FIL_ERR_CUDA;
       break;
     }
-    // one wave of persistent CTAs: every CTA loads its group's tables once
-    const int gx = static_cast<int>(
-      std::min<int64_t>(n_tiles, std::max(1, sm_count / f.q_n_groups)));
+    const int gx = quantise_ctas_per_group(f.q_n_groups, sm_count, n_tiles);
     const dim3 qgrid(gx, f.q_n_groups);
     const dim3 qblock(1024);
     if (precision == B2FIL_F32) {
@@ -1473,8 +1493,7 @@ int launch_predict_fixed_scratch(const PredictParams& p, int chunk_size, int sm_
     return B2FIL_ERR_CUDA;
   }
   const size_t q_smem = 16 + static_cast<size_t>(f.q_max_blob_bytes);
-  const int gx = static_cast<int>(
-    std::min<int64_t>(n_tiles, std::max(1, sm_count / f.q_n_groups)));
+  const int gx = quantise_ctas_per_group(f.q_n_groups, sm_count, n_tiles);
   const dim3 qgrid(gx, f.q_n_groups);
   const dim3 qblock(1024);
   if (precision == B2FIL_F32) {
